@@ -1,0 +1,150 @@
+"""Generate golden vectors for the linear-attention path from the reference itself.
+
+Run where the HazyResearch/based tree is available (``--ref`` or the
+``BASED_REFERENCE`` environment variable points at its root)::
+
+    python tests/golden/make_golden.py --ref /path/to/based
+
+It imports the reference's own ``TaylorExp`` / ``LinearAttention``
+(based/models/mixers/linear_attention.py) and ``InferenceParams``
+(based/generation.py:18-35) on CPU, runs them on seeded inputs, and writes
+small ``.npz`` files next to this script.  The tests never import the
+reference; they read these files.
+
+One import shim is needed: based/generation.py:15 imports two output classes
+that newer ``transformers`` releases no longer export.
+"""
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def import_reference(ref_root):
+    import transformers.generation as tg
+
+    for name in ("GreedySearchDecoderOnlyOutput", "SampleDecoderOnlyOutput"):
+        if not hasattr(tg, name):
+            setattr(tg, name, types.SimpleNamespace)
+    sys.path.insert(0, ref_root)
+    import contextlib
+    import io
+
+    with contextlib.redirect_stdout(io.StringIO()):
+        from based.generation import InferenceParams
+        from based.models.mixers.linear_attention import LinearAttention, TaylorExp
+    return LinearAttention, TaylorExp, InferenceParams
+
+
+def t2n(t):
+    return t.detach().to(torch.float64 if t.dtype == torch.float64 else torch.float32).numpy()
+
+
+def feature_map_case(TaylorExp):
+    torch.manual_seed(1)
+    x = torch.randn(2, 3, 5, 16, dtype=torch.float64)
+    phi = TaylorExp(input_dim=16)(x)
+    np.savez(os.path.join(HERE, "taylor_exp.npz"), x=t2n(x), phi=t2n(phi))
+
+
+def qkv_level_case(LinearAttention, TaylorExp, InferenceParams, name, B, H, L, dv, steps, dtype):
+    """Reference prefill on explicit q, k, v (out_proj = identity), then decode steps."""
+    torch.manual_seed(7)
+    d = 16
+    m = LinearAttention(d_model=H * dv, feature_map=TaylorExp(input_dim=d), feature_dim=d,
+                        num_heads=H, head_dim=dv).to(dtype)
+    m.out_proj = torch.nn.Identity()
+    q = (torch.randn(B, H, L + steps, d) / 2).to(dtype)
+    k = (torch.randn(B, H, L + steps, d) / 2).to(dtype)
+    v = torch.randn(B, H, L + steps, dv).to(dtype)
+    x = torch.zeros(B, L, H * dv, dtype=dtype)
+    m.is_inference = True
+    y, kv_state, k_state = m.parallel_forward(x, q[:, :, :L], k[:, :, :L], v[:, :, :L])
+    out = dict(q=t2n(q), k=t2n(k), v=t2n(v), y_prefill=t2n(y),
+               kv_state_prefill=t2n(kv_state), k_state_prefill=t2n(k_state))
+    kv_state, k_state = kv_state.clone(), k_state.clone()
+    fm = m.feature_map
+    ys = []
+    for s in range(steps):
+        sl = slice(L + s, L + s + 1)
+        xs = torch.zeros(B, 1, H * dv, dtype=dtype)
+        ys.append(m.recurrent_forward(xs, kv_state, k_state, fm(q[:, :, sl]), fm(k[:, :, sl]), v[:, :, sl]))
+    out["y_decode"] = t2n(torch.stack(ys, 0))          # [steps, B, 1, H*dv]
+    out["kv_state_final"] = t2n(kv_state)
+    out["k_state_final"] = t2n(k_state)
+    # the full-length parallel answer for the decoded positions (recurrent == parallel pin,
+    # based/tests/test_generation.py:169-173)
+    m.is_inference = False
+    y_full = m.parallel_forward(torch.zeros(B, L + steps, H * dv, dtype=dtype), q, k, v)
+    out["y_full"] = t2n(y_full)
+    np.savez(os.path.join(HERE, name), **out)
+
+
+def mixer_level_case(LinearAttention, TaylorExp, InferenceParams):
+    """Whole mixer with projections through forward(), prefill + 3 decode steps via InferenceParams."""
+    torch.manual_seed(0)
+    d_model, H, d, dv, B, L, steps = 64, 2, 16, 32, 2, 37, 3
+    m = LinearAttention(d_model=d_model, feature_map=TaylorExp(input_dim=d), feature_dim=d,
+                        num_heads=H, head_dim=dv, layer_idx=0)
+    x = torch.randn(B, L + steps, d_model)
+    y_train = m(x[:, :L])
+    ip = InferenceParams(max_seqlen=L + steps, max_batch_size=B)
+    y_prefill = m(x[:, :L], inference_params=ip)
+    kv0, k0 = [t.clone() for t in ip.key_value_memory_dict[0]]
+    ys = []
+    for s in range(steps):
+        ip.seqlen_offset = L + s
+        ys.append(m(x[:, L + s: L + s + 1], inference_params=ip))
+    kv1, k1 = ip.key_value_memory_dict[0]
+    np.savez(os.path.join(HERE, "linattn_mixer.npz"),
+             x=t2n(x), wq=t2n(m.proj_q.weight), wk=t2n(m.proj_k.weight), wv=t2n(m.proj_v.weight),
+             wo=t2n(m.out_proj.weight), y_train=t2n(y_train), y_prefill=t2n(y_prefill),
+             kv_state_prefill=t2n(kv0), k_state_prefill=t2n(k0),
+             y_decode=t2n(torch.cat(ys, 1)), kv_state_final=t2n(kv1), k_state_final=t2n(k1),
+             meta=np.array([d_model, H, d, dv, B, L, steps]))
+
+
+def config1_samples(LinearAttention, TaylorExp, InferenceParams):
+    """BASELINE config 1 (d_model 1024, 16 heads, feature_dim 16, head_dim 64, B=2, L=1024, fp32, seed 0):
+    the inputs are regenerated from the seed by the test; only strided samples of the outputs are stored."""
+    torch.manual_seed(0)
+    m = LinearAttention(d_model=1024, feature_map=TaylorExp(input_dim=16), feature_dim=16,
+                        num_heads=16, head_dim=64, layer_idx=0)
+    x = torch.randn(2, 1024, 1024)
+    ip = InferenceParams(max_seqlen=1024, max_batch_size=2)
+    with torch.no_grad():
+        y = m(x, inference_params=ip)
+        y_train = m(x)
+    kv, ks = ip.key_value_memory_dict[0]
+    np.savez(os.path.join(HERE, "linattn_config1_samples.npz"),
+             y=t2n(y[:, ::37, ::29]), y_train=t2n(y_train[:, ::37, ::29]),
+             kv_state=t2n(kv[:, ::5, :, ::7, ::11]), k_state=t2n(ks[..., ::3]),
+             x_probe=t2n(x[:, ::301, ::307]), wq_probe=t2n(m.proj_q.weight[::31, ::101]),
+             y_abs_mean=np.float64(y.abs().mean().item()))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default=os.environ.get("BASED_REFERENCE"))
+    args = ap.parse_args()
+    if not args.ref:
+        ap.error("--ref or BASED_REFERENCE must point at the HazyResearch/based tree")
+    LA, TE, IP = import_reference(args.ref)
+    with torch.no_grad():
+        feature_map_case(TE)
+        qkv_level_case(LA, TE, IP, "linattn_qkv_f64.npz", B=1, H=2, L=77, dv=64, steps=4, dtype=torch.float64)
+        qkv_level_case(LA, TE, IP, "linattn_qkv_f32_dv112.npz", B=1, H=2, L=130, dv=112, steps=2, dtype=torch.float32)
+        mixer_level_case(LA, TE, IP)
+        config1_samples(LA, TE, IP)
+    for f in sorted(os.listdir(HERE)):
+        if f.endswith(".npz"):
+            print(f, os.path.getsize(os.path.join(HERE, f)))
+
+
+if __name__ == "__main__":
+    main()

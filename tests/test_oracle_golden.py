@@ -1,0 +1,100 @@
+"""The CPU oracle against golden vectors produced by the reference's own code
+(tests/golden/make_golden.py).  No GPU, no reference import."""
+import torch
+
+from conftest import load_golden, rel_err
+from oracle import based_oracle as O
+
+
+def test_taylor_exp_matches_reference():
+    g = load_golden("taylor_exp.npz")
+    phi = O.taylor_exp(g["x"])
+    assert phi.shape[-1] == 273 == O.expanded_size(16)
+    assert rel_err(phi, g["phi"]) < 1e-14
+
+
+def test_feature_inner_product_identity():
+    # phi(q).phi(k) = 1 + s + s^2/2 with s = q.k/sqrt(d): what the kernels rely on
+    torch.manual_seed(3)
+    q, k = torch.randn(50, 16, dtype=torch.float64), torch.randn(50, 16, dtype=torch.float64)
+    s = (q * k).sum(-1) / 4
+    lhs = (O.taylor_exp(q) * O.taylor_exp(k)).sum(-1)
+    assert torch.allclose(lhs, 1 + s + s * s / 2, rtol=1e-13, atol=1e-13)
+
+
+def _check_qkv_case(name, dtype, tol):
+    g = load_golden(name, dtype)
+    L = g["y_prefill"].shape[1]
+    B, H, Ltot, d = g["q"].shape
+    dv = g["v"].shape[-1]
+    steps = Ltot - L
+    q, k, v = g["q"], g["k"], g["v"]
+    y, kv, ks = O.linattn_parallel(q[:, :, :L], k[:, :, :L], v[:, :, :L])
+    y_blhd = y.transpose(1, 2).reshape(B, L, H * dv)
+    assert rel_err(y_blhd, g["y_prefill"]) < tol
+    assert kv.shape == g["kv_state_prefill"].shape == (B, H, 1, dv, 273)
+    assert ks.shape == g["k_state_prefill"].shape == (B, H, 1, 1, 273)
+    assert rel_err(kv, g["kv_state_prefill"]) < tol
+    assert rel_err(ks, g["k_state_prefill"]) < tol
+    # chunked restatement == quadratic, including a ragged last chunk
+    for chunk in (16, 33, 256):
+        yc, kvc, ksc = O.linattn_chunked(q[:, :, :L], k[:, :, :L], v[:, :, :L], chunk=chunk)
+        assert rel_err(yc, y) < tol and rel_err(kvc, kv) < tol and rel_err(ksc, ks) < tol
+    # decode steps from the prefill state
+    for s in range(steps):
+        sl = slice(L + s, L + s + 1)
+        ys = O.linattn_recurrent_step(kv, ks, q[:, :, sl], k[:, :, sl], v[:, :, sl])
+        ys = ys.transpose(1, 2).reshape(B, 1, H * dv)
+        assert rel_err(ys, g["y_decode"][s]) < tol
+        # recurrent == parallel (based/tests/test_generation.py:169-173)
+        assert rel_err(ys[:, 0], g["y_full"][:, L + s]) < 10 * tol
+    assert rel_err(kv, g["kv_state_final"]) < tol
+    assert rel_err(ks, g["k_state_final"]) < tol
+
+
+def test_linattn_qkv_f64():
+    _check_qkv_case("linattn_qkv_f64.npz", torch.float64, 1e-12)
+
+
+def test_linattn_qkv_f32_dv112():
+    _check_qkv_case("linattn_qkv_f32_dv112.npz", torch.float32, 2e-5)
+
+
+def test_linattn_mixer_forward():
+    g = load_golden("linattn_mixer.npz")
+    d_model, H, d, dv, B, L, steps = [int(x) for x in g["meta"]]
+    x = g["x"]
+    out, kv, ks = O.linattn_mixer_forward(x[:, :L], g["wq"], g["wk"], g["wv"], g["wo"], H, d, dv)
+    assert rel_err(out, g["y_prefill"]) < 2e-5
+    assert rel_err(out, g["y_train"]) < 2e-5
+    assert rel_err(kv, g["kv_state_prefill"]) < 2e-5
+    assert rel_err(ks, g["k_state_prefill"]) < 2e-5
+    for s in range(steps):
+        xs = x[:, L + s: L + s + 1]
+        q = (xs @ g["wq"].T).view(B, 1, H, d).transpose(1, 2)
+        k = (xs @ g["wk"].T).view(B, 1, H, d).transpose(1, 2)
+        v = (xs @ g["wv"].T).view(B, 1, H, dv).transpose(1, 2)
+        y = O.linattn_recurrent_step(kv, ks, q, k, v).transpose(1, 2).reshape(B, 1, H * dv)
+        assert rel_err(y @ g["wo"].T, g["y_decode"][:, s: s + 1]) < 2e-5
+    assert rel_err(kv, g["kv_state_final"]) < 2e-5
+    assert rel_err(ks, g["k_state_final"]) < 2e-5
+
+
+def test_linattn_config1_samples():
+    """BASELINE config 1 at full size: inputs regenerated from seed 0, outputs compared
+    with strided samples the reference produced."""
+    g = load_golden("linattn_config1_samples.npz")
+    torch.manual_seed(0)
+    lin = [torch.nn.Linear(1024, n, bias=False) for n in (256, 256, 1024)]
+    out_proj = torch.nn.Linear(1024, 1024, bias=False)
+    x = torch.randn(2, 1024, 1024)
+    if rel_err(x[:, ::301, ::307], g["x_probe"]) > 0 or rel_err(lin[0].weight[::31, ::101], g["wq_probe"]) > 0:
+        import pytest
+        pytest.skip("torch RNG stream differs from the one the fixture was generated with")
+    with torch.no_grad():
+        out, kv, ks = O.linattn_mixer_forward(x, lin[0].weight, lin[1].weight, lin[2].weight,
+                                              out_proj.weight, 16, 16, 64)
+    assert rel_err(out[:, ::37, ::29], g["y"]) < 1e-4
+    assert rel_err(out[:, ::37, ::29], g["y_train"]) < 1e-4
+    assert rel_err(kv[:, ::5, :, ::7, ::11], g["kv_state"]) < 1e-4
+    assert rel_err(ks[..., ::3], g["k_state"]) < 1e-4
