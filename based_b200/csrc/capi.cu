@@ -1,0 +1,134 @@
+// extern "C" entry points: host-side argument validation, then dispatch to the launchers.
+// Nothing here allocates device memory or synchronises.
+#include "common.cuh"
+
+using namespace based;
+
+namespace {
+
+bool dtype_ok(int dt) { return dt == BASED_F32 || dt == BASED_BF16; }
+size_t dtype_size(int dt) { return dt == BASED_F32 ? 4 : 2; }
+Strides3 s3(const int64_t* s) { return Strides3{s[0], s[1], s[2]}; }
+Strides2 s2(const int64_t* s) { return Strides2{s[0], s[1]}; }
+
+}  // namespace
+
+extern "C" {
+
+int based_b200_version(void) { return 1; }
+
+const char* based_error_string(int code) {
+  switch (code) {
+    case BASED_OK: return "ok";
+    case BASED_ERR_NULL: return "a required pointer is NULL";
+    case BASED_ERR_SHAPE: return "unsupported shape";
+    case BASED_ERR_DTYPE: return "unsupported dtype";
+    case BASED_ERR_ALIGN: return "pointer or stride not aligned as required";
+    case BASED_ERR_IMPL: return "requested implementation cannot run these arguments";
+    case BASED_ERR_TOO_LARGE: return "size exceeds a fixed capacity";
+    default: break;
+  }
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "unknown error";
+}
+
+int based_linattn_prefill(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
+                          int B, int H, int L, int d, int dv, const int64_t q_strides[3],
+                          const int64_t k_strides[3], const int64_t v_strides[3], const int64_t y_strides[3],
+                          int io_dtype, int state_dtype, float eps, int impl, void* stream) {
+  if (!q || !k || !v || !y || !q_strides || !k_strides || !v_strides || !y_strides) return BASED_ERR_NULL;
+  if ((kv_state == nullptr) != (k_state == nullptr)) return BASED_ERR_NULL;
+  if (!dtype_ok(io_dtype) || !dtype_ok(state_dtype)) return BASED_ERR_DTYPE;
+  if (B < 0 || H < 0 || L < 0 || d != kFeatureDim || dv < 16 || dv > 128 || dv % 16 != 0) return BASED_ERR_SHAPE;
+  if ((int64_t)B * H > 2147483647LL) return BASED_ERR_TOO_LARGE;
+  if (B == 0 || H == 0) return BASED_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (L == 0) {
+    // empty sequence: the states are the empty sums
+    if (kv_state) {
+      const size_t es = dtype_size(state_dtype);
+      cudaError_t e = cudaMemsetAsync(kv_state, 0, (size_t)B * H * dv * kExpandedDim * es, st);
+      if (e == cudaSuccess) e = cudaMemsetAsync(k_state, 0, (size_t)B * H * kExpandedDim * es, st);
+      return (int)e;
+    }
+    return BASED_OK;
+  }
+  // AUTO: the tensor-core kernel when it accepts the arguments (bf16 I/O, its alignment
+  // rules), else the CUDA-core kernel.  Both are GPU kernels; there is no host path.
+  const bool autosel = impl == BASED_IMPL_AUTO;
+  if (autosel) impl = (io_dtype == BASED_BF16) ? BASED_IMPL_TCGEN05 : BASED_IMPL_SIMT;
+  if (impl == BASED_IMPL_TCGEN05) {
+    if (io_dtype != BASED_BF16) return BASED_ERR_IMPL;
+    const int rc = launch_linattn_prefill_tc(q, k, v, y, kv_state, k_state, B, H, L, dv, s3(q_strides),
+                                             s3(k_strides), s3(v_strides), s3(y_strides), state_dtype, eps, st);
+    if (!(autosel && rc == BASED_ERR_IMPL)) return rc;
+    impl = BASED_IMPL_SIMT;
+  }
+  if (impl != BASED_IMPL_SIMT) return BASED_ERR_IMPL;
+  return launch_linattn_prefill_simt(q, k, v, y, kv_state, k_state, B, H, L, dv, s3(q_strides), s3(k_strides),
+                                     s3(v_strides), s3(y_strides), io_dtype, state_dtype, eps, st);
+}
+
+int based_linattn_decode(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
+                         int B, int H, int d, int dv, const int64_t q_strides[2], const int64_t k_strides[2],
+                         const int64_t v_strides[2], const int64_t y_strides[2], int io_dtype, int state_dtype,
+                         float eps, void* stream) {
+  if (!q || !k || !v || !y || !kv_state || !k_state || !q_strides || !k_strides || !v_strides || !y_strides)
+    return BASED_ERR_NULL;
+  if (!dtype_ok(io_dtype) || !dtype_ok(state_dtype)) return BASED_ERR_DTYPE;
+  const int rows_per_group = state_dtype == BASED_F32 ? 4 : 8;
+  if (B < 0 || H < 0 || d != kFeatureDim || dv < rows_per_group || dv > 128 || dv % rows_per_group != 0)
+    return BASED_ERR_SHAPE;
+  if ((int64_t)B * H > 2147483647LL) return BASED_ERR_TOO_LARGE;
+  if (!aligned16(kv_state)) return BASED_ERR_ALIGN;
+  if (B == 0 || H == 0) return BASED_OK;
+  return launch_linattn_decode(q, k, v, y, kv_state, k_state, B, H, dv, s2(q_strides), s2(k_strides),
+                               s2(v_strides), s2(y_strides), io_dtype, state_dtype, eps,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int based_swa_prefill(const void* q, const void* k, const void* v, void* o, int B, int L, int H, int hd,
+                      const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                      const int64_t o_strides[3], int window_left, float softmax_scale, int io_dtype, int impl,
+                      void* stream) {
+  if (!q || !k || !v || !o || !q_strides || !k_strides || !v_strides || !o_strides) return BASED_ERR_NULL;
+  if (!dtype_ok(io_dtype)) return BASED_ERR_DTYPE;
+  if (B < 0 || H < 0 || L < 0 || hd < 16 || hd > 128 || hd % 16 != 0 || window_left < 0) return BASED_ERR_SHAPE;
+  if (H > 65535 || B > 65535) return BASED_ERR_TOO_LARGE;
+  if (B == 0 || H == 0 || L == 0) return BASED_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool autosel = impl == BASED_IMPL_AUTO;
+  if (autosel) impl = (io_dtype == BASED_BF16) ? BASED_IMPL_TCGEN05 : BASED_IMPL_SIMT;
+  if (impl == BASED_IMPL_TCGEN05) {
+    if (io_dtype != BASED_BF16) return BASED_ERR_IMPL;
+    const int rc = launch_swa_prefill_tc(q, k, v, o, B, L, H, hd, s3(q_strides), s3(k_strides), s3(v_strides),
+                                         s3(o_strides), window_left, softmax_scale, st);
+    if (!(autosel && rc == BASED_ERR_IMPL)) return rc;
+    impl = BASED_IMPL_SIMT;
+  }
+  if (impl != BASED_IMPL_SIMT) return BASED_ERR_IMPL;
+  return launch_swa_prefill_simt(q, k, v, o, B, L, H, hd, s3(q_strides), s3(k_strides), s3(v_strides),
+                                 s3(o_strides), window_left, softmax_scale, io_dtype, st);
+}
+
+int based_swa_decode(const void* q, const void* k_new, const void* v_new, void* o, void* kv_cache,
+                     const int32_t* cache_seqlens, int cache_seqlen_scalar, const void* rotary_cos,
+                     const void* rotary_sin, int rotary_dim, int B, int H, int hd, int max_seqlen,
+                     const int64_t q_strides[2], const int64_t k_strides[2], const int64_t v_strides[2],
+                     const int64_t o_strides[2], int window_left, float softmax_scale, int io_dtype, void* stream) {
+  if (!q || !k_new || !v_new || !o || !kv_cache || !q_strides || !k_strides || !v_strides || !o_strides)
+    return BASED_ERR_NULL;
+  if ((rotary_cos == nullptr) != (rotary_sin == nullptr)) return BASED_ERR_NULL;
+  if (!dtype_ok(io_dtype)) return BASED_ERR_DTYPE;
+  if (B < 0 || H < 0 || hd < 16 || hd > 128 || hd % 16 != 0 || window_left < 0 || max_seqlen <= 0)
+    return BASED_ERR_SHAPE;
+  if (rotary_cos && (rotary_dim <= 0 || rotary_dim > hd || rotary_dim % 2 != 0)) return BASED_ERR_SHAPE;
+  if (!cache_seqlens && (cache_seqlen_scalar < 0 || cache_seqlen_scalar >= max_seqlen)) return BASED_ERR_SHAPE;
+  if (B == 0 || H == 0) return BASED_OK;
+  return launch_swa_decode(q, k_new, v_new, o, kv_cache, cache_seqlens, cache_seqlen_scalar, rotary_cos, rotary_sin,
+                           rotary_dim, B, H, hd, max_seqlen, s2(q_strides), s2(k_strides), s2(v_strides),
+                           s2(o_strides), window_left, softmax_scale, io_dtype,
+                           static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,227 @@
+// Sliding-window causal softmax attention on CUDA cores: the prefill kernel used for fp32 I/O
+// and as the reference point of the tensor-core kernel, and the decode-step kernel (RoPE on
+// q/k at the new position, append to the KV cache, attend over <= window_left+1 cached keys),
+// which is latency/bandwidth-bound and needs no tensor cores.
+//
+// Semantics follow the reference's calls into flash-attn:
+//   prefill  based/models/mixers/slide_attention.py:100-106, :206-213
+//            (causal=True, window_size=(window_left, 0): keys [i - window_left, i])
+//   decode   slide_attention.py:414-427, :471-481 (append at cache_seqlens, then attend)
+//   RoPE     based/ops/triton/rotary.py:75-105 (non-interleaved halves, fp32 math)
+#include "common.cuh"
+
+namespace based {
+namespace {
+
+constexpr int kWarpsPerBlock = 4;
+constexpr int kMaxHd = 128;
+constexpr int kMaxKeysPerLane = 9;  // supports window_left + 1 <= 288
+
+// One warp per query.  Lane l scores keys lo + l, lo + l + 32, ...; then the lanes switch to
+// owning output channels for the weighted sum of value rows.
+template <typename IO>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+swa_prefill_simt_kernel(const IO* __restrict__ q, const IO* __restrict__ k, const IO* __restrict__ v,
+                        IO* __restrict__ o, int L, int H, int hd, Strides3 sq, Strides3 sk, Strides3 sv,
+                        Strides3 so, int window_left, float scale) {
+  __shared__ float s_q[kWarpsPerBlock][kMaxHd];
+  __shared__ float s_p[kWarpsPerBlock][kMaxKeysPerLane * 32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i = blockIdx.x * kWarpsPerBlock + warp;  // query position
+  const int h = blockIdx.y, b = blockIdx.z;
+  if (i >= L) return;
+  const IO* qp = q + b * sq.b + (int64_t)i * sq.l + h * sq.h;
+  for (int c = lane; c < hd; c += 32) s_q[warp][c] = to_float(qp[c]);
+  __syncwarp();
+  const int lo = max(0, i - window_left);
+  const int nk = i - lo + 1;
+  float sc[kMaxKeysPerLane];
+  float m = -INFINITY;
+#pragma unroll
+  for (int n = 0; n < kMaxKeysPerLane; ++n) {
+    const int jj = lane + 32 * n;
+    sc[n] = -INFINITY;
+    if (jj < nk) {
+      const IO* kp = k + b * sk.b + (int64_t)(lo + jj) * sk.l + h * sk.h;
+      float dot = 0.f;
+      for (int c = 0; c < hd; ++c) dot = fmaf(s_q[warp][c], to_float(kp[c]), dot);
+      sc[n] = dot * scale;
+      m = fmaxf(m, sc[n]);
+    }
+  }
+  m = warp_max(m);
+  float sum = 0.f;
+#pragma unroll
+  for (int n = 0; n < kMaxKeysPerLane; ++n) {
+    const int jj = lane + 32 * n;
+    if (jj < nk) {
+      const float p = __expf(sc[n] - m);
+      s_p[warp][jj] = p;
+      sum += p;
+    }
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  const float inv = 1.f / sum;
+  for (int c = lane; c < hd; c += 32) {
+    float acc = 0.f;
+    for (int jj = 0; jj < nk; ++jj) {
+      acc = fmaf(s_p[warp][jj], to_float(v[b * sv.b + (int64_t)(lo + jj) * sv.l + h * sv.h + c]), acc);
+    }
+    o[b * so.b + (int64_t)i * so.l + h * so.h + c] = from_float<IO>(acc * inv);
+  }
+}
+
+// One warp per (batch, head).
+template <typename IO>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+swa_decode_kernel(const IO* __restrict__ q, const IO* __restrict__ k_new, const IO* __restrict__ v_new,
+                  IO* __restrict__ o, IO* __restrict__ kv_cache, const int32_t* __restrict__ cache_seqlens,
+                  int cache_seqlen_scalar, const IO* __restrict__ rcos, const IO* __restrict__ rsin, int rotary_dim,
+                  int BH, int H, int hd, int max_seqlen, Strides2 sq, Strides2 sk, Strides2 sv, Strides2 so,
+                  int window_left, float scale) {
+  __shared__ float s_q[kWarpsPerBlock][kMaxHd];
+  __shared__ float s_k[kWarpsPerBlock][kMaxHd];
+  __shared__ float s_p[kWarpsPerBlock][kMaxKeysPerLane * 32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x * kWarpsPerBlock + warp;
+  if (bh >= BH) return;
+  const int b = bh / H, h = bh - b * H;
+  const int pos = cache_seqlens ? cache_seqlens[b] : cache_seqlen_scalar;
+  if (pos < 0 || pos >= max_seqlen) return;  // nothing sensible to do; the host validates the scalar case
+  const IO* qp = q + b * sq.b + h * sq.h;
+  const IO* kp = k_new + b * sk.b + h * sk.h;
+  const IO* vp = v_new + b * sv.b + h * sv.h;
+  for (int c = lane; c < hd; c += 32) {
+    s_q[warp][c] = to_float(qp[c]);
+    s_k[warp][c] = to_float(kp[c]);
+  }
+  __syncwarp();
+  const size_t row = (size_t)2 * H * hd;  // elements per cached position
+  IO* cache_b = kv_cache + (size_t)b * max_seqlen * row;
+  IO* knew = cache_b + (size_t)pos * row + (size_t)h * hd;
+  IO* vnew = knew + (size_t)H * hd;
+  // RoPE in fp32, result rounded to the I/O dtype like the reference kernel's store.
+  const int half = rcos ? rotary_dim / 2 : 0;
+  float qr[kMaxHd / 32], kr[kMaxHd / 32];
+#pragma unroll
+  for (int n = 0; n < kMaxHd / 32; ++n) {
+    const int c = lane + 32 * n;
+    if (c < hd) {
+      float qv = s_q[warp][c], kv = s_k[warp][c];
+      if (c < 2 * half) {
+        const int cc = c < half ? c : c - half;
+        const float cs = to_float(rcos[(size_t)pos * half + cc]);
+        const float sn = to_float(rsin[(size_t)pos * half + cc]);
+        if (c < half) {
+          qv = s_q[warp][c] * cs - s_q[warp][c + half] * sn;
+          kv = s_k[warp][c] * cs - s_k[warp][c + half] * sn;
+        } else {
+          qv = s_q[warp][c - half] * sn + s_q[warp][c] * cs;
+          kv = s_k[warp][c - half] * sn + s_k[warp][c] * cs;
+        }
+      }
+      qr[n] = to_float(from_float<IO>(qv));
+      kr[n] = to_float(from_float<IO>(kv));
+    }
+  }
+  __syncwarp();
+#pragma unroll
+  for (int n = 0; n < kMaxHd / 32; ++n) {
+    const int c = lane + 32 * n;
+    if (c < hd) {
+      s_q[warp][c] = qr[n];
+      knew[c] = from_float<IO>(kr[n]);
+      vnew[c] = vp[c];
+    }
+  }
+  __syncwarp();  // orders this warp's cache writes before its reads below
+  const int lo = max(0, pos - window_left);
+  const int nk = pos - lo + 1;
+  float sc[kMaxKeysPerLane];
+  float m = -INFINITY;
+#pragma unroll
+  for (int n = 0; n < kMaxKeysPerLane; ++n) {
+    const int jj = lane + 32 * n;
+    sc[n] = -INFINITY;
+    if (jj < nk) {
+      const IO* kc = cache_b + (size_t)(lo + jj) * row + (size_t)h * hd;
+      float dot = 0.f;
+      for (int c = 0; c < hd; ++c) dot = fmaf(s_q[warp][c], to_float(kc[c]), dot);
+      sc[n] = dot * scale;
+      m = fmaxf(m, sc[n]);
+    }
+  }
+  m = warp_max(m);
+  float sum = 0.f;
+#pragma unroll
+  for (int n = 0; n < kMaxKeysPerLane; ++n) {
+    const int jj = lane + 32 * n;
+    if (jj < nk) {
+      const float p = __expf(sc[n] - m);
+      s_p[warp][jj] = p;
+      sum += p;
+    }
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  const float inv = 1.f / sum;
+  for (int c = lane; c < hd; c += 32) {
+    float acc = 0.f;
+    for (int jj = 0; jj < nk; ++jj) {
+      const IO* vc = cache_b + (size_t)(lo + jj) * row + (size_t)(H + h) * hd;
+      acc = fmaf(s_p[warp][jj], to_float(vc[c]), acc);
+    }
+    o[b * so.b + h * so.h + c] = from_float<IO>(acc * inv);
+  }
+}
+
+}  // namespace
+
+int launch_swa_prefill_simt(const void* q, const void* k, const void* v, void* o, int B, int L, int H, int hd,
+                            Strides3 sq, Strides3 sk, Strides3 sv, Strides3 so, int window_left, float scale,
+                            int io_dtype, cudaStream_t stream) {
+  if (window_left + 1 > kMaxKeysPerLane * 32) return BASED_ERR_TOO_LARGE;
+  const dim3 grid((L + kWarpsPerBlock - 1) / kWarpsPerBlock, H, B);
+  if (io_dtype == BASED_BF16) {
+    using T = __nv_bfloat16;
+    swa_prefill_simt_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), static_cast<T*>(o), L, H, hd,
+        sq, sk, sv, so, window_left, scale);
+  } else if (io_dtype == BASED_F32) {
+    swa_prefill_simt_kernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
+        static_cast<float*>(o), L, H, hd, sq, sk, sv, so, window_left, scale);
+  } else {
+    return BASED_ERR_DTYPE;
+  }
+  return (int)cudaGetLastError();
+}
+
+int launch_swa_decode(const void* q, const void* k_new, const void* v_new, void* o, void* kv_cache,
+                      const int32_t* cache_seqlens, int cache_seqlen_scalar, const void* rotary_cos,
+                      const void* rotary_sin, int rotary_dim, int B, int H, int hd, int max_seqlen, Strides2 sq,
+                      Strides2 sk, Strides2 sv, Strides2 so, int window_left, float scale, int io_dtype,
+                      cudaStream_t stream) {
+  if (window_left + 1 > kMaxKeysPerLane * 32) return BASED_ERR_TOO_LARGE;
+  const int BH = B * H;
+  const int grid = (BH + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (io_dtype == BASED_BF16) {
+    using T = __nv_bfloat16;
+    swa_decode_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        static_cast<const T*>(q), static_cast<const T*>(k_new), static_cast<const T*>(v_new), static_cast<T*>(o),
+        static_cast<T*>(kv_cache), cache_seqlens, cache_seqlen_scalar, static_cast<const T*>(rotary_cos),
+        static_cast<const T*>(rotary_sin), rotary_dim, BH, H, hd, max_seqlen, sq, sk, sv, so, window_left, scale);
+  } else if (io_dtype == BASED_F32) {
+    swa_decode_kernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+        static_cast<const float*>(q), static_cast<const float*>(k_new), static_cast<const float*>(v_new),
+        static_cast<float*>(o), static_cast<float*>(kv_cache), cache_seqlens, cache_seqlen_scalar,
+        static_cast<const float*>(rotary_cos), static_cast<const float*>(rotary_sin), rotary_dim, BH, H, hd,
+        max_seqlen, sq, sk, sv, so, window_left, scale);
+  } else {
+    return BASED_ERR_DTYPE;
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // namespace based

@@ -1,0 +1,191 @@
+"""Torch-facing wrappers of the C-ABI kernels.
+
+Each function validates what only the Python side can know (device, dtype, contiguity of
+the innermost dimension), passes raw device pointers, element strides and torch's current
+stream to the library, and returns torch tensors.  CUDA tensors only.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _capi
+from ._capi import BASED_BF16, BASED_F32, IMPL_AUTO, IMPL_SIMT, IMPL_TCGEN05  # noqa: F401
+
+EXPANDED_DIM = 273
+_IMPLS = {"auto": IMPL_AUTO, "simt": IMPL_SIMT, "tcgen05": IMPL_TCGEN05}
+
+
+def _dt(t: torch.dtype) -> int:
+    if t == torch.float32:
+        return BASED_F32
+    if t == torch.bfloat16:
+        return BASED_BF16
+    raise TypeError(f"unsupported dtype {t}: the kernels take float32 or bfloat16")
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("based_b200 ops run on CUDA tensors only (there is no CPU path)")
+
+
+def _inner_contig(t, name):
+    if t.stride(-1) != 1:
+        raise ValueError(f"{name}: innermost stride must be 1")
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def linattn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: float = 1e-12,
+                    return_state: bool = True, state_dtype: Optional[torch.dtype] = None,
+                    out: Optional[torch.Tensor] = None, impl: str = "auto",
+                    kv_state: Optional[torch.Tensor] = None, k_state: Optional[torch.Tensor] = None,
+                    ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """Causal Taylor linear attention over a whole sequence.
+
+    q, k ``[B, H, L, 16]`` (raw), v ``[B, H, L, dv]``; any batch/head/seq strides (e.g. the
+    transposed views LinearAttention.forward makes, linear_attention.py:127-129).
+    Returns ``y`` as a ``[B, H, L, dv]`` view of a ``[B, L, H, dv]`` buffer (so the reference's
+    ``'b h l d -> b l (h d)'`` rearrange is free), ``kv_state [B, H, 1, dv, 273]`` and
+    ``k_state [B, H, 1, 1, 273]`` (linear_attention.py:220-222), or ``None`` for the states
+    when ``return_state`` is false.  ``kv_state``/``k_state`` may be given to be filled in place.
+    """
+    _need_cuda(q, k, v)
+    B, H, L, d = q.shape
+    dv = v.shape[-1]
+    if k.shape != q.shape or v.shape[:3] != q.shape[:3]:
+        raise ValueError("q, k, v shapes disagree")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError("q, k, v must share a dtype")
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _inner_contig(t, n)
+    if out is None:
+        out = torch.empty(B, L, H, dv, dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
+    else:
+        _inner_contig(out, "out")
+    sdt = state_dtype or (kv_state.dtype if kv_state is not None else q.dtype)
+    if return_state:
+        if kv_state is None:
+            kv_state = torch.empty(B, H, 1, dv, EXPANDED_DIM, dtype=sdt, device=q.device)
+            k_state = torch.empty(B, H, 1, 1, EXPANDED_DIM, dtype=sdt, device=q.device)
+        elif not (kv_state.is_contiguous() and k_state.is_contiguous()):
+            raise ValueError("kv_state / k_state must be contiguous")
+    with torch.cuda.device(q.device):
+        code = _capi.lib().based_linattn_prefill(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+            kv_state.data_ptr() if return_state else None, k_state.data_ptr() if return_state else None,
+            B, H, L, d, dv,
+            _capi.strides(*q.stride()[:3]), _capi.strides(*k.stride()[:3]),
+            _capi.strides(*v.stride()[:3]), _capi.strides(*out.stride()[:3]),
+            _dt(q.dtype), _dt(sdt), float(eps), _IMPLS[impl], _stream())
+    _capi.check(code, "based_linattn_prefill")
+    return out, (kv_state if return_state else None), (k_state if return_state else None)
+
+
+def linattn_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_state: torch.Tensor,
+                   k_state: torch.Tensor, *, eps: float = 1e-12, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One recurrent step; ``kv_state``/``k_state`` are updated IN PLACE.
+
+    q, k ``[B, H, 1, 16]`` or ``[B, H, 16]`` (raw), v ``[B, H, 1, dv]`` or ``[B, H, dv]``;
+    ``kv_state [B, H, 1, dv, 273]``, ``k_state [B, H, 1, 1, 273]`` (fp32 or bf16).
+    Returns ``y [B, 1, H*dv]`` in ``q.dtype`` (the layout recurrent_forward hands to out_proj,
+    linear_attention.py:251).
+    """
+    _need_cuda(q, k, v, kv_state, k_state)
+    if q.dim() == 4:
+        q, k, v = q[:, :, 0], k[:, :, 0], v[:, :, 0]
+    B, H, d = q.shape
+    dv = v.shape[-1]
+    if kv_state.shape != (B, H, 1, dv, EXPANDED_DIM) or k_state.shape != (B, H, 1, 1, EXPANDED_DIM):
+        raise ValueError(f"state shapes {tuple(kv_state.shape)}, {tuple(k_state.shape)} do not match B={B} H={H} dv={dv}")
+    if not (kv_state.is_contiguous() and k_state.is_contiguous()):
+        raise ValueError("kv_state / k_state must be contiguous")
+    if kv_state.dtype != k_state.dtype:
+        raise TypeError("kv_state and k_state must share a dtype")
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _inner_contig(t, n)
+    if out is None:
+        out = torch.empty(B, 1, H * dv, dtype=q.dtype, device=q.device)
+    y = out.view(B, H, dv)
+    with torch.cuda.device(q.device):
+        code = _capi.lib().based_linattn_decode(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), kv_state.data_ptr(), k_state.data_ptr(),
+            B, H, d, dv, _capi.strides(*q.stride()[:2]), _capi.strides(*k.stride()[:2]),
+            _capi.strides(*v.stride()[:2]), _capi.strides(*y.stride()[:2]),
+            _dt(q.dtype), _dt(kv_state.dtype), float(eps), _stream())
+    _capi.check(code, "based_linattn_decode")
+    return out
+
+
+def swa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_left: int,
+                softmax_scale: Optional[float] = None, *, impl: str = "auto",
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal sliding-window softmax attention; q, k, v ``[B, L, H, hd]`` (views into a packed
+    qkv tensor are fine).  Query i sees keys ``[i - window_left, i]`` (slide_attention.py:97)."""
+    _need_cuda(q, k, v)
+    B, L, H, hd = q.shape
+    if k.shape != q.shape or v.shape != q.shape:
+        raise ValueError("q, k, v shapes disagree")
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _inner_contig(t, n)
+    if out is None:
+        out = torch.empty(B, L, H, hd, dtype=q.dtype, device=q.device)
+    scale = hd ** -0.5 if softmax_scale is None else float(softmax_scale)
+    with torch.cuda.device(q.device):
+        code = _capi.lib().based_swa_prefill(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, L, H, hd,
+            _capi.strides(*q.stride()[:3]), _capi.strides(*k.stride()[:3]),
+            _capi.strides(*v.stride()[:3]), _capi.strides(*out.stride()[:3]),
+            int(window_left), scale, _dt(q.dtype), _IMPLS[impl], _stream())
+    _capi.check(code, "based_swa_prefill")
+    return out
+
+
+def swa_decode(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, kv_cache: torch.Tensor,
+               cache_seqlens, window_left: int, softmax_scale: Optional[float] = None, *,
+               rotary_cos: Optional[torch.Tensor] = None, rotary_sin: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One decode step: optional RoPE at the new position, append to ``kv_cache
+    [B, maxL, 2, H, hd]`` IN PLACE, attend over the window (slide_attention.py:414-427).
+    q, k_new, v_new ``[B, 1, H, hd]``; ``cache_seqlens`` an int or an int32 ``[B]`` CUDA tensor."""
+    _need_cuda(q, k_new, v_new, kv_cache)
+    B, one, H, hd = q.shape
+    assert one == 1
+    if not kv_cache.is_contiguous() or kv_cache.shape[0] < B or kv_cache.shape[2:] != (2, H, hd):
+        raise ValueError("kv_cache must be contiguous [B, maxL, 2, H, hd]")
+    if kv_cache.dtype != q.dtype:
+        raise TypeError("kv_cache and q must share a dtype")
+    q3, k3, v3 = q[:, 0], k_new[:, 0], v_new[:, 0]
+    for t, n in ((q3, "q"), (k3, "k_new"), (v3, "v_new")):
+        _inner_contig(t, n)
+    if out is None:
+        out = torch.empty(B, 1, H, hd, dtype=q.dtype, device=q.device)
+    o3 = out[:, 0]
+    if torch.is_tensor(cache_seqlens):
+        if cache_seqlens.dtype != torch.int32 or not cache_seqlens.is_cuda or not cache_seqlens.is_contiguous():
+            raise TypeError("cache_seqlens must be a contiguous int32 CUDA tensor")
+        import ctypes
+        lens_ptr = ctypes.cast(cache_seqlens.data_ptr(), ctypes.POINTER(ctypes.c_int32))
+        lens_scalar = 0
+    else:
+        lens_ptr, lens_scalar = None, int(cache_seqlens)
+    rdim = 0
+    if rotary_cos is not None:
+        if rotary_cos.dtype != q.dtype or rotary_sin.dtype != q.dtype:
+            raise TypeError("rotary tables must be in the q dtype")
+        if not (rotary_cos.is_contiguous() and rotary_sin.is_contiguous()):
+            raise ValueError("rotary tables must be contiguous")
+        rdim = 2 * rotary_cos.shape[-1]
+    scale = hd ** -0.5 if softmax_scale is None else float(softmax_scale)
+    with torch.cuda.device(q.device):
+        code = _capi.lib().based_swa_decode(
+            q3.data_ptr(), k3.data_ptr(), v3.data_ptr(), o3.data_ptr(), kv_cache.data_ptr(), lens_ptr, lens_scalar,
+            rotary_cos.data_ptr() if rotary_cos is not None else None,
+            rotary_sin.data_ptr() if rotary_sin is not None else None, rdim,
+            B, H, hd, kv_cache.shape[1], _capi.strides(*q3.stride()[:2]), _capi.strides(*k3.stride()[:2]),
+            _capi.strides(*v3.stride()[:2]), _capi.strides(*o3.stride()[:2]),
+            int(window_left), scale, _dt(q.dtype), _stream())
+    _capi.check(code, "based_swa_decode")
+    return out

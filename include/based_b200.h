@@ -1,0 +1,142 @@
+/*
+ * based_b200 — C ABI of the B200 (sm_100a) kernels for the Based hot path:
+ * Taylor-feature-map linear attention (prefill + recurrent decode step) and
+ * sliding-window softmax attention (prefill + decode step).
+ *
+ * Conventions shared by every entry point
+ * ---------------------------------------
+ *  - All tensor arguments are DEVICE pointers owned by the caller.  The library
+ *    never allocates, frees or keeps device memory between calls.
+ *  - Strides are in ELEMENTS; the innermost (feature / head_dim) stride of every
+ *    tensor must be 1, as the reference's own CUDA op requires
+ *    (train/csrc/causal_dot_prod/causal_attention_cuda.cu:774-777).
+ *  - `stream` is a cudaStream_t passed as void*; launches are asynchronous on it,
+ *    so the calls can be captured in a CUDA graph the way
+ *    based/generation.py:689-739 captures a decode step.
+ *  - The current CUDA device must be the one that owns the pointers.
+ *  - Return value: 0 = ok; negative = argument rejected on the host before any
+ *    launch (BASED_ERR_*); positive = a cudaError_t from the launch.  No entry
+ *    point throws, aborts or traps.
+ */
+#ifndef BASED_B200_H
+#define BASED_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BASED_OK 0
+#define BASED_ERR_NULL (-1)      /* a required pointer is NULL */
+#define BASED_ERR_SHAPE (-2)     /* unsupported size (see each entry point) */
+#define BASED_ERR_DTYPE (-3)     /* unknown dtype code / unsupported combination */
+#define BASED_ERR_ALIGN (-4)     /* pointer or stride not aligned as required */
+#define BASED_ERR_IMPL (-5)      /* requested implementation cannot run these arguments */
+#define BASED_ERR_TOO_LARGE (-6) /* size exceeds a fixed capacity */
+
+/* dtype codes */
+#define BASED_F32 0
+#define BASED_BF16 1
+
+/* implementation selectors */
+#define BASED_IMPL_AUTO 0
+#define BASED_IMPL_SIMT 1    /* CUDA-core kernel, fp32 arithmetic throughout */
+#define BASED_IMPL_TCGEN05 2 /* tcgen05 tensor-core kernel (bf16 operands, fp32 accumulation) */
+
+/* Width of the expanded feature vector for feature_dim 16: 1 + 16 + 256. */
+#define BASED_EXPANDED_DIM 273
+
+int based_b200_version(void);
+const char* based_error_string(int code);
+
+/*
+ * Causal linear attention with the 2nd-order Taylor feature map, whole sequence.
+ *
+ * Replaces the body of LinearAttention.parallel_forward
+ * (based/models/mixers/linear_attention.py:169-183: feature map, tril(phi(q)phi(k)^T) v,
+ * normaliser) and the state hand-off (:220-222), i.e. the job the reference gives to
+ * causal_dot_product(q, k, v) (train/csrc/causal_dot_prod/causal_attention_cuda.cu:1273-1285)
+ * plus the torch ops around it.
+ *
+ *   q, k      [B, H, L, 16]   raw (un-expanded) queries / keys
+ *   v         [B, H, L, dv]
+ *   y         [B, H, L, dv]   normalised output, before the 'b h l d -> b l (h d)' rearrange
+ *   kv_state  [B, H, 1, dv, 273] contiguous, or NULL   (final sum_t phi(k_t) v_t^T, feature index fastest)
+ *   k_state   [B, H, 1, 1, 273]  contiguous, or NULL   (final sum_t phi(k_t))
+ *   *_strides (batch, head, seq) element strides of q, k, v, y
+ *   io_dtype  dtype of q, k, v, y;  state_dtype dtype of kv_state / k_state
+ *   d must be 16; dv a multiple of 16 in [16, 128].
+ *   impl: AUTO picks TCGEN05 for bf16 I/O and SIMT for fp32 I/O.
+ */
+int based_linattn_prefill(const void* q, const void* k, const void* v, void* y,
+                          void* kv_state, void* k_state,
+                          int B, int H, int L, int d, int dv,
+                          const int64_t q_strides[3], const int64_t k_strides[3],
+                          const int64_t v_strides[3], const int64_t y_strides[3],
+                          int io_dtype, int state_dtype, float eps, int impl, void* stream);
+
+/*
+ * One recurrent decode step; updates kv_state and k_state IN PLACE.
+ *
+ * Replaces TaylorExp.forward on q and k (linear_attention.py:139) followed by
+ * LinearAttention.recurrent_forward (:230-251) up to, not including, out_proj:
+ *   kv_state += phi(k) v^T ; k_state += phi(k) ;
+ *   y = (phi(q) . kv_state) / (phi(q) . k_state + eps).
+ *
+ *   q, k      [B, H, 16]  raw; v, y [B, H, dv]; *_strides = (batch, head) element strides
+ *   kv_state  [B, H, 1, dv, 273], k_state [B, H, 1, 1, 273], contiguous, 16-byte aligned
+ *   dv a multiple of 8 (fp32 state) / 16 (bf16 state), at most 128.
+ */
+int based_linattn_decode(const void* q, const void* k, const void* v, void* y,
+                         void* kv_state, void* k_state,
+                         int B, int H, int d, int dv,
+                         const int64_t q_strides[2], const int64_t k_strides[2],
+                         const int64_t v_strides[2], const int64_t y_strides[2],
+                         int io_dtype, int state_dtype, float eps, void* stream);
+
+/*
+ * Causal sliding-window softmax attention over a whole sequence.
+ *
+ * Replaces flash_attn_qkvpacked_func / flash_attn_kvpacked_func as called with
+ * causal=True, window_size=(window_left, 0) at
+ * based/models/mixers/slide_attention.py:100-106 and :206-213: query i attends keys
+ * [i - window_left, i].
+ *
+ *   q, k, v, o  [B, L, H, hd]; *_strides = (batch, seq, head) element strides
+ *               (q, k, v may point into one packed [B, L, 3, H, hd] tensor)
+ *   hd a multiple of 16 in [16, 128]; window_left >= 0.
+ *   io_dtype BASED_BF16 or BASED_F32 (fp32 runs the SIMT kernel only).
+ */
+int based_swa_prefill(const void* q, const void* k, const void* v, void* o,
+                      int B, int L, int H, int hd,
+                      const int64_t q_strides[3], const int64_t k_strides[3],
+                      const int64_t v_strides[3], const int64_t o_strides[3],
+                      int window_left, float softmax_scale, int io_dtype, int impl, void* stream);
+
+/*
+ * One sliding-window decode step against the full-length KV cache.
+ *
+ * Replaces flash_attn_with_kvcache as called at slide_attention.py:414-427 and
+ * :471-481: optionally rotate q and k_new at the new position (non-interleaved
+ * RoPE), append k_new / v_new to the cache at that position, attend over cache
+ * positions [pos - window_left, pos].
+ *
+ *   q, k_new, v_new, o  [B, H, hd]; *_strides = (batch, head)
+ *   kv_cache            [B, max_seqlen, 2, H, hd] contiguous (slide_attention.py:374-377)
+ *   cache_seqlens       device int32 [B] (tokens already cached = position of the new
+ *                       token), or NULL to use cache_seqlen_scalar for every sample
+ *   rotary_cos/sin      [>= max position + 1, rotary_dim / 2] in io_dtype, or NULL
+ */
+int based_swa_decode(const void* q, const void* k_new, const void* v_new, void* o,
+                     void* kv_cache, const int32_t* cache_seqlens, int cache_seqlen_scalar,
+                     const void* rotary_cos, const void* rotary_sin, int rotary_dim,
+                     int B, int H, int hd, int max_seqlen,
+                     const int64_t q_strides[2], const int64_t k_strides[2],
+                     const int64_t v_strides[2], const int64_t o_strides[2],
+                     int window_left, float softmax_scale, int io_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BASED_B200_H */

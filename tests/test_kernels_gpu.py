@@ -1,0 +1,205 @@
+"""Parity of the CUDA kernels (called through the C ABI) with the CPU oracle and with the
+golden vectors the reference produced.  Tolerances: relative error (max |a-b| / max |b|)
+1e-4 for fp32 I/O and 2e-2 for bf16 I/O, against an fp64/fp32 oracle on the same inputs."""
+import pytest
+import torch
+
+from conftest import load_golden, rel_err
+from oracle import based_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from based_b200 import ops as _ops
+    return _ops
+
+
+def _qkv(B, H, L, dv, dtype, seed=0, qscale=0.5):
+    g = torch.Generator().manual_seed(seed)
+    q = (torch.randn(B, H, L, 16, generator=g) * qscale).to(dtype)
+    k = (torch.randn(B, H, L, 16, generator=g) * qscale).to(dtype)
+    v = torch.randn(B, H, L, dv, generator=g).to(dtype)
+    return q, k, v
+
+
+# ------------------------------------------------------------------ linear attention prefill
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("L,dv", [(1, 64), (15, 64), (16, 64), (17, 64), (77, 64), (128, 64), (129, 64), (300, 112),
+                                  (1024, 64), (130, 128), (64, 16)])
+def test_linattn_prefill_vs_oracle(ops, impl, dtype, L, dv):
+    if impl == "tcgen05" and dtype == torch.float32:
+        pytest.skip("the tensor-core kernel takes bf16 I/O only")
+    B, H = 2, 3
+    q, k, v = _qkv(B, H, L, dv, dtype, seed=L + dv)
+    y_ref, kv_ref, ks_ref = O.linattn_chunked(q.double(), k.double(), v.double(), chunk=128)
+    y, kv, ks = ops.linattn_prefill(q.cuda(), k.cuda(), v.cuda(), impl=impl, state_dtype=torch.float32)
+    torch.cuda.synchronize()
+    tol = TOL[dtype]
+    assert y.shape == (B, H, L, dv) and kv.shape == (B, H, 1, dv, 273) and ks.shape == (B, H, 1, 1, 273)
+    assert rel_err(y.cpu(), y_ref) < tol
+    assert rel_err(kv.cpu(), kv_ref) < tol
+    assert rel_err(ks.cpu(), ks_ref) < tol
+
+
+def test_linattn_prefill_golden_fp32(ops):
+    """Golden vectors the reference itself produced (quadratic branch, fp64 run)."""
+    g = load_golden("linattn_qkv_f64.npz")
+    L = g["y_prefill"].shape[1]
+    B, H = g["q"].shape[:2]
+    q, k, v = (g[n][:, :, :L].float().cuda() for n in ("q", "k", "v"))
+    y, kv, ks = ops.linattn_prefill(q, k, v)
+    y = y.permute(0, 2, 1, 3).reshape(B, L, -1)
+    assert rel_err(y.cpu(), g["y_prefill"]) < 1e-4
+    assert rel_err(kv.cpu(), g["kv_state_prefill"]) < 1e-4
+    assert rel_err(ks.cpu(), g["k_state_prefill"]) < 1e-4
+
+
+def test_linattn_prefill_strided_views_and_no_state(ops):
+    """q/k/v as the transposed views LinearAttention.forward makes (linear_attention.py:127-129)."""
+    B, L, H, dv = 2, 50, 4, 64
+    torch.manual_seed(5)
+    qf, kf, vf = torch.randn(B, L, H * 16) / 2, torch.randn(B, L, H * 16) / 2, torch.randn(B, L, H * dv)
+    q = qf.cuda().view(B, L, H, 16).transpose(1, 2)
+    k = kf.cuda().view(B, L, H, 16).transpose(1, 2)
+    v = vf.cuda().view(B, L, H, dv).transpose(1, 2)
+    y, kv, ks = ops.linattn_prefill(q, k, v, return_state=False)
+    assert kv is None and ks is None
+    y_ref, _, _ = O.linattn_parallel(q.cpu().double(), k.cpu().double(), v.cpu().double())
+    assert rel_err(y.cpu(), y_ref) < 1e-4
+    assert y.permute(0, 2, 1, 3).is_contiguous()  # the 'b h l d -> b l (h d)' rearrange is free
+
+
+def test_linattn_prefill_empty_sequence(ops):
+    q = torch.zeros(1, 2, 0, 16, device="cuda")
+    v = torch.zeros(1, 2, 0, 64, device="cuda")
+    y, kv, ks = ops.linattn_prefill(q, q, v)
+    assert y.shape == (1, 2, 0, 64) and kv.abs().max() == 0 and ks.abs().max() == 0
+
+
+# ------------------------------------------------------------------ linear attention decode
+@pytest.mark.parametrize("io,st", [(torch.bfloat16, torch.float32), (torch.float32, torch.float32),
+                                   (torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("dv", [64, 112, 16])
+def test_linattn_decode_vs_oracle(ops, io, st, dv):
+    B, H, steps = 3, 5, 4
+    g = torch.Generator().manual_seed(dv)
+    kv0 = (0.02 * torch.randn(B, H, 1, dv, 273, generator=g)).to(st)
+    ks0 = (1.0 + 0.02 * torch.randn(B, H, 1, 1, 273, generator=g)).to(st)
+    kv_ref, ks_ref = kv0.double(), ks0.double()
+    kv, ks = kv0.cuda(), ks0.cuda()
+    tol = 2e-2 if (io == torch.bfloat16 or st == torch.bfloat16) else 1e-4
+    for s in range(steps):
+        q = (torch.randn(B, H, 1, 16, generator=g) / 2).to(io)
+        k = (torch.randn(B, H, 1, 16, generator=g) / 2).to(io)
+        v = torch.randn(B, H, 1, dv, generator=g).to(io)
+        y_ref = O.linattn_recurrent_step(kv_ref, ks_ref, q.double(), k.double(), v.double())
+        y = ops.linattn_decode(q.cuda(), k.cuda(), v.cuda(), kv, ks)
+        assert y.shape == (B, 1, H * dv) and y.dtype == io
+        y_ref = y_ref.transpose(1, 2).reshape(B, 1, H * dv)
+        assert rel_err(y.cpu(), y_ref) < tol, f"step {s}"
+        assert rel_err(kv.cpu(), kv_ref) < tol and rel_err(ks.cpu(), ks_ref) < tol
+        if st == torch.bfloat16:
+            # the oracle follows the state as stored (bf16), like the reference does
+            kv_ref, ks_ref = kv.cpu().double(), ks.cpu().double()
+
+
+def test_linattn_decode_golden(ops):
+    """Decode steps the reference itself ran (recurrent_forward), from its prefill state."""
+    g = load_golden("linattn_qkv_f32_dv112.npz")
+    L = g["y_prefill"].shape[1]
+    B, H, Ltot, _ = g["q"].shape
+    kv, ks = g["kv_state_prefill"].cuda().contiguous(), g["k_state_prefill"].cuda().contiguous()
+    for s in range(Ltot - L):
+        sl = slice(L + s, L + s + 1)
+        y = ops.linattn_decode(g["q"][:, :, sl].cuda(), g["k"][:, :, sl].cuda(), g["v"][:, :, sl].cuda(), kv, ks)
+        assert rel_err(y.cpu(), g["y_decode"][s]) < 1e-4
+    assert rel_err(kv.cpu(), g["kv_state_final"]) < 1e-4
+    assert rel_err(ks.cpu(), g["k_state_final"]) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prefill_then_decode_equals_longer_prefill(ops, dtype):
+    """The reference's own pin (based/tests/test_generation.py:169-173): recurrent == parallel."""
+    B, H, L, N, dv = 2, 4, 96, 8, 64
+    q, k, v = _qkv(B, H, L + N, dv, dtype, seed=11)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    y_full, kv_full, ks_full = ops.linattn_prefill(q, k, v, state_dtype=torch.float32)
+    _, kv, ks = ops.linattn_prefill(q[:, :, :L], k[:, :, :L], v[:, :, :L], state_dtype=torch.float32)
+    tol = TOL[dtype]
+    for s in range(N):
+        sl = slice(L + s, L + s + 1)
+        y = ops.linattn_decode(q[:, :, sl], k[:, :, sl], v[:, :, sl], kv, ks).view(B, H, dv)
+        assert rel_err(y.float().cpu(), y_full[:, :, L + s].float().cpu()) < tol
+    assert rel_err(kv.cpu(), kv_full.cpu()) < tol and rel_err(ks.cpu(), ks_full.cpu()) < tol
+
+
+# ------------------------------------------------------------------ sliding-window attention
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("L,hd,w", [(1, 64, 64), (5, 64, 64), (64, 64, 64), (65, 64, 64), (130, 64, 64),
+                                    (300, 112, 64), (257, 64, 128), (200, 128, 0), (1000, 64, 64)])
+def test_swa_prefill_vs_oracle(ops, impl, dtype, L, hd, w):
+    if impl == "tcgen05" and dtype == torch.float32:
+        pytest.skip("the tensor-core kernel takes bf16 I/O only")
+    B, H = 2, 3
+    g = torch.Generator().manual_seed(L + hd + w)
+    qkv = torch.randn(B, L, 3, H, hd, generator=g).to(dtype)
+    ref = O.swa_prefill(qkv[:, :, 0].double(), qkv[:, :, 1].double(), qkv[:, :, 2].double(), w)
+    qkv_d = qkv.cuda()
+    out = ops.swa_prefill(qkv_d[:, :, 0], qkv_d[:, :, 1], qkv_d[:, :, 2], w, impl=impl)
+    assert out.shape == (B, L, H, hd) and out.dtype == dtype
+    assert rel_err(out.cpu(), ref) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rotary", [False, True])
+@pytest.mark.parametrize("hd", [64, 112])
+def test_swa_decode_vs_oracle(ops, dtype, rotary, hd):
+    B, H, maxL, w = 3, 4, 100, 64
+    g = torch.Generator().manual_seed(hd)
+    cache = torch.randn(B, maxL, 2, H, hd, generator=g).to(dtype)
+    cache_d = cache.cuda()
+    cache_ref = cache.clone()
+    cos = sin = cos_d = sin_d = None
+    if rotary:
+        cos, sin = O.rotary_cos_sin(maxL, hd, dtype=dtype)
+        cos_d, sin_d = cos.cuda(), sin.cuda()
+    lens = torch.tensor([3, 64, 80], dtype=torch.int32)
+    for step in range(5):
+        q = torch.randn(B, 1, H, hd, generator=g).to(dtype)
+        kn = torch.randn(B, 1, H, hd, generator=g).to(dtype)
+        vn = torch.randn(B, 1, H, hd, generator=g).to(dtype)
+        ref = O.swa_decode_step(q, kn, vn, cache_ref, lens, w, cos=cos, sin=sin)
+        out = ops.swa_decode(q.cuda(), kn.cuda(), vn.cuda(), cache_d, lens.cuda(), w,
+                             rotary_cos=cos_d, rotary_sin=sin_d)
+        assert rel_err(out.cpu(), ref) < TOL[dtype]
+        for b in range(B):  # the appended rows
+            p = int(lens[b])
+            assert rel_err(cache_d[b, p].cpu(), cache_ref[b, p]) < TOL[dtype]
+        lens = lens + 1
+    # scalar cache_seqlens path
+    q = torch.randn(B, 1, H, hd, generator=g).to(dtype)
+    kn, vn = torch.randn(B, 1, H, hd, generator=g).to(dtype), torch.randn(B, 1, H, hd, generator=g).to(dtype)
+    ref = O.swa_decode_step(q, kn, vn, cache_ref, 90, w, cos=cos, sin=sin)
+    out = ops.swa_decode(q.cuda(), kn.cuda(), vn.cuda(), cache_d, 90, w, rotary_cos=cos_d, rotary_sin=sin_d)
+    assert rel_err(out.cpu(), ref) < TOL[dtype]
+
+
+def test_swa_decode_equals_prefill(ops):
+    """Self-consistency the reference's 'sliding' generation test encodes
+    (based/tests/test_generation.py:69-80, :169-173): decode over the cache == prefill."""
+    B, H, L, N, hd, w = 2, 4, 90, 6, 64, 64
+    torch.manual_seed(2)
+    qkv = torch.randn(B, L + N, 3, H, hd).bfloat16().cuda()
+    full = ops.swa_prefill(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], w)
+    cache = torch.zeros(B, L + N, 2, H, hd, dtype=torch.bfloat16, device="cuda")
+    cache[:, :L] = qkv[:, :L, 1:]
+    for s in range(N):
+        t = L + s
+        out = ops.swa_decode(qkv[:, t:t + 1, 0], qkv[:, t:t + 1, 1], qkv[:, t:t + 1, 2], cache, t, w)
+        assert rel_err(out[:, 0].float().cpu(), full[:, t].float().cpu()) < 2e-2
