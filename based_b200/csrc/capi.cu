@@ -8,7 +8,8 @@ namespace {
 
 bool dtype_ok(int dt) { return dt == BASED_F32 || dt == BASED_BF16; }
 size_t dtype_size(int dt) { return dt == BASED_F32 ? 4 : 2; }
-Strides3 s3(const int64_t* s) { return Strides3{s[0], s[1], s[2]}; }
+Strides3 s3(const int64_t* s) { return Strides3{s[0], s[1], s[2]}; }       // given as (batch, head, seq)
+Strides3 s3_blh(const int64_t* s) { return Strides3{s[0], s[2], s[1]}; }   // given as (batch, seq, head)
 Strides2 s2(const int64_t* s) { return Strides2{s[0], s[1]}; }
 
 }  // namespace
@@ -101,14 +102,14 @@ int based_swa_prefill(const void* q, const void* k, const void* v, void* o, int 
   if (autosel) impl = (io_dtype == BASED_BF16) ? BASED_IMPL_TCGEN05 : BASED_IMPL_SIMT;
   if (impl == BASED_IMPL_TCGEN05) {
     if (io_dtype != BASED_BF16) return BASED_ERR_IMPL;
-    const int rc = launch_swa_prefill_tc(q, k, v, o, B, L, H, hd, s3(q_strides), s3(k_strides), s3(v_strides),
-                                         s3(o_strides), window_left, softmax_scale, st);
+    const int rc = launch_swa_prefill_tc(q, k, v, o, B, L, H, hd, s3_blh(q_strides), s3_blh(k_strides), s3_blh(v_strides),
+                                         s3_blh(o_strides), window_left, softmax_scale, st);
     if (!(autosel && rc == BASED_ERR_IMPL)) return rc;
     impl = BASED_IMPL_SIMT;
   }
   if (impl != BASED_IMPL_SIMT) return BASED_ERR_IMPL;
-  return launch_swa_prefill_simt(q, k, v, o, B, L, H, hd, s3(q_strides), s3(k_strides), s3(v_strides),
-                                 s3(o_strides), window_left, softmax_scale, io_dtype, st);
+  return launch_swa_prefill_simt(q, k, v, o, B, L, H, hd, s3_blh(q_strides), s3_blh(k_strides), s3_blh(v_strides),
+                                 s3_blh(o_strides), window_left, softmax_scale, io_dtype, st);
 }
 
 int based_swa_decode(const void* q, const void* k_new, const void* v_new, void* o, void* kv_cache,

@@ -72,6 +72,11 @@ def linattn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: f
             k_state = torch.empty(B, H, 1, 1, EXPANDED_DIM, dtype=sdt, device=q.device)
         elif not (kv_state.is_contiguous() and k_state.is_contiguous()):
             raise ValueError("kv_state / k_state must be contiguous")
+    if L == 0 or B == 0 or H == 0:  # empty tensors have no device pointer to pass
+        if return_state:
+            kv_state.zero_()
+            k_state.zero_()
+        return out, (kv_state if return_state else None), (k_state if return_state else None)
     with torch.cuda.device(q.device):
         code = _capi.lib().based_linattn_prefill(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
@@ -133,6 +138,8 @@ def swa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_left: 
     if out is None:
         out = torch.empty(B, L, H, hd, dtype=q.dtype, device=q.device)
     scale = hd ** -0.5 if softmax_scale is None else float(softmax_scale)
+    if out.numel() == 0:
+        return out
     with torch.cuda.device(q.device):
         code = _capi.lib().based_swa_prefill(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, L, H, hd,

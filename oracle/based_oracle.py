@@ -10,9 +10,10 @@ The sliding-window functions restate the semantics of the reference's call
 sites into flash-attn (pinned ``flash-attn==2.5.2`` in the reference's root
 ``setup.py:34``; its source is an un-vendored submodule and is not part of the
 reference tree).  The reference has no CPU implementation of that mixer, so
-those functions are pinned only through fixtures produced by the installed
-flash-attn on a GPU (``tests/golden/make_swa_golden_gpu.py``) when such
-fixtures are present; otherwise parity for them is unpinned.
+those functions are pinned through ``tests/golden/swa_flash.npz``: outputs of
+the flash-attn build installed in the image (2.8.3) called on a B200 with the
+reference's own arguments by ``tests/golden/make_swa_golden_gpu.py`` (windowed
+prefill at head_dim 64 / 112 and window 64 / 128; rotary + cache-append decode).
 
 All functions run on CPU tensors in the dtype they are given (float64 and
 float32 are the intended ones) and never touch CUDA.

@@ -98,3 +98,29 @@ def test_linattn_config1_samples():
     assert rel_err(out[:, ::37, ::29], g["y_train"]) < 1e-4
     assert rel_err(kv[:, ::5, :, ::7, ::11], g["kv_state"]) < 1e-4
     assert rel_err(ks[..., ::3], g["k_state"]) < 1e-4
+
+
+# ---------------------------------------------------------------- sliding window vs flash-attn
+def test_swa_prefill_matches_flash_attn():
+    """The oracle's sliding-window restatement against outputs of flash-attn itself, called the
+    way the reference calls it (tests/golden/make_swa_golden_gpu.py); bf16 outputs."""
+    g = load_golden("swa_flash.npz")
+    for name in ("p64", "p112", "p64w128"):
+        qkv, w = g[f"{name}_qkv"], int(g[f"{name}_w"])
+        out = O.swa_prefill(qkv[:, :, 0].double(), qkv[:, :, 1].double(), qkv[:, :, 2].double(), w)
+        assert rel_err(out, g[f"{name}_out"]) < 1e-2, name
+
+
+def test_swa_decode_matches_flash_attn():
+    g = load_golden("swa_flash.npz")
+    cache = g["d_cache_in"].bfloat16()
+    B, maxL, _, H, hd = cache.shape
+    cos, sin = O.rotary_cos_sin(maxL, hd, dtype=torch.bfloat16)
+    lens = g["d_lens0"].to(torch.int32)
+    w = int(g["d_w"])
+    for s in range(g["d_q"].shape[0]):
+        out = O.swa_decode_step(g["d_q"][s].bfloat16(), g["d_k"][s].bfloat16(), g["d_v"][s].bfloat16(),
+                                cache, lens, w, cos=cos, sin=sin)
+        assert rel_err(out.float(), g["d_out"][s]) < 1e-2, s
+        lens = lens + 1
+    assert rel_err(cache.float(), g["d_cache_out"]) < 1e-2
