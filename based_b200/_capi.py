@@ -21,6 +21,7 @@ _I64P = POINTER(c_int64)
 SIGNATURES = {
     "based_b200_version": (c_int, []),
     "based_error_string": (c_char_p, [c_int]),
+    "based_read_status": (c_int, [POINTER(ctypes.c_uint), c_int]),
     "based_linattn_prefill": (c_int, [c_void_p] * 6 + [c_int] * 5 + [_I64P] * 4 + [c_int, c_int, c_float, c_int, c_void_p]),
     "based_linattn_decode": (c_int, [c_void_p] * 6 + [c_int] * 4 + [_I64P] * 4 + [c_int, c_int, c_float, c_void_p]),
     "based_swa_prefill": (c_int, [c_void_p] * 4 + [c_int] * 4 + [_I64P] * 4 + [c_int, c_float, c_int, c_int, c_void_p]),
@@ -50,6 +51,13 @@ def lib():
             fn.argtypes = args
         _lib = handle
     return _lib
+
+
+def read_status(reset: bool = True) -> int:
+    """The tensor-core kernels' status word (0 = no bounded wait has expired); synchronises."""
+    out = ctypes.c_uint(0)
+    check(lib().based_read_status(ctypes.byref(out), 1 if reset else 0), "based_read_status")
+    return out.value
 
 
 def strides(*vals):

@@ -33,6 +33,8 @@ const char* based_error_string(int code) {
   return "unknown error";
 }
 
+int based_read_status(unsigned int* out, int reset) { return read_tc_status(out, reset); }
+
 int based_linattn_prefill(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
                           int B, int H, int L, int d, int dv, const int64_t q_strides[3],
                           const int64_t k_strides[3], const int64_t v_strides[3], const int64_t y_strides[3],

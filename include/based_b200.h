@@ -51,6 +51,16 @@ int based_b200_version(void);
 const char* based_error_string(int code);
 
 /*
+ * Device-side status word of the tensor-core kernels.  Every wait inside those kernels is
+ * bounded (about a second); a wait that expires ORs a code into this word and lets the kernel
+ * run to its end with meaningless results instead of hanging.  This call synchronises with
+ * the device (cudaMemcpyFromSymbol), stores the word in *out and clears it when reset != 0.
+ * 0 means no wait has expired since the last reset.  No counterpart in the reference, whose
+ * kernels have no in-kernel waits.
+ */
+int based_read_status(unsigned int* out, int reset);
+
+/*
  * Causal linear attention with the 2nd-order Taylor feature map, whole sequence.
  *
  * Replaces the body of LinearAttention.parallel_forward

@@ -36,9 +36,16 @@ def test_linattn_prefill_vs_oracle(ops, impl, dtype, L, dv):
         pytest.skip("the tensor-core kernel takes bf16 I/O only")
     B, H = 2, 3
     q, k, v = _qkv(B, H, L, dv, dtype, seed=L + dv)
+    if impl == "tcgen05" and dv > 112:
+        from based_b200._capi import BasedLibraryError
+        with pytest.raises(BasedLibraryError):  # V' = dv + 16 columns must fit 128 TMEM lanes
+            ops.linattn_prefill(q.cuda(), k.cuda(), v.cuda(), impl=impl)
+        return
     y_ref, kv_ref, ks_ref = O.linattn_chunked(q.double(), k.double(), v.double(), chunk=128)
     y, kv, ks = ops.linattn_prefill(q.cuda(), k.cuda(), v.cuda(), impl=impl, state_dtype=torch.float32)
     torch.cuda.synchronize()
+    from based_b200 import _capi
+    assert _capi.read_status() == 0
     tol = TOL[dtype]
     assert y.shape == (B, H, L, dv) and kv.shape == (B, H, 1, dv, 273) and ks.shape == (B, H, 1, 1, 273)
     assert rel_err(y.cpu(), y_ref) < tol
