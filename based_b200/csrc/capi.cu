@@ -114,6 +114,18 @@ int based_swa_prefill(const void* q, const void* k, const void* v, void* o, int 
                                  s3_blh(o_strides), window_left, softmax_scale, io_dtype, st);
 }
 
+int based_rotary_apply(void* x, int B, int L, int H, int hd, const int64_t x_strides[3], const void* rotary_cos,
+                       const void* rotary_sin, int rotary_dim, const int32_t* seqlen_offsets, int seqlen_offset_scalar,
+                       int io_dtype, void* stream) {
+  if (!x || !x_strides || !rotary_cos || !rotary_sin) return BASED_ERR_NULL;
+  if (!dtype_ok(io_dtype)) return BASED_ERR_DTYPE;
+  if (B < 0 || L < 0 || H < 0 || hd <= 0 || rotary_dim <= 0 || rotary_dim > hd || rotary_dim % 2 != 0 ||
+      seqlen_offset_scalar < 0)
+    return BASED_ERR_SHAPE;
+  return launch_rotary(x, B, L, H, s3_blh(x_strides), rotary_cos, rotary_sin, rotary_dim, seqlen_offsets,
+                       seqlen_offset_scalar, io_dtype, static_cast<cudaStream_t>(stream));
+}
+
 int based_swa_decode(const void* q, const void* k_new, const void* v_new, void* o, void* kv_cache,
                      const int32_t* cache_seqlens, int cache_seqlen_scalar, const void* rotary_cos,
                      const void* rotary_sin, int rotary_dim, int B, int H, int hd, int max_seqlen,

@@ -74,6 +74,9 @@ int launch_swa_prefill_tc(const void* q, const void* k, const void* v, void* o, 
                           Strides3 sq, Strides3 sk, Strides3 sv, Strides3 so, int window_left, float scale,
                           cudaStream_t stream);
 
+int launch_rotary(void* x, int B, int L, int H, Strides3 sx, const void* rcos, const void* rsin, int rotary_dim,
+                  const int32_t* offsets, int offset_scalar, int io_dtype, cudaStream_t stream);
+
 int launch_swa_decode(const void* q, const void* k_new, const void* v_new, void* o, void* kv_cache,
                       const int32_t* cache_seqlens, int cache_seqlen_scalar, const void* rotary_cos,
                       const void* rotary_sin, int rotary_dim, int B, int H, int hd, int max_seqlen,

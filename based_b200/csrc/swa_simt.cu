@@ -176,7 +176,50 @@ swa_decode_kernel(const IO* __restrict__ q, const IO* __restrict__ k_new, const 
   }
 }
 
+// In-place non-interleaved RoPE on x [B, L, H, hd]: one thread per rotated pair.
+template <typename IO>
+__global__ void rotary_kernel(IO* __restrict__ x, int L, int H, Strides3 sx, const IO* __restrict__ rcos,
+                              const IO* __restrict__ rsin, int half, const int32_t* __restrict__ offsets,
+                              int offset_scalar, long long total) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int c = (int)(idx % half);
+  long long r = idx / half;
+  const int h = (int)(r % H); r /= H;
+  const int l = (int)(r % L);
+  const int b = (int)(r / L);
+  const int pos = l + (offsets ? offsets[b] : offset_scalar);
+  IO* px = x + b * sx.b + (int64_t)l * sx.l + h * sx.h;
+  const float cs = to_float(rcos[(size_t)pos * half + c]), sn = to_float(rsin[(size_t)pos * half + c]);
+  const float x0 = to_float(px[c]), x1 = to_float(px[c + half]);
+  px[c] = from_float<IO>(x0 * cs - x1 * sn);
+  px[c + half] = from_float<IO>(x0 * sn + x1 * cs);
+}
+
 }  // namespace
+
+int launch_rotary(void* x, int B, int L, int H, Strides3 sx, const void* rcos, const void* rsin, int rotary_dim,
+                  const int32_t* offsets, int offset_scalar, int io_dtype, cudaStream_t stream) {
+  const int half = rotary_dim / 2;
+  const long long total = (long long)B * L * H * half;
+  if (total == 0) return 0;
+  const int threads = 256;
+  const long long blocks = (total + threads - 1) / threads;
+  if (blocks > 2147483647LL) return BASED_ERR_TOO_LARGE;
+  if (io_dtype == BASED_BF16) {
+    using T = __nv_bfloat16;
+    rotary_kernel<T><<<(unsigned)blocks, threads, 0, stream>>>(static_cast<T*>(x), L, H, sx, static_cast<const T*>(rcos),
+                                                              static_cast<const T*>(rsin), half, offsets,
+                                                              offset_scalar, total);
+  } else if (io_dtype == BASED_F32) {
+    rotary_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
+        static_cast<float*>(x), L, H, sx, static_cast<const float*>(rcos), static_cast<const float*>(rsin), half,
+        offsets, offset_scalar, total);
+  } else {
+    return BASED_ERR_DTYPE;
+  }
+  return (int)cudaGetLastError();
+}
 
 int launch_swa_prefill_simt(const void* q, const void* k, const void* v, void* o, int B, int L, int H, int hd,
                             Strides3 sq, Strides3 sk, Strides3 sv, Strides3 so, int window_left, float scale,

@@ -65,7 +65,7 @@ def linattn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: f
         out = torch.empty(B, L, H, dv, dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
     else:
         _inner_contig(out, "out")
-    sdt = state_dtype or (kv_state.dtype if kv_state is not None else q.dtype)
+    sdt = kv_state.dtype if kv_state is not None else (state_dtype or q.dtype)
     if return_state:
         if kv_state is None:
             kv_state = torch.empty(B, H, 1, dv, EXPANDED_DIM, dtype=sdt, device=q.device)
@@ -196,3 +196,33 @@ def swa_decode(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, kv_cac
             int(window_left), scale, _dt(q.dtype), _stream())
     _capi.check(code, "based_swa_decode")
     return out
+
+
+def rotary_apply_(x: torch.Tensor, rotary_cos: torch.Tensor, rotary_sin: torch.Tensor, seqlen_offset=0) -> torch.Tensor:
+    """In-place non-interleaved RoPE on ``x [B, L, H, hd]`` (a view into packed qkv is fine);
+    ``seqlen_offset`` an int or an int32 ``[B]`` CUDA tensor (based/ops/triton/rotary.py:68-105)."""
+    _need_cuda(x, rotary_cos, rotary_sin)
+    B, L, H, hd = x.shape
+    _inner_contig(x, "x")
+    if rotary_cos.dtype != x.dtype or rotary_sin.dtype != x.dtype:
+        raise TypeError("rotary tables must be in the dtype of x")
+    if not (rotary_cos.is_contiguous() and rotary_sin.is_contiguous()):
+        raise ValueError("rotary tables must be contiguous")
+    if x.numel() == 0:
+        return x
+    if torch.is_tensor(seqlen_offset):
+        import ctypes
+        if seqlen_offset.dtype != torch.int32 or not seqlen_offset.is_cuda:
+            raise TypeError("seqlen_offset tensor must be int32 on CUDA")
+        off_ptr, off_scalar = ctypes.cast(seqlen_offset.data_ptr(), ctypes.POINTER(ctypes.c_int32)), 0
+        max_pos = None
+    else:
+        off_ptr, off_scalar = None, int(seqlen_offset)
+        if off_scalar + L > rotary_cos.shape[0]:
+            raise ValueError("rotary tables are shorter than seqlen_offset + L")
+    with torch.cuda.device(x.device):
+        code = _capi.lib().based_rotary_apply(
+            x.data_ptr(), B, L, H, hd, _capi.strides(*x.stride()[:3]), rotary_cos.data_ptr(), rotary_sin.data_ptr(),
+            2 * rotary_cos.shape[-1], off_ptr, off_scalar, _dt(x.dtype), _stream())
+    _capi.check(code, "based_rotary_apply")
+    return x

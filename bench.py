@@ -150,11 +150,11 @@ def time_kernel(fn, iters, warmup=3):
     return e0.elapsed_time(e1) / iters  # ms
 
 
-def prefill_sweep(ops, peaks, quick):
+def prefill_sweep(ops, peaks, lengths):
     """Prefill sweep: B=8, H=16, d=16, dv=64, bf16, q/k/v ~ N(0,1)/4; linear attention and window-64 SWA."""
     out_lin, out_swa = [], []
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-    for L in ([2048] if quick else [2048, 8192, 32768]):
+    for L in lengths:
         g = torch.Generator(device="cuda").manual_seed(L)
         q = (torch.randn(8, H, L, 16, device="cuda", generator=g) / 4).bfloat16()
         k = (torch.randn(8, H, L, 16, device="cuda", generator=g) / 4).bfloat16()
@@ -200,6 +200,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the prefill / SWA sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--quick", action="store_true", help="prefill sweep at L=2048 only")
+    ap.add_argument("--sweep-L", type=int, nargs="*", default=None, help="sequence lengths of the prefill sweep")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -301,7 +302,8 @@ def main():
         if os.path.exists(traffic_file):
             line["roofline"]["traffic"] = json.load(open(traffic_file)).get("dram_bytes_per_launch")
         if world == 1 and not args.no_sweep:
-            lin, swa = prefill_sweep(ops, peaks, args.quick)
+            lengths = args.sweep_L if args.sweep_L else ([2048] if args.quick else [2048, 8192, 32768])
+            lin, swa = prefill_sweep(ops, peaks, lengths)
             line["prefill"] = lin
             line["swa"] = swa
         if world == 1 and not args.no_cpu:

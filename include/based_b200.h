@@ -125,6 +125,21 @@ int based_swa_prefill(const void* q, const void* k, const void* v, void* o,
                       int window_left, float softmax_scale, int io_dtype, int impl, void* stream);
 
 /*
+ * In-place rotary position embedding (non-interleaved: halves split at rotary_dim/2,
+ * o0 = x0 cos - x1 sin, o1 = x0 sin + x1 cos, fp32 math) on x [B, L, H, hd].
+ *
+ * Replaces the rotary kernel the reference applies to q and k of the packed qkv before
+ * prefill attention (slide_attention.py:553-556; formula based/ops/triton/rotary.py:75-105).
+ * Token l of sample b uses table row l + seqlen_offsets[b] (device int32 [B]) or
+ * l + seqlen_offset_scalar when seqlen_offsets is NULL.
+ *   x_strides = (batch, seq, head); rotary_cos/sin [rows, rotary_dim/2] in io_dtype.
+ */
+int based_rotary_apply(void* x, int B, int L, int H, int hd, const int64_t x_strides[3],
+                       const void* rotary_cos, const void* rotary_sin, int rotary_dim,
+                       const int32_t* seqlen_offsets, int seqlen_offset_scalar,
+                       int io_dtype, void* stream);
+
+/*
  * One sliding-window decode step against the full-length KV cache.
  *
  * Replaces flash_attn_with_kvcache as called at slide_attention.py:414-427 and

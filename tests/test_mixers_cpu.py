@@ -1,0 +1,66 @@
+"""Host-side behaviour of the drop-in mixers that needs no GPU: parameter names and shapes
+(checkpoint compatibility with the reference), cache shapes, argument checks."""
+import pytest
+import torch
+
+from based_b200.generation import InferenceParams
+from based_b200.mixers import LinearAttention, SlidingAttention, TaylorExp
+
+
+def test_linear_attention_parameters_match_reference_layout():
+    m = LinearAttention(d_model=1024, feature_map=TaylorExp(input_dim=16), feature_dim=16, num_heads=16,
+                        head_dim=64, layer_idx=3)
+    shapes = {k: tuple(v.shape) for k, v in m.state_dict().items()}
+    # based/models/mixers/linear_attention.py:106-109
+    assert shapes == {"proj_q.weight": (256, 1024), "proj_k.weight": (256, 1024),
+                      "proj_v.weight": (1024, 1024), "out_proj.weight": (1024, 1024)}
+    assert m.expanded_size() == 273
+    kv, ks = m.allocate_inference_cache(4, 2048, dtype=torch.float32)
+    assert kv.shape == (4, 16, 1, 64, 273) and ks.shape == (4, 16, 1, 1, 273)  # :261-266
+    assert kv.abs().max() == 0 and ks.abs().max() == 0
+
+
+def test_linear_attention_default_head_dim_and_1b_shape():
+    m = LinearAttention(d_model=1792, feature_map=TaylorExp(input_dim=16), num_heads=16)
+    assert m.head_dim == 112  # d_model // num_heads (:101)
+    kv, _ = m.allocate_inference_cache(1, 16)
+    assert kv.shape == (1, 16, 1, 112, 273)
+
+
+def test_linear_attention_rejects_unknown_implementation():
+    with pytest.raises(ValueError):
+        LinearAttention(64, feature_map=TaylorExp(16), num_heads=2, parallel_implementation="tk")
+    with pytest.raises(ValueError):
+        LinearAttention(64, feature_map=TaylorExp(16), num_heads=2, feature_dim=8)
+
+
+def test_taylor_exp_matches_golden():
+    from conftest import load_golden, rel_err
+    g = load_golden("taylor_exp.npz")
+    assert rel_err(TaylorExp(16)(g["x"]), g["phi"]) < 1e-14
+
+
+def test_mixers_have_no_cpu_path():
+    m = LinearAttention(64, feature_map=TaylorExp(16), num_heads=2, head_dim=32)
+    with pytest.raises(RuntimeError):
+        m(torch.zeros(1, 4, 64))
+
+
+def test_sliding_attention_parameters_and_cache():
+    s = SlidingAttention(1024, 16, qkv_proj_bias=False, out_proj_bias=False, rotary_emb_dim=64, window_size=128,
+                         layer_idx=2)
+    shapes = {k: tuple(v.shape) for k, v in s.state_dict().items()}
+    assert shapes == {"Wqkv.weight": (3072, 1024), "out_proj.weight": (1024, 1024)}  # slide_attention.py:365,:372
+    assert s.window == (64, 0)  # :336: the argument is halved; 64 previous keys + self
+    cache = s.allocate_inference_cache(3, 100, dtype=torch.bfloat16)
+    assert cache.shape == (3, 100, 2, 16, 64)  # :374-377
+    with pytest.raises(NotImplementedError):
+        SlidingAttention(1024, 16, num_heads_kv=4)
+
+
+def test_inference_params_mirror():
+    ip = InferenceParams(max_seqlen=10, max_batch_size=2)
+    ip.seqlen_offset = 5
+    ip.reset(20, 4)
+    assert (ip.max_seqlen, ip.max_batch_size, ip.seqlen_offset) == (20, 4, 0)
+    assert ip.key_value_memory_dict == {}
