@@ -33,7 +33,13 @@ const char* based_error_string(int code) {
   return "unknown error";
 }
 
-int based_read_status(unsigned int* out, int reset) { return read_tc_status(out, reset); }
+int based_read_status(unsigned int* out, int reset) {
+  unsigned int a = 0, b = 0;
+  int rc = read_tc_status(&a, reset);
+  if (rc == 0) rc = read_tc_status_swa(&b, reset);
+  if (out) *out = a | b;
+  return rc;
+}
 
 int based_linattn_prefill(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
                           int B, int H, int L, int d, int dv, const int64_t q_strides[3],

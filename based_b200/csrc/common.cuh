@@ -64,7 +64,8 @@ int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void*
                               int B, int H, int L, int dv, Strides3 sq, Strides3 sk, Strides3 sv, Strides3 sy,
                               int state_dtype, float eps, cudaStream_t stream);
 
-int read_tc_status(unsigned int* out, int reset);
+int read_tc_status(unsigned int* out, int reset);      // linear-attention prefill kernel
+int read_tc_status_swa(unsigned int* out, int reset);  // sliding-window prefill kernel
 
 int launch_swa_prefill_simt(const void* q, const void* k, const void* v, void* o, int B, int L, int H, int hd,
                             Strides3 sq, Strides3 sk, Strides3 sv, Strides3 so, int window_left, float scale,
