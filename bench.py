@@ -273,10 +273,8 @@ def main():
     barrier()
     ms_e2e = f0.elapsed_time(f1)
 
-    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = t.tolist()
+    from based_b200.sharding import max_over_ranks
+    ms, ms_e2e = max_over_ranks([ms, ms_e2e], dev)
 
     if rank == 0:
         launch_ms = ms / K
