@@ -13,7 +13,8 @@ LIBNAME = "libbased_b200.so"
 
 
 def library_path() -> str:
-    return os.path.join(LIBDIR, LIBNAME)
+    """Path of the shared library; the environment variable BASED_B200_LIB overrides it."""
+    return os.environ.get("BASED_B200_LIB") or os.path.join(LIBDIR, LIBNAME)
 
 
 def _sources():
@@ -31,6 +32,8 @@ def _stale(lib: str) -> bool:
 def build_library(force: bool = False, verbose: bool = False) -> str:
     """Build (if stale) and return the path of the shared library.  Needs ``nvcc`` only; no GPU."""
     lib = library_path()
+    if os.environ.get("BASED_B200_LIB"):
+        return lib  # an explicitly chosen library is used as it is
     if not force and not _stale(lib):
         return lib
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"

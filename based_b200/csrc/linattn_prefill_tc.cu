@@ -28,24 +28,39 @@ namespace based {
 
 __device__ unsigned int g_tc_status = 0;  // ORed with a code when a bounded wait expires
 
+#ifdef BASED_TC_TRACE
+// Debug build only: per-role cycle counters of CTA 0 (cycles spent in each barrier wait, total
+// cycles), read back with based_tc_trace_read().
+__device__ unsigned long long g_tc_trace[4][24];
+#endif
+
 namespace {
 
 using namespace tc;
 
 constexpr int C = 128;     // tokens per chunk
 constexpr int DR = 160;    // packed + padded feature count
-constexpr int NT = 256;    // threads per CTA
+constexpr int NT = 384;    // threads per CTA: 4 expansion warps, 4 polynomial/epilogue warps, MMA warp, 3 load warps
+constexpr int W_MMA = 8, W_LOAD = 9;
 
-// shared memory map (bytes)
-constexpr int SM_Q = 0;                    // 2 stages x 4096   K-major [128 tok x 16]
-constexpr int SM_K = 8192;                 // 2 stages x 4096
-constexpr int SM_V = 16384;                // 2 stages x 32768  MN-major [16 groups of 8 cols][128 tok][16 B]
-constexpr int SM_PHIK = SM_V + 65536;      // 40960             MN-major [20 groups of 8 feats][128 tok][16 B]
-constexpr int SM_STB = SM_PHIK + 40960;    // 40960             K-major  [20 k-units][128 rows][16 B]
-constexpr int SM_BAR = SM_STB + 40960;     // barriers, TMEM base, abort flag
-constexpr int SM_TOTAL = SM_BAR + 64;
-constexpr int STAGE_STRIDE_F = 164;        // floats per row of the final fp32 staging (conflict-free 16 B stores)
-static_assert(SM_V + C * STAGE_STRIDE_F * 4 <= SM_BAR, "final staging must fit below the barriers");
+// Shared memory map (bytes).  One stage = Q [128 tok x 16] K-major (4096) + K (4096) +
+// V' MN-major [NV/8 groups of 8 columns][128 tok][16 B].  The state-update MMA reads V'^T as an
+// M = 128 operand, i.e. 16 column groups from the stage's V' base; the groups past NV/8 are
+// whatever follows in shared memory and only feed accumulator lanes >= NV, which nobody reads.
+struct Smem {
+  int nstage, stage_bytes, phik, stb, ystage, yrow_bytes, bar, total;
+  __host__ __device__ explicit Smem(int dv) {
+    nstage = dv <= 64 ? 3 : 2;     // what fits in 227 KB
+    stage_bytes = 8192 + ((dv + 16) >> 3) * 2048;
+    phik = nstage * stage_bytes;   // 40960  MN-major [20 groups of 8 feats][128 tok][16 B]
+    stb = phik + 40960;            // 40960  K-major  [20 k-units][128 rows][16 B]
+    ystage = stb + 40960;          // output tile [128 rows][dv bf16 + 16 B pad] for the bulk stores
+    yrow_bytes = dv * 2 + 16;      // the pad makes the per-row 16-byte stores bank-conflict free
+    bar = ystage + C * yrow_bytes; // mbarriers, TMEM base, abort flag
+    total = bar + 256;
+  }
+};
+constexpr int STAGE_STRIDE_F = 164;  // floats per row of the final fp32 staging (conflict-free 16 B stores)
 
 // TMEM columns (32-bit each), 512 allocated
 constexpr uint32_t TM_ST = 0;     // state^T accumulator: lanes = V' column, 160 feature columns, fp32
@@ -54,40 +69,9 @@ constexpr uint32_t TM_O = 288;    // O accumulator, NV <= 128 columns
 constexpr uint32_t TM_PQ = 416;   // phi'(Q) bf16, 80 columns
 constexpr uint32_t TM_COLS = 512;
 
-__host__ __device__ constexpr int pair_row(int p) {
-  int a = 0;
-  while (p >= 16 - a) { p -= 16 - a; ++a; }
-  return a;
-}
-__host__ __device__ constexpr int pair_col(int p) {
-  int a = 0;
-  while (p >= 16 - a) { p -= 16 - a; ++a; }
-  return a + p;
-}
-
-// Packed feature F (0..159) of x[16].
-template <int F>
-__device__ __forceinline__ float packed_feature(const float (&x)[16]) {
-  if constexpr (F == 0) {
-    return 1.0f;
-  } else if constexpr (F <= 16) {
-    return x[F - 1] * kC1;
-  } else if constexpr (F < 153) {
-    constexpr int a = pair_row(F - 17), b = pair_col(F - 17);
-    if constexpr (a == b) return x[a] * x[a] * kC2;
-    else return x[a] * x[b] * 0.25f;
-  } else {
-    return 0.0f;
-  }
-}
-// Features 8G .. 8G+7 as four packed bf16x2 words.
-template <int G>
-__device__ __forceinline__ void packed_group(const float (&x)[16], uint32_t* out) {
-  out[0] = pack_bf16(packed_feature<8 * G + 0>(x), packed_feature<8 * G + 1>(x));
-  out[1] = pack_bf16(packed_feature<8 * G + 2>(x), packed_feature<8 * G + 3>(x));
-  out[2] = pack_bf16(packed_feature<8 * G + 4>(x), packed_feature<8 * G + 5>(x));
-  out[3] = pack_bf16(packed_feature<8 * G + 6>(x), packed_feature<8 * G + 7>(x));
-}
+// mbarrier slots (8 bytes each) from Smem::bar
+enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_P_READY, B_O_DONE, B_ST_DONE, B_PQ_READY, B_PK_READY,
+           B_STB_READY, B_O_FREE, B_COUNT };
 
 template <int G0, int G1, typename F>
 __device__ __forceinline__ void static_for(F&& f) {
@@ -97,24 +81,91 @@ __device__ __forceinline__ void static_for(F&& f) {
   }
 }
 
+// ---------------------------------------------------------------- packed feature map, bf16x2 arithmetic
+// Feature order of phi' (160 features = 80 bf16x2 words; u = x/2, c = 1/sqrt2):
+//   0        : 1            (features 1..7 are zero padding)
+//   8  + i   : u_i                                  i = 0..15      (= x_i / 2)
+//   24 + a   : c * u_a^2                            a = 0..15      (= x_a^2 / (4 sqrt2))
+//   40 + m   : u_{2m} u_{2m+1}                      m = 0..7
+//   48 + 4*blk(m,n) + 2*(a&1) + (b&1) : u_a u_b     a in pair m, b in pair n, m < n,
+//                                                   blk(m,n) = 7m - m(m-1)/2 + (n - m - 1)
+// Off-diagonal products appear once with weight 1/4 = sqrt2 * 1/(4 sqrt2), so that
+// phi'(q).phi'(k) = 1 + s + s^2/2 (s = q.k/4) exactly as for the 273-feature map.
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// pair-block number blk = 0..27 -> (m, n), m < n
+__host__ __device__ constexpr int blk_m(int blk) {
+  int m = 0;
+  while (blk >= 7 - m) { blk -= 7 - m; ++m; }
+  return m;
+}
+__host__ __device__ constexpr int blk_n(int blk) {
+  int m = 0;
+  while (blk >= 7 - m) { blk -= 7 - m; ++m; }
+  return m + 1 + blk;
+}
+constexpr uint32_t kHalf2 = 0x3F003F00u;    // (0.5, 0.5)
+constexpr uint32_t kRsqrt2_2 = 0x3F353F35u; // (0.70703125, 0.70703125): bf16(1/sqrt2)
+constexpr uint32_t kOneLo = 0x00003F80u;    // (1.0, 0)
+
+// Expands one token: X = the 16 raw bf16 values as 8 packed words.  emit(G, w0, w1, w2, w3) is
+// called for G = 0..19 in order with the four words of feature group G (features 8G .. 8G+7).
+template <typename Emit>
+__device__ __forceinline__ void expand_packed(const uint32_t (&X)[8], Emit&& emit) {
+  uint32_t U[8];
+#pragma unroll
+  for (int m = 0; m < 8; ++m) U[m] = mul_bf16x2(X[m], kHalf2);
+  emit(std::integral_constant<int, 0>{}, kOneLo, 0u, 0u, 0u);
+  emit(std::integral_constant<int, 1>{}, U[0], U[1], U[2], U[3]);
+  emit(std::integral_constant<int, 2>{}, U[4], U[5], U[6], U[7]);
+  {
+    uint32_t d[8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) d[m] = mul_bf16x2(mul_bf16x2(U[m], U[m]), kRsqrt2_2);
+    emit(std::integral_constant<int, 3>{}, d[0], d[1], d[2], d[3]);
+    emit(std::integral_constant<int, 4>{}, d[4], d[5], d[6], d[7]);
+  }
+  {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)  // (u_{4j} u_{4j+1}, u_{4j+2} u_{4j+3})
+      w[j] = mul_bf16x2(__byte_perm(U[2 * j], U[2 * j + 1], 0x5410), __byte_perm(U[2 * j], U[2 * j + 1], 0x7632));
+    emit(std::integral_constant<int, 5>{}, w[0], w[1], w[2], w[3]);
+  }
+  // cross blocks (m < n), two blocks (four words) per group
+  static_for<0, 14>([&](auto GG) {
+    constexpr int g = decltype(GG)::value;
+    constexpr int m0 = blk_m(2 * g), n0 = blk_n(2 * g), m1 = blk_m(2 * g + 1), n1 = blk_n(2 * g + 1);
+    const uint32_t w0 = mul_bf16x2(__byte_perm(U[m0], 0, 0x1010), U[n0]);
+    const uint32_t w1 = mul_bf16x2(__byte_perm(U[m0], 0, 0x3232), U[n0]);
+    const uint32_t w2 = mul_bf16x2(__byte_perm(U[m1], 0, 0x1010), U[n1]);
+    const uint32_t w3 = mul_bf16x2(__byte_perm(U[m1], 0, 0x3232), U[n1]);
+    emit(std::integral_constant<int, 6 + g>{}, w0, w1, w2, w3);
+  });
+}
+
 // Index of full feature f (0..272) in the packed vector, and whether it is an off-diagonal
 // second-order term (whose packed value is sqrt2 times the full-map value).
 __device__ __forceinline__ int packed_index(int f, bool& offdiag) {
   offdiag = false;
-  if (f < 17) return f;
+  if (f == 0) return 0;
+  if (f < 17) return 8 + (f - 1);
   const int g = f - 17, i = g >> 4, j = g & 15;
   const int a = min(i, j), b = max(i, j);
-  offdiag = a != b;
-  return 17 + a * 16 - (a * (a - 1)) / 2 + (b - a);
-}
-
-__device__ __forceinline__ void unpack8(const uint4& u, float* x) {
-  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    x[2 * i] = __uint_as_float(w[i] << 16);
-    x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
+  if (a == b) return 24 + a;
+  offdiag = true;
+  const int m = a >> 1, n = b >> 1;
+  if (m == n) return 40 + m;
+  const int blk = 7 * m - (m * (m - 1)) / 2 + (n - m - 1);
+  return 48 + 4 * blk + 2 * (a & 1) + (b & 1);
 }
 
 struct Params {
@@ -131,249 +182,414 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int qd = warp & 3;   // TMEM lane quadrant this warp can reach
-  const int hf = warp >> 2;  // which half of the column work this warp takes
-  const int t = qd * 32 + lane;  // token within the chunk == TMEM lane
+  const int qd = warp & 3;       // TMEM lane quadrant this warp can reach
+  const int t = qd * 32 + lane;  // token within the chunk == TMEM lane (compute warps)
   const int bh = blockIdx.x, b = bh / p.H, h = bh - b * p.H;
   const int dv = p.dv, NV = dv + 16, L = p.L;
+  const Smem lay(dv);
+  const int nchunks = (L + C - 1) / C;
 
-  const uint32_t bar_s = sb + SM_BAR, bar_o = sb + SM_BAR + 8, bar_st = sb + SM_BAR + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 24);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_BAR + 28);
-
-  const __nv_bfloat16* qb = p.q + b * p.sq.b + h * p.sq.h;
-  const __nv_bfloat16* kb = p.k + b * p.sk.b + h * p.sk.h;
-  const __nv_bfloat16* vb = p.v + b * p.sv.b + h * p.sv.h;
-  __nv_bfloat16* yb = p.y + b * p.sy.b + h * p.sy.h;
+  auto bar = [&](int i) { return sb + lay.bar + 8 * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + lay.bar + 8 * B_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + lay.bar + 8 * B_COUNT + 4);
+#ifdef BASED_TC_TRACE
+  unsigned long long tr_wait[24];
+  for (int i = 0; i < 24; ++i) tr_wait[i] = 0;
+  long long tr_t = 0;
+  long long tr_t2 = 0;
+#define TR_BEGIN() tr_t = clock64()
+#define TR_END(slot) tr_wait[slot] += clock64() - tr_t
+#define TR2_BEGIN() tr_t2 = clock64()
+#define TR2_END(slot) tr_wait[slot] += clock64() - tr_t2
+  const long long tr_start = clock64();
+  auto wait = [&](int i, uint32_t parity, unsigned int code) {
+    const long long t0 = clock64();
+    mbar_wait_bounded(bar(i), parity & 1u, abort_flag, p.status, code);
+    tr_wait[i] += clock64() - t0;
+  };
+#else
+#define TR_BEGIN()
+#define TR_END(slot)
+#define TR2_BEGIN()
+#define TR2_END(slot)
+  auto wait = [&](int i, uint32_t parity, unsigned int code) {
+    mbar_wait_bounded(bar(i), parity & 1u, abort_flag, p.status, code);
+  };
+#endif
 
   // ------------------------------------------------------------------ set-up
   if (tid == 0) {
-    mbar_init(bar_s, 1);
-    mbar_init(bar_o, 1);
-    mbar_init(bar_st, 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
+    mbar_init(bar(B_S_DONE), 1);
+    mbar_init(bar(B_O_DONE), 1);
+    mbar_init(bar(B_ST_DONE), 1);
+    mbar_init(bar(B_P_READY), 4);
+    mbar_init(bar(B_PQ_READY), 4);
+    mbar_init(bar(B_PK_READY), 4);
+    mbar_init(bar(B_STB_READY), 4);
+    mbar_init(bar(B_O_FREE), 4);
     *abort_flag = 0;
     fence_mbar_init();
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TM_COLS);
-  // V' stages: zero everything once; the column groups above dv stay constant for the whole
-  // kernel (group dv/8 = [1,0,...,0] per token, the rest 0), the groups below are refilled.
-  for (int i = tid; i < 65536 / 16; i += NT) reinterpret_cast<uint4*>(smem + SM_V)[i] = make_uint4(0, 0, 0, 0);
-  __syncthreads();
-  if (tid < C) {
-    const uint32_t off = (dv >> 3) * 2048 + (tid >> 3) * 128 + (tid & 7) * 16;
-    const uint4 one = make_uint4(0x00003F80u, 0, 0, 0);  // bf16 1.0 in element 0
-    *reinterpret_cast<uint4*>(smem + SM_V + off) = one;
-    *reinterpret_cast<uint4*>(smem + SM_V + 32768 + off) = one;
+  // V' column groups dv/8 (ones column) and dv/8 + 1 (zeros) are constant for the whole kernel.
+  for (int i = tid; i < lay.nstage * 2 * C; i += NT) {
+    const int st = i / (2 * C), r = i - st * 2 * C, g = r / C, tk = r - g * C;
+    const uint4 val = g == 0 ? make_uint4(0x00003F80u, 0, 0, 0) : make_uint4(0, 0, 0, 0);  // bf16 1.0 in element 0
+    *reinterpret_cast<uint4*>(smem + st * lay.stage_bytes + 8192 + ((dv >> 3) + g) * 2048 + tk * 16) = val;
   }
+  fence_proxy_async();
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tlane = tmem + ((uint32_t)(qd * 32) << 16);  // this warp's lane window, column 0
 
-  const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-  const uint32_t idesc_o_pv = make_idesc_bf16(128, NV, 0, 1);   // A = P (TMEM), B = V' MN-major
-  const uint32_t idesc_o_st = make_idesc_bf16(128, NV, 0, 0);   // A = phi'(Q) (TMEM), B = state K-major
-  const uint32_t idesc_st = make_idesc_bf16(128, DR, 1, 1);     // A = V'^T MN-major, B = phi'(K) MN-major
-
-  const int nchunks = (L + C - 1) / C;
-  const int vpieces = C * (dv >> 3);
-
-  auto issue_loads = [&](int c, int stage) {
-    const int tok0 = c * C;
-    {
-      const int tk = tid >> 1, half = tid & 1;
-      const bool ok = tok0 + tk < L;
-      const int64_t row = ok ? tok0 + tk : 0;
-      const uint32_t off = stage * 4096 + (tk >> 3) * 256 + half * 128 + (tk & 7) * 16;
-      cp_async16(sb + SM_Q + off, qb + row * p.sq.l + half * 8, ok);
-      cp_async16(sb + SM_K + off, kb + row * p.sk.l + half * 8, ok);
-    }
-    const int gpt = dv >> 3;  // 16-byte pieces per token
-    for (int i = tid; i < vpieces; i += NT) {
-      const int tk = i / gpt, g = i - tk * gpt;
-      const bool ok = tok0 + tk < L;
-      const int64_t row = ok ? tok0 + tk : 0;
-      cp_async16(sb + SM_V + stage * 32768 + g * 2048 + (tk >> 3) * 128 + (tk & 7) * 16, vb + row * p.sv.l + g * 8,
-                 ok);
-    }
-  };
-
-  issue_loads(0, 0);
-  cp_async_commit();
-
-  for (int c = 0; c < nchunks; ++c) {
-    const int stage = c & 1;
-    const uint32_t par = c & 1;
-    const bool last = c + 1 == nchunks;
-    const bool valid = c * C + t < L;
-
-    // (A) chunk c's q/k/v have landed; everything written by the previous iteration
-    //     (bf16 state in smem, TMEM reads) is ordered before this chunk's MMAs.
-    cp_async_wait_all();
-    fence_proxy_async();
-    fence_before_sync();
-    __syncthreads();
-    fence_after_sync();
-
-    if (tid == 0) {
-      const uint64_t da = make_smem_desc(sb + SM_Q + stage * 4096, 128, 256);
-      const uint64_t db = make_smem_desc(sb + SM_K + stage * 4096, 128, 256);
-      mma_ss(tmem + TM_S, da, db, idesc_s, 0);
-      mma_commit(bar_s);
-    }
-    __syncwarp();
-    if (!last) issue_loads(c + 1, stage ^ 1);
-    cp_async_commit();
-
-    // ---- feature expansion: half 0 -> phi'(Q) into TMEM, half 1 -> phi'(K) into smem ----
-    {
-      float x[16];
-      const uint8_t* src = smem + (hf == 0 ? SM_Q : SM_K) + stage * 4096 + (t >> 3) * 256 + (t & 7) * 16;
-      unpack8(*reinterpret_cast<const uint4*>(src), x);
-      unpack8(*reinterpret_cast<const uint4*>(src + 128), x + 8);
-      if (hf == 0) {
-        static_for<0, 10>([&](auto G2) {
-          uint32_t r[8];
-          packed_group<2 * decltype(G2)::value>(x, r);
-          packed_group<2 * decltype(G2)::value + 1>(x, r + 4);
-          tmem_st8(tlane + TM_PQ + 8 * decltype(G2)::value, r);
-        });
-      } else {
-        uint8_t* dst = smem + SM_PHIK + (t >> 3) * 128 + (t & 7) * 16;
-        static_for<0, 20>([&](auto G) {
-          uint32_t r[4];
-          packed_group<decltype(G)::value>(x, r);
-          // tokens past the end contribute nothing to the state
-          const uint4 val = valid ? make_uint4(r[0], r[1], r[2], r[3]) : make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(dst + decltype(G)::value * 2048) = val;
-        });
-      }
-    }
-
-    // ---- P = causal(1 + x + x^2/2), x = S/4: read S, block barrier, overwrite in place ----
-    mbar_wait_bounded(bar_s, par, abort_flag, p.status, 1u);
-    fence_after_sync();
-    uint32_t sreg[2][32];
-    tmem_ld32(tlane + TM_S + hf * 64, sreg[0]);
-    tmem_ld32(tlane + TM_S + hf * 64 + 32, sreg[1]);
-    tmem_ld_wait();
-    fence_before_sync();
-    __syncthreads();
-    fence_after_sync();
+#ifndef BASED_EXPERIMENT_MMA_MASK
+#define BASED_EXPERIMENT_MMA_MASK 15
+#endif
+#ifdef BASED_EXPERIMENT_MMA_ONLY
+  // Timing experiment: only the MMA warp runs, without waiting for operands (results are garbage).
+  const bool mma_only = true;
+#else
+  const bool mma_only = false;
+#endif
+  if (mma_only && warp != W_MMA) {
+    // nothing
+  } else if (warp >= W_LOAD) {
+    // ================================================================ loaders: cp.async, 16-byte pieces.
+    // Load warp w owns buffer w and the chunks j = w (mod the buffer count): wait until the buffer is free,
+    // issue the chunk, wait for it to land, publish it.  Three chunks are in flight per CTA.
+    const int st = warp - W_LOAD, NS = lay.nstage;
+    const __nv_bfloat16* qb = p.q + b * p.sq.b + h * p.sq.h;
+    const __nv_bfloat16* kb = p.k + b * p.sk.b + h * p.sk.h;
+    const __nv_bfloat16* vb = p.v + b * p.sv.b + h * p.sv.h;
+    const uint32_t base = sb + st * lay.stage_bytes;
+    // q/k: piece i = lane + 32 n  ->  token (lane >> 1) + 16 n, half lane & 1
+    const int qk_tk = lane >> 1, qk_half = lane & 1;
+    const uint32_t qk_off = (qk_tk >> 3) * 256 + qk_half * 128 + (qk_tk & 7) * 16;
+    // v: piece i = lane + 32 n  ->  token i / gpt, 16-byte column group i % gpt, advanced incrementally
+    const int gpt = dv >> 3, dq = 32 / gpt, dr = 32 % gpt;
+    for (int j = st; j < nchunks && st < NS; j += NS) {
+      if (j >= NS) wait(B_EMPTY + st, j / NS - 1, 0x100u);
+      const int tok0 = j * C;
+      {
+        const __nv_bfloat16* qp = qb + (int64_t)(tok0 + qk_tk) * p.sq.l + qk_half * 8;
+        const __nv_bfloat16* kp = kb + (int64_t)(tok0 + qk_tk) * p.sk.l + qk_half * 8;
 #pragma unroll
-    for (int piece = 0; piece < 2; ++piece) {
-      uint32_t pk[16];
-      const int s0 = hf * 64 + piece * 32;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float pv[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float xx = __uint_as_float(sreg[piece][2 * i + e]) * 0.25f;
-          const float val = fmaf(xx, fmaf(xx, 0.5f, 1.0f), 1.0f);
-          pv[e] = (s0 + 2 * i + e <= t) ? val : 0.0f;
+        for (int n = 0; n < 8; ++n) {
+          const bool ok = tok0 + qk_tk + 16 * n < L;
+          cp_async16(base + qk_off + n * 512, ok ? qp + (int64_t)(16 * n) * p.sq.l : qb, ok);
+          cp_async16(base + 4096 + qk_off + n * 512, ok ? kp + (int64_t)(16 * n) * p.sk.l : kb, ok);
         }
-        pk[i] = pack_bf16(pv[0], pv[1]);
       }
-      tmem_st16(tlane + TM_S + (s0 >> 1), pk);
+      {
+        int tk = lane / gpt, g = lane - tk * gpt;
+        for (int n = 0; n < 4 * gpt; ++n) {
+          const bool ok = tok0 + tk < L;
+          cp_async16(base + 8192 + g * 2048 + tk * 16, ok ? vb + (int64_t)(tok0 + tk) * p.sv.l + g * 8 : vb, ok);
+          tk += dq; g += dr;
+          if (g >= gpt) { g -= gpt; ++tk; }
+        }
+      }
+      cp_async_commit();
+      cp_async_wait_all();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_FULL + st));
     }
-    tmem_st_wait();
-    fence_proxy_async();  // phi'(K) smem writes -> async proxy
-    fence_before_sync();
-    __syncthreads();
-
-    // ---- MMAs of the chunk ----
-    if (tid == 0) {
+  } else if (warp == W_MMA) {
+    // ================================================================ MMA issue (lane 0 issues; all lanes wait)
+    auto mwait = [&](int i, uint32_t parity, unsigned int code) { if (!mma_only) wait(i, parity, code); };
+    const int NS = lay.nstage;
+    const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+    const uint32_t idesc_o_pv = make_idesc_bf16(128, NV, 0, 1);   // A = P (TMEM), B = V' MN-major
+    const uint32_t idesc_o_st = make_idesc_bf16(128, NV, 0, 0);   // A = phi'(Q) (TMEM), B = state K-major
+    const uint32_t idesc_st = make_idesc_bf16(128, DR, 1, 1);     // A = V'^T MN-major, B = phi'(K) MN-major
+    // Descriptors differ between K-steps only in the start address (bits 0-13, units of 16 B).
+    const uint64_t d_q = make_smem_desc(sb, 128, 256);                 // + stage offset
+    const uint64_t d_k = make_smem_desc(sb + 4096, 128, 256);
+    const uint64_t d_v = make_smem_desc(sb + 8192, 128, 2048);         // + stage offset, + 16 per K-step
+    const uint64_t d_pk = make_smem_desc(sb + lay.phik, 128, 2048);    // + 16 per K-step
+    const uint64_t d_stb = make_smem_desc(sb + lay.stb, 2048, 128);    // + 256 per K-step
+    const uint32_t stage_units = (uint32_t)lay.stage_bytes >> 4;
+    auto issue_s = [&](int c) {  // S(c) = Q K^T
+      const uint32_t so = (c % NS) * stage_units;
+      mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
+      mma_commit(bar(B_S_DONE));
+    };
+    mwait(B_FULL + 0, 0, 0x200u);
+    fence_after_sync();
+    if (lane == 0) issue_s(0);
+    __syncwarp();
+    for (int c = 0; c < nchunks; ++c) {
+      const uint64_t dv_c = d_v + (c % NS) * stage_units;
+      // O(c) = P(c) V'(c): needs P(c) written and the previous chunk's O read out
+      mwait(B_P_READY, c, 0x201u);
+      if (c > 0) mwait(B_O_FREE, c - 1, 0x202u);
       fence_after_sync();
-      const uint32_t vbase = sb + SM_V + stage * 32768;
-#pragma unroll 1
-      for (int j = 0; j < C / 16; ++j)  // O = P V'
-        mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, make_smem_desc(vbase + j * 256, 128, 2048), idesc_o_pv, j > 0);
-      if (c > 0) {
-#pragma unroll 1
-        for (int j = 0; j < DR / 16; ++j)  // O += phi'(Q) State
-          mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, make_smem_desc(sb + SM_STB + j * 4096, 2048, 128), idesc_o_st,
-                 1);
-      }
-      mma_commit(bar_o);
-#pragma unroll 1
-      for (int j = 0; j < C / 16; ++j)  // St += V'^T phi'(K)
-        mma_ss(tmem + TM_ST, make_smem_desc(vbase + j * 256, 128, 2048),
-               make_smem_desc(sb + SM_PHIK + j * 256, 128, 2048), idesc_st, (c > 0 || j > 0) ? 1u : 0u);
-      mma_commit(bar_st);
-    }
-    __syncwarp();
-
-    // ---- epilogue: y = O[:, :dv] / (O[:, dv] + eps) ----
-    mbar_wait_bounded(bar_o, par, abort_flag, p.status, 2u);
-    fence_after_sync();
-    {
-      uint32_t dreg;
-      tmem_ld1(tlane + TM_O + dv, dreg);
-      tmem_ld_wait();
-      const float inv = 1.0f / (__uint_as_float(dreg) + p.eps);
-      const int j0 = hf * (dv >> 1);
-      __nv_bfloat16* yrow = yb + (int64_t)(c * C + t) * p.sy.l + j0;
-      for (int i = 0; i < (dv >> 4); ++i) {
-        uint32_t r[8];
-        tmem_ld8(tlane + TM_O + j0 + 8 * i, r);
-        tmem_ld_wait();
-        if (valid) {
-          uint4 o;
-          o.x = pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
-          o.y = pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
-          o.z = pack_bf16(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
-          o.w = pack_bf16(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
-          *reinterpret_cast<uint4*>(yrow + 8 * i) = o;
-        }
-      }
-    }
-
-    // ---- state: fp32 TMEM -> bf16 smem operand for the next chunk, or fp32 staging at the end ----
-    mbar_wait_bounded(bar_st, par, abort_flag, p.status, 4u);
-    fence_after_sync();
-    if (!last) {
-#pragma unroll 1
-      for (int i = 0; i < 5; ++i) {
-        uint32_t r[16];
-        const int col = hf * 80 + 16 * i;
-        tmem_ld16(tlane + TM_ST + col, r);
-        tmem_ld_wait();
-        uint4 lo, hi;
-        lo.x = pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1]));
-        lo.y = pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3]));
-        lo.z = pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5]));
-        lo.w = pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7]));
-        hi.x = pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9]));
-        hi.y = pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11]));
-        hi.z = pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13]));
-        hi.w = pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15]));
-        uint8_t* dst = smem + SM_STB + (col >> 3) * 2048 + t * 16;
-        *reinterpret_cast<uint4*>(dst) = lo;
-        *reinterpret_cast<uint4*>(dst + 2048) = hi;
-      }
-    } else if (p.kv_state != nullptr) {
-      float* stg = reinterpret_cast<float*>(smem + SM_V) + t * STAGE_STRIDE_F;
-#pragma unroll 1
-      for (int i = 0; i < 5; ++i) {
-        uint32_t r[16];
-        const int col = hf * 80 + 16 * i;
-        tmem_ld16(tlane + TM_ST + col, r);
-        tmem_ld_wait();
+      if (lane == 0 && (BASED_EXPERIMENT_MMA_MASK & 1)) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          *reinterpret_cast<uint4*>(stg + col + 4 * e) = make_uint4(r[4 * e], r[4 * e + 1], r[4 * e + 2], r[4 * e + 3]);
+        for (int j = 0; j < C / 16; ++j)
+          mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
+      }
+      __syncwarp();
+      // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
+      if (c + 1 < nchunks) {
+        mwait(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x203u);
+        fence_after_sync();
+        if (lane == 0 && (BASED_EXPERIMENT_MMA_MASK & 2)) issue_s(c + 1);
+        __syncwarp();
+      }
+      // O(c) += phi'(Q_c) State(c-1)
+      mwait(B_PQ_READY, c, 0x204u);
+      if (c > 0) mwait(B_STB_READY, c - 1, 0x205u);
+      fence_after_sync();
+      if (lane == 0) {
+        if (c > 0 && (BASED_EXPERIMENT_MMA_MASK & 4)) {
+#pragma unroll
+          for (int j = 0; j < DR / 16; ++j)
+            mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb + 256 * j, idesc_o_st, 1);
+        }
+        mma_commit(bar(B_O_DONE));
+      }
+      __syncwarp();
+      // State^T += V'(c)^T phi'(K_c)
+      mwait(B_PK_READY, c, 0x206u);
+      fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < ((BASED_EXPERIMENT_MMA_MASK & 8) ? C / 16 : 0); ++j)
+          mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk + 16 * j, idesc_st, (c > 0 || j > 0) ? 1u : 0u);
+        mma_commit(bar(B_ST_DONE));
+        mma_commit(bar(B_EMPTY + c % NS));
+      }
+      __syncwarp();
+    }
+    if (mma_only) wait(B_ST_DONE, nchunks - 1, 0x2FFu);
+  } else if (warp < 4) {
+    // ================================================================ expansion warps: phi'(Q) -> TMEM, phi'(K) -> smem
+    for (int c = 0; c < nchunks; ++c) {
+      const uint8_t* stg = smem + (c % lay.nstage) * lay.stage_bytes + (t >> 3) * 256 + (t & 7) * 16;
+      const bool valid = c * C + t < L;
+      wait(B_FULL + c % lay.nstage, c / lay.nstage, 0x300u);
+      uint32_t X[8];
+      {
+        const uint4 a = *reinterpret_cast<const uint4*>(stg), bq = *reinterpret_cast<const uint4*>(stg + 128);
+        X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
+      }
+      if (c > 0) wait(B_O_DONE, c - 1, 0x301u);  // the previous phi'(Q) has been consumed
+      fence_after_sync();
+      TR_BEGIN();
+      {
+        uint32_t hold[4];
+        expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+          constexpr int g = decltype(G)::value;
+          if constexpr ((g & 1) == 0) {
+            hold[0] = w0; hold[1] = w1; hold[2] = w2; hold[3] = w3;
+          } else {
+            const uint32_t r[8] = {hold[0], hold[1], hold[2], hold[3], w0, w1, w2, w3};
+            tmem_st8(tlane + TM_PQ + 4 * (g - 1), r);
+          }
+        });
+      }
+      TR_END(15);
+      TR_BEGIN();
+      tmem_st_wait();
+      fence_before_sync();
+      __syncwarp();
+      TR_END(16);
+      if (lane == 0) mbar_arrive(bar(B_PQ_READY));
+      {
+        const uint4 a = *reinterpret_cast<const uint4*>(stg + 4096), bq = *reinterpret_cast<const uint4*>(stg + 4096 + 128);
+        X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
+      }
+      if (!valid) {  // tokens past the end contribute nothing to the state: phi'(K) = 0, also the constant
+#pragma unroll
+        for (int m = 0; m < 8; ++m) X[m] = 0;
+      }
+      const uint32_t one = valid ? 0xFFFFFFFFu : 0u;
+      if (c > 0) wait(B_ST_DONE, c - 1, 0x302u);  // the previous phi'(K) has been consumed
+      uint8_t* dst = smem + lay.phik + t * 16;
+      TR_BEGIN();
+      expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+        constexpr int g = decltype(G)::value;
+        if constexpr (g == 0) w0 &= one;
+        *reinterpret_cast<uint4*>(dst + g * 2048) = make_uint4(w0, w1, w2, w3);
+      });
+      TR_END(17);
+      TR_BEGIN();
+      fence_proxy_async();
+      __syncwarp();
+      TR_END(18);
+      if (lane == 0) mbar_arrive(bar(B_PK_READY));
+    }
+  } else {
+    // ================================================================ polynomial / epilogue / state-drain warps
+    __nv_bfloat16* yb = p.y + b * p.sy.b + h * p.sy.h;
+    // P(c) = causal(1 + s/4 + s^2/32), evaluated in bf16x2 (two FMAs per pair), in place over S.
+    // Column pieces right of this warp's diagonal block are all masked: zeros, no load; only the
+    // diagonal piece needs the per-element mask.
+    auto make_p = [&](int c) {
+      wait(B_S_DONE, c, 0x400u);
+      fence_after_sync();
+      TR_BEGIN();
+      constexpr uint32_t k1 = 0x3F803F80u, kq = 0x3E803E80u, k32 = 0x3D003D00u;  // (1,1) (1/4,1/4) (1/32,1/32)
+#pragma unroll 1
+      for (int piece = 0; piece <= qd; ++piece) {
+        uint32_t sreg[32], pk[16];
+        tmem_ld32(tlane + TM_S + piece * 32, sreg);
+        tmem_ld_wait();
+        const int rel = t - piece * 32;  // columns 0..rel of this piece are visible (rel >= 31 left of the diagonal)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+          const uint32_t pv = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
+          const uint32_t mask = (2 * i + 1 <= rel) ? 0xFFFFFFFFu : ((2 * i <= rel) ? 0x0000FFFFu : 0u);
+          pk[i] = pv & mask;
+        }
+        tmem_st16(tlane + TM_S + piece * 16, pk);
+      }
+      {
+        uint32_t z[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) z[i] = 0;
+#pragma unroll 1
+        for (int piece = qd + 1; piece < 4; ++piece) tmem_st16(tlane + TM_S + piece * 16, z);
+      }
+      tmem_st_wait();
+      fence_before_sync();
+      __syncwarp();
+      TR_END(19);
+      if (lane == 0) mbar_arrive(bar(B_P_READY));
+    };
+    auto cvt16 = [&](const uint32_t (&r)[16], float sc, uint4& lo, uint4& hi) {
+      lo.x = pack_bf16(__uint_as_float(r[0]) * sc, __uint_as_float(r[1]) * sc);
+      lo.y = pack_bf16(__uint_as_float(r[2]) * sc, __uint_as_float(r[3]) * sc);
+      lo.z = pack_bf16(__uint_as_float(r[4]) * sc, __uint_as_float(r[5]) * sc);
+      lo.w = pack_bf16(__uint_as_float(r[6]) * sc, __uint_as_float(r[7]) * sc);
+      hi.x = pack_bf16(__uint_as_float(r[8]) * sc, __uint_as_float(r[9]) * sc);
+      hi.y = pack_bf16(__uint_as_float(r[10]) * sc, __uint_as_float(r[11]) * sc);
+      hi.z = pack_bf16(__uint_as_float(r[12]) * sc, __uint_as_float(r[13]) * sc);
+      hi.w = pack_bf16(__uint_as_float(r[14]) * sc, __uint_as_float(r[15]) * sc);
+    };
+    make_p(0);
+    for (int c = 0; c < nchunks; ++c) {
+      const bool last = c + 1 == nchunks;
+      if (!last) make_p(c + 1);
+      // ---- epilogue: y = O[:, :dv] / (O[:, dv] + eps), 32 columns per round trip ----
+      wait(B_O_DONE, c, 0x401u);
+      fence_after_sync();
+      TR_BEGIN();
+      {
+        uint32_t dreg;
+        tmem_ld1(tlane + TM_O + dv, dreg);
+        // Each thread parks its normalised row in this warp's 32-row staging tile; the warp then
+        // copies the tile out with every store instruction covering whole 128-byte lines
+        // (row-per-thread stores would touch 32 different lines per instruction).
+        uint8_t* ytile = smem + lay.ystage + (qd * 32) * lay.yrow_bytes;
+        uint8_t* yrow_s = ytile + lane * lay.yrow_bytes;
+        const int n16 = dv >> 4;
+        float inv = 0.f;
+#pragma unroll 1
+        for (int i0 = 0; i0 < n16; i0 += 2) {
+          uint32_t r0[16], r1[16];
+          TR2_BEGIN();
+          tmem_ld16(tlane + TM_O + 16 * i0, r0);
+          if (i0 + 1 < n16) tmem_ld16(tlane + TM_O + 16 * (i0 + 1), r1);
+          tmem_ld_wait();
+          TR2_END(22);
+          if (i0 == 0) inv = 1.0f / (__uint_as_float(dreg) + p.eps);
+          uint4 lo, hi;
+          cvt16(r0, inv, lo, hi);
+          *reinterpret_cast<uint4*>(yrow_s + 32 * i0) = lo;
+          *reinterpret_cast<uint4*>(yrow_s + 32 * i0 + 16) = hi;
+          if (i0 + 1 < n16) {
+            cvt16(r1, inv, lo, hi);
+            *reinterpret_cast<uint4*>(yrow_s + 32 * i0 + 32) = lo;
+            *reinterpret_cast<uint4*>(yrow_s + 32 * i0 + 48) = hi;
+          }
+        }
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_O_FREE));  // O has been read; the next chunk may overwrite it
+        const int cpr = dv >> 3;                     // 16-byte pieces per row
+        const int tok_w = c * C + qd * 32;           // first token of this warp's tile
+        __nv_bfloat16* ytok = yb + (int64_t)tok_w * p.sy.l;
+#ifndef BASED_EXPERIMENT_SKIP_YSTORE
+        for (int idx = lane; idx < 32 * cpr; idx += 32) {
+          const int r = idx / cpr, cc = idx - r * cpr;
+          if (tok_w + r < L) {
+            const uint4 val = *reinterpret_cast<const uint4*>(ytile + r * lay.yrow_bytes + cc * 16);
+            *reinterpret_cast<uint4*>(ytok + (int64_t)r * p.sy.l + cc * 8) = val;
+          }
+        }
+#endif
+        __syncwarp();  // the tile is rewritten by other lanes in the next chunk
+      }
+      TR_END(20);
+      // ---- state: fp32 TMEM -> bf16 smem operand for the next chunk, or fp32 staging at the end ----
+      wait(B_ST_DONE, c, 0x402u);
+      fence_after_sync();
+      if (!last) {
+        TR_BEGIN();
+#pragma unroll 1
+        for (int i = 0; i < 5; ++i) {  // 32 feature columns per round trip
+          uint32_t r0[16], r1[16];
+          TR2_BEGIN();
+          tmem_ld16(tlane + TM_ST + 32 * i, r0);
+          tmem_ld16(tlane + TM_ST + 32 * i + 16, r1);
+          tmem_ld_wait();
+          TR2_END(23);
+          uint4 a0, a1, b0, b1;
+          cvt16(r0, 1.0f, a0, a1);
+          cvt16(r1, 1.0f, b0, b1);
+          if (t < NV) {  // rows >= NV of the B operand are never read (N = NV)
+            uint8_t* dst = smem + lay.stb + (4 * i) * 2048 + t * 16;
+            *reinterpret_cast<uint4*>(dst) = a0;
+            *reinterpret_cast<uint4*>(dst + 2048) = a1;
+            *reinterpret_cast<uint4*>(dst + 4096) = b0;
+            *reinterpret_cast<uint4*>(dst + 6144) = b1;
+          }
+        }
+        fence_proxy_async();
+        fence_before_sync();
+        __syncwarp();
+        TR_END(21);
+        if (lane == 0) mbar_arrive(bar(B_STB_READY));
+      } else if (p.kv_state != nullptr) {
+        // every MMA and every other warp's use of shared memory is over: stage at offset 0.
+        // The TMEM loads are warp-collective, so every lane issues them; only rows < NV are kept.
+        float* stg = reinterpret_cast<float*>(smem) + t * STAGE_STRIDE_F;
+#pragma unroll 1
+        for (int i = 0; i < 10; ++i) {
+          uint32_t r[16];
+          tmem_ld16(tlane + TM_ST + 16 * i, r);
+          tmem_ld_wait();
+          if (t < NV) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              *reinterpret_cast<uint4*>(stg + 16 * i + 4 * e) =
+                  make_uint4(r[4 * e], r[4 * e + 1], r[4 * e + 2], r[4 * e + 3]);
+          }
+        }
       }
     }
   }
 
+#ifdef BASED_TC_TRACE
+  if (bh == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == W_MMA || warp == W_LOAD)) {
+    const int role = warp == 0 ? 0 : warp == 4 ? 1 : warp == W_MMA ? 2 : 3;
+    for (int i = 0; i < 24; ++i) g_tc_trace[role][i] = tr_wait[i];
+    g_tc_trace[role][B_COUNT] = clock64() - tr_start;
+  }
+#endif
   // ------------------------------------------------------------------ final state, reference layout
   fence_before_sync();
   __syncthreads();
   if (p.kv_state != nullptr) {
-    const float* stg = reinterpret_cast<const float*>(smem + SM_V);
+    const float* stg = reinterpret_cast<const float*>(smem);
     const int total = (dv + 1) * kExpandedDim;
     for (int e = tid; e < total; e += NT) {
       const int n = e / kExpandedDim, f = e - n * kExpandedDim;
@@ -400,6 +616,12 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
 }
 
 }  // namespace
+
+#ifdef BASED_TC_TRACE
+extern "C" int based_tc_trace_read(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 4 * 24);
+}
+#endif
 
 int read_tc_status(unsigned int* out, int reset) {
   unsigned int v = 0;
@@ -435,9 +657,10 @@ int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void*
   p.eps = eps;
   cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_tc_status);
   if (e != cudaSuccess) return (int)e;
-  e = cudaFuncSetAttribute(linattn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
+  const Smem lay(dv);
+  e = cudaFuncSetAttribute(linattn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total);
   if (e != cudaSuccess) return (int)e;
-  linattn_prefill_tc_kernel<<<B * H, NT, SM_TOTAL, stream>>>(p);
+  linattn_prefill_tc_kernel<<<B * H, NT, lay.total, stream>>>(p);
   return (int)cudaGetLastError();
 }
 
