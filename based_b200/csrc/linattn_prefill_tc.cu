@@ -31,7 +31,7 @@ __device__ unsigned int g_tc_status = 0;  // ORed with a code when a bounded wai
 #ifdef BASED_TC_TRACE
 // Debug build only: per-role cycle counters of CTA 0 (cycles spent in each barrier wait, total
 // cycles), read back with based_tc_trace_read().
-__device__ unsigned long long g_tc_trace[4][24];
+__device__ unsigned long long g_tc_trace[4][32];
 #endif
 
 namespace {
@@ -48,12 +48,13 @@ constexpr int W_MMA = 8, W_LOAD = 9;
 // M = 128 operand, i.e. 16 column groups from the stage's V' base; the groups past NV/8 are
 // whatever follows in shared memory and only feed accumulator lanes >= NV, which nobody reads.
 struct Smem {
-  int nstage, stage_bytes, phik, stb, ystage, yrow_bytes, bar, total;
+  int nstage, npk, stage_bytes, phik, stb, ystage, yrow_bytes, bar, total;
   __host__ __device__ explicit Smem(int dv) {
     nstage = dv <= 64 ? 3 : 2;     // what fits in 227 KB
+    npk = dv <= 64 ? 2 : 1;        // phi'(K) buffers
     stage_bytes = 8192 + ((dv + 16) >> 3) * 2048;
-    phik = nstage * stage_bytes;   // 40960  MN-major [20 groups of 8 feats][128 tok][16 B]
-    stb = phik + 40960;            // 40960  K-major  [20 k-units][128 rows][16 B]
+    phik = nstage * stage_bytes;   // npk x 40960  MN-major [20 groups of 8 feats][128 tok][16 B]
+    stb = phik + npk * 40960;      // 40960  K-major  [20 k-units][128 rows][16 B]
     ystage = stb + 40960;          // output tile [128 rows][dv bf16 + 16 B pad] for the bulk stores
     yrow_bytes = dv * 2 + 16;      // the pad makes the per-row 16-byte stores bank-conflict free
     bar = ystage + C * yrow_bytes; // mbarriers, TMEM base, abort flag
@@ -71,7 +72,7 @@ constexpr uint32_t TM_COLS = 512;
 
 // mbarrier slots (8 bytes each) from Smem::bar
 enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_P_READY, B_O_DONE, B_ST_DONE, B_PQ_READY, B_PK_READY,
-           B_STB_READY, B_O_FREE, B_COUNT };
+           B_STB_READY, B_O_FREE, B_PK_FREE, B_PK_FREE1, B_COUNT };
 
 template <int G0, int G1, typename F>
 __device__ __forceinline__ void static_for(F&& f) {
@@ -193,8 +194,8 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + lay.bar + 8 * B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + lay.bar + 8 * B_COUNT + 4);
 #ifdef BASED_TC_TRACE
-  unsigned long long tr_wait[24];
-  for (int i = 0; i < 24; ++i) tr_wait[i] = 0;
+  unsigned long long tr_wait[32];
+  for (int i = 0; i < 32; ++i) tr_wait[i] = 0;
   long long tr_t = 0;
   long long tr_t2 = 0;
 #define TR_BEGIN() tr_t = clock64()
@@ -228,6 +229,8 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
     mbar_init(bar(B_PK_READY), 4);
     mbar_init(bar(B_STB_READY), 4);
     mbar_init(bar(B_O_FREE), 4);
+    mbar_init(bar(B_PK_FREE), 1);
+    mbar_init(bar(B_PK_FREE + 1), 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -300,74 +303,95 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       if (lane == 0) mbar_arrive(bar(B_FULL + st));
     }
   } else if (warp == W_MMA) {
-    // ================================================================ MMA issue (lane 0 issues; all lanes wait)
-    auto mwait = [&](int i, uint32_t parity, unsigned int code) { if (!mma_only) wait(i, parity, code); };
-    const int NS = lay.nstage;
-    const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-    const uint32_t idesc_o_pv = make_idesc_bf16(128, NV, 0, 1);   // A = P (TMEM), B = V' MN-major
-    const uint32_t idesc_o_st = make_idesc_bf16(128, NV, 0, 0);   // A = phi'(Q) (TMEM), B = state K-major
-    const uint32_t idesc_st = make_idesc_bf16(128, DR, 1, 1);     // A = V'^T MN-major, B = phi'(K) MN-major
-    // Descriptors differ between K-steps only in the start address (bits 0-13, units of 16 B).
-    const uint64_t d_q = make_smem_desc(sb, 128, 256);                 // + stage offset
-    const uint64_t d_k = make_smem_desc(sb + 4096, 128, 256);
-    const uint64_t d_v = make_smem_desc(sb + 8192, 128, 2048);         // + stage offset, + 16 per K-step
-    const uint64_t d_pk = make_smem_desc(sb + lay.phik, 128, 2048);    // + 16 per K-step
-    const uint64_t d_stb = make_smem_desc(sb + lay.stb, 2048, 128);    // + 256 per K-step
-    const uint32_t stage_units = (uint32_t)lay.stage_bytes >> 4;
-    auto issue_s = [&](int c) {  // S(c) = Q K^T
-      const uint32_t so = (c % NS) * stage_units;
-      mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
+    // ================================================================ MMA issue: one thread runs the whole loop
+    if (lane == 0) {
+#ifdef BASED_TC_TRACE
+      auto mwait = [&](int i, uint32_t parity, unsigned int code) {
+        if (mma_only) return;
+        const long long t0 = clock64();
+        mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
+        tr_wait[i] += clock64() - t0;
+      };
+#else
+      auto mwait = [&](int i, uint32_t parity, unsigned int code) {
+        mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
+      };
+#endif
+      const int NS = lay.nstage, NPK = lay.npk;
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o_pv = make_idesc_bf16(128, NV, 0, 1);   // A = P (TMEM), B = V' MN-major
+      const uint32_t idesc_o_st = make_idesc_bf16(128, NV, 0, 0);   // A = phi'(Q) (TMEM), B = state K-major
+      const uint32_t idesc_st = make_idesc_bf16(128, DR, 1, 1);     // A = V'^T MN-major, B = phi'(K) MN-major
+      // Descriptors differ between K-steps only in the start address (bits 0-13, units of 16 B).
+      const uint64_t d_q = make_smem_desc(sb, 128, 256);                 // + stage offset
+      const uint64_t d_k = make_smem_desc(sb + 4096, 128, 256);
+      const uint64_t d_v = make_smem_desc(sb + 8192, 128, 2048);         // + stage offset, + 16 per K-step
+      const uint64_t d_pk = make_smem_desc(sb + lay.phik, 128, 2048);    // + buffer offset, + 16 per K-step
+      const uint64_t d_stb = make_smem_desc(sb + lay.stb, 2048, 128);    // + 256 per K-step
+      const uint32_t stage_units = (uint32_t)lay.stage_bytes >> 4;
+      // stage / phase bookkeeping by counters: st = c % NS, st_par = (c / NS) & 1, and the same for c + 1
+      int st = 0, st1 = (1 % NS);
+      uint32_t st1_par = (NS == 1) ? 1u : 0u;
+      int pkb = 0;
+      mwait(B_FULL + 0, 0, 0x200u);
+      fence_after_sync();
+      mma_ss(tmem + TM_S, d_q, d_k, idesc_s, 0);
       mma_commit(bar(B_S_DONE));
-    };
-    mwait(B_FULL + 0, 0, 0x200u);
-    fence_after_sync();
-    if (lane == 0) issue_s(0);
-    __syncwarp();
-    for (int c = 0; c < nchunks; ++c) {
-      const uint64_t dv_c = d_v + (c % NS) * stage_units;
-      // O(c) = P(c) V'(c): needs P(c) written and the previous chunk's O read out
-      mwait(B_P_READY, c, 0x201u);
-      if (c > 0) mwait(B_O_FREE, c - 1, 0x202u);
-      fence_after_sync();
-      if (lane == 0 && (BASED_EXPERIMENT_MMA_MASK & 1)) {
-#pragma unroll
-        for (int j = 0; j < C / 16; ++j)
-          mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
-      }
-      __syncwarp();
-      // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
-      if (c + 1 < nchunks) {
-        mwait(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x203u);
+      for (int c = 0; c < nchunks; ++c) {
+        const uint64_t dv_c = d_v + st * stage_units;
+        // O(c) = P(c) V'(c): needs P(c) written and the previous chunk's O read out
+        mwait(B_P_READY, c, 0x201u);
+        if (c > 0) mwait(B_O_FREE, c - 1, 0x202u);
         fence_after_sync();
-        if (lane == 0 && (BASED_EXPERIMENT_MMA_MASK & 2)) issue_s(c + 1);
-        __syncwarp();
-      }
-      // O(c) += phi'(Q_c) State(c-1)
-      mwait(B_PQ_READY, c, 0x204u);
-      if (c > 0) mwait(B_STB_READY, c - 1, 0x205u);
-      fence_after_sync();
-      if (lane == 0) {
+        if (BASED_EXPERIMENT_MMA_MASK & 1) {
+#pragma unroll
+          for (int j = 0; j < C / 16; ++j)
+            mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
+        }
+        // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
+        if (c + 1 < nchunks) {
+          mwait(B_FULL + st1, st1_par, 0x203u);
+          fence_after_sync();
+          if (BASED_EXPERIMENT_MMA_MASK & 2) {
+            const uint32_t so = st1 * stage_units;
+            mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
+          }
+          mma_commit(bar(B_S_DONE));
+        }
+        // O(c) += phi'(Q_c) State(c-1)
+        mwait(B_PQ_READY, c, 0x204u);
+        if (c > 0) mwait(B_STB_READY, c - 1, 0x205u);
+        fence_after_sync();
         if (c > 0 && (BASED_EXPERIMENT_MMA_MASK & 4)) {
 #pragma unroll
           for (int j = 0; j < DR / 16; ++j)
             mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb + 256 * j, idesc_o_st, 1);
         }
         mma_commit(bar(B_O_DONE));
-      }
-      __syncwarp();
-      // State^T += V'(c)^T phi'(K_c)
-      mwait(B_PK_READY, c, 0x206u);
-      fence_after_sync();
-      if (lane == 0) {
+        // State^T += V'(c)^T phi'(K_c)
+        mwait(B_PK_READY, c, 0x206u);
+        fence_after_sync();
+        {
+          const uint64_t d_pk_c = d_pk + pkb * (40960 >> 4);
 #pragma unroll
-        for (int j = 0; j < ((BASED_EXPERIMENT_MMA_MASK & 8) ? C / 16 : 0); ++j)
-          mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk + 16 * j, idesc_st, (c > 0 || j > 0) ? 1u : 0u);
+          for (int j = 0; j < ((BASED_EXPERIMENT_MMA_MASK & 8) ? C / 16 : 0); ++j)
+            mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (c > 0 || j > 0) ? 1u : 0u);
+        }
         mma_commit(bar(B_ST_DONE));
-        mma_commit(bar(B_EMPTY + c % NS));
+        mma_commit(bar(B_EMPTY + st));
+        mma_commit(bar(B_PK_FREE + pkb));
+        st = st1;
+        if (++st1 == NS) { st1 = 0; st1_par ^= 1u; }
+        if (++pkb == NPK) pkb = 0;
       }
-      __syncwarp();
+      if (mma_only) mbar_wait_bounded<false>(bar(B_ST_DONE), (nchunks - 1) & 1u, abort_flag, p.status, 0x2FFu);
+#ifdef BASED_TC_TRACE
+      if (bh == 0) {
+        for (int i = 0; i < 32; ++i) g_tc_trace[2][i] = tr_wait[i];
+        g_tc_trace[2][31] = clock64() - tr_start;
+      }
+#endif
     }
-    if (mma_only) wait(B_ST_DONE, nchunks - 1, 0x2FFu);
   } else if (warp < 4) {
     // ================================================================ expansion warps: phi'(Q) -> TMEM, phi'(K) -> smem
     for (int c = 0; c < nchunks; ++c) {
@@ -394,12 +418,12 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
           }
         });
       }
-      TR_END(15);
+      TR_END(17);
       TR_BEGIN();
       tmem_st_wait();
       fence_before_sync();
       __syncwarp();
-      TR_END(16);
+      TR_END(18);
       if (lane == 0) mbar_arrive(bar(B_PQ_READY));
       {
         const uint4 a = *reinterpret_cast<const uint4*>(stg + 4096), bq = *reinterpret_cast<const uint4*>(stg + 4096 + 128);
@@ -410,19 +434,21 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         for (int m = 0; m < 8; ++m) X[m] = 0;
       }
       const uint32_t one = valid ? 0xFFFFFFFFu : 0u;
-      if (c > 0) wait(B_ST_DONE, c - 1, 0x302u);  // the previous phi'(K) has been consumed
-      uint8_t* dst = smem + lay.phik + t * 16;
+      // the phi'(K) buffer is free once the state update that read it (NPK chunks ago) has completed
+      const int pkb = c % lay.npk;
+      if (c >= lay.npk) wait(B_PK_FREE + pkb, c / lay.npk - 1, 0x302u);
+      uint8_t* dst = smem + lay.phik + pkb * 40960 + t * 16;
       TR_BEGIN();
       expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
         constexpr int g = decltype(G)::value;
         if constexpr (g == 0) w0 &= one;
         *reinterpret_cast<uint4*>(dst + g * 2048) = make_uint4(w0, w1, w2, w3);
       });
-      TR_END(17);
+      TR_END(19);
       TR_BEGIN();
       fence_proxy_async();
       __syncwarp();
-      TR_END(18);
+      TR_END(20);
       if (lane == 0) mbar_arrive(bar(B_PK_READY));
     }
   } else {
@@ -461,7 +487,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       tmem_st_wait();
       fence_before_sync();
       __syncwarp();
-      TR_END(19);
+      TR_END(21);
       if (lane == 0) mbar_arrive(bar(B_P_READY));
     };
     auto cvt16 = [&](const uint32_t (&r)[16], float sc, uint4& lo, uint4& hi) {
@@ -499,7 +525,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
           tmem_ld16(tlane + TM_O + 16 * i0, r0);
           if (i0 + 1 < n16) tmem_ld16(tlane + TM_O + 16 * (i0 + 1), r1);
           tmem_ld_wait();
-          TR2_END(22);
+          TR2_END(24);
           if (i0 == 0) inv = 1.0f / (__uint_as_float(dreg) + p.eps);
           uint4 lo, hi;
           cvt16(r0, inv, lo, hi);
@@ -518,17 +544,32 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         const int tok_w = c * C + qd * 32;           // first token of this warp's tile
         __nv_bfloat16* ytok = yb + (int64_t)tok_w * p.sy.l;
 #ifndef BASED_EXPERIMENT_SKIP_YSTORE
-        for (int idx = lane; idx < 32 * cpr; idx += 32) {
-          const int r = idx / cpr, cc = idx - r * cpr;
-          if (tok_w + r < L) {
-            const uint4 val = *reinterpret_cast<const uint4*>(ytile + r * lay.yrow_bytes + cc * 16);
-            *reinterpret_cast<uint4*>(ytok + (int64_t)r * p.sy.l + cc * 8) = val;
+        // piece idx = lane + 32 n -> (row idx / cpr, piece idx % cpr), advanced incrementally;
+        // four loads are issued before their four stores so their latencies overlap
+        {
+          const int dq = 32 / cpr, dr = 32 % cpr;
+          int r = lane / cpr, cc = lane - r * cpr;
+          const int total = cpr;  // 32 * cpr pieces / 32 lanes
+          for (int n0 = 0; n0 < total; n0 += 4) {
+            uint4 val[4];
+            int rr[4], cq[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              rr[u] = r; cq[u] = cc;
+              if (n0 + u < total) val[u] = *reinterpret_cast<const uint4*>(ytile + r * lay.yrow_bytes + cc * 16);
+              r += dq; cc += dr;
+              if (cc >= cpr) { cc -= cpr; ++r; }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (n0 + u < total && tok_w + rr[u] < L)
+                *reinterpret_cast<uint4*>(ytok + (int64_t)rr[u] * p.sy.l + cq[u] * 8) = val[u];
           }
         }
 #endif
         __syncwarp();  // the tile is rewritten by other lanes in the next chunk
       }
-      TR_END(20);
+      TR_END(22);
       // ---- state: fp32 TMEM -> bf16 smem operand for the next chunk, or fp32 staging at the end ----
       wait(B_ST_DONE, c, 0x402u);
       fence_after_sync();
@@ -541,7 +582,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
           tmem_ld16(tlane + TM_ST + 32 * i, r0);
           tmem_ld16(tlane + TM_ST + 32 * i + 16, r1);
           tmem_ld_wait();
-          TR2_END(23);
+          TR2_END(25);
           uint4 a0, a1, b0, b1;
           cvt16(r0, 1.0f, a0, a1);
           cvt16(r1, 1.0f, b0, b1);
@@ -556,7 +597,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         fence_proxy_async();
         fence_before_sync();
         __syncwarp();
-        TR_END(21);
+        TR_END(23);
         if (lane == 0) mbar_arrive(bar(B_STB_READY));
       } else if (p.kv_state != nullptr) {
         // every MMA and every other warp's use of shared memory is over: stage at offset 0.
@@ -579,10 +620,10 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   }
 
 #ifdef BASED_TC_TRACE
-  if (bh == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == W_MMA || warp == W_LOAD)) {
-    const int role = warp == 0 ? 0 : warp == 4 ? 1 : warp == W_MMA ? 2 : 3;
-    for (int i = 0; i < 24; ++i) g_tc_trace[role][i] = tr_wait[i];
-    g_tc_trace[role][B_COUNT] = clock64() - tr_start;
+  if (bh == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == W_LOAD)) {
+    const int role = warp == 0 ? 0 : warp == 4 ? 1 : 3;
+    for (int i = 0; i < 32; ++i) g_tc_trace[role][i] = tr_wait[i];
+    g_tc_trace[role][31] = clock64() - tr_start;
   }
 #endif
   // ------------------------------------------------------------------ final state, reference layout
@@ -619,7 +660,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
 
 #ifdef BASED_TC_TRACE
 extern "C" int based_tc_trace_read(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 4 * 24);
+  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 4 * 32);
 }
 #endif
 

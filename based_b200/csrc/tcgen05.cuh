@@ -146,6 +146,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t saddr, uint32_t parity) {
 // *abort_flag (shared) so that every later wait of the CTA returns at once, and ORs `code`
 // into *status (global).  The kernel then runs to its end with meaningless results instead of
 // hanging; the host reads the status word.
+template <bool kWarpSync = true>
 __device__ __forceinline__ void mbar_wait_bounded(uint32_t saddr, uint32_t parity, volatile int* abort_flag,
                                                   unsigned int* status, unsigned int code,
                                                   long long max_cycles = 2000000000LL) {
@@ -162,7 +163,7 @@ __device__ __forceinline__ void mbar_wait_bounded(uint32_t saddr, uint32_t parit
       }
     }
   }
-  __syncwarp();
+  if (kWarpSync) __syncwarp();  // kWarpSync = false: called by a single lane of a diverged warp
 }
 
 // ---------------------------------------------------------------- cp.async (16-byte, zero-fill when !valid)
