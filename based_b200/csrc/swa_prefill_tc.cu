@@ -23,6 +23,14 @@ namespace based {
 
 __device__ unsigned int g_tc_status_swa = 0;
 
+#ifdef BASED_TC_TRACE
+// Debug build only: cycles per phase summed over all CTAs (thread 0), and the CTA count.
+__device__ unsigned long long g_swa_trace[16];
+#define SWA_TR(slot) do { if (tid == 0) { const long long now_ = clock64(); atomicAdd(&g_swa_trace[slot], (unsigned long long)(now_ - tr_t)); tr_t = now_; } } while (0)
+#else
+#define SWA_TR(slot)
+#endif
+
 namespace {
 
 using namespace tc;
@@ -58,41 +66,60 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const Params p) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_BAR + 20);
 
+#ifdef BASED_TC_TRACE
+  long long tr_t = clock64();
+#endif
   if (tid == 0) {
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
-  __syncwarp();
-  if (warp == 0) tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
 
   // ---- loads: 16-byte pieces straight into the operand layouts, zero-filled outside [0, L) ----
   const int upr = hd >> 3;  // 16-byte units per row
   {
+    // piece i = tid + 128 n  ->  row i / upr, unit i % upr, advanced incrementally
+    const int dq = NT / upr, dr = NT % upr;
     const __nv_bfloat16* qb = p.q + b * p.sq.b + h * p.sq.h;
-    for (int i = tid; i < TQ * upr; i += NT) {
-      const int r = i / upr, u = i - r * upr;
-      const bool ok = t0 + r < L;
-      cp_async16(sb + SM_Q + u * 2048 + r * 16, qb + (int64_t)(ok ? t0 + r : 0) * p.sq.l + u * 8, ok);
+    {
+      int r = tid / upr, u = tid - r * upr;
+      for (int n = 0; n < upr; ++n) {  // 128 rows x upr units / 128 threads
+        const bool ok = t0 + r < L;
+        cp_async16(sb + SM_Q + u * 2048 + r * 16, ok ? qb + (int64_t)(t0 + r) * p.sq.l + u * 8 : qb, ok);
+        r += dq; u += dr;
+        if (u >= upr) { u -= upr; ++r; }
+      }
     }
     const __nv_bfloat16* kb = p.k + b * p.sk.b + h * p.sk.h;
     const __nv_bfloat16* vb = p.v + b * p.sv.b + h * p.sv.h;
-    for (int i = tid; i < NK * upr; i += NT) {
-      const int r = i / upr, u = i - r * upr;
-      const int pos = k0 + r;
-      const bool ok = pos >= 0 && pos < L;
-      const int64_t row = ok ? pos : 0;
-      cp_async16(sb + SM_K + u * (NK * 16) + r * 16, kb + row * p.sk.l + u * 8, ok);
-      cp_async16(sb + SM_V + u * (NK * 16) + r * 16, vb + row * p.sv.l + u * 8, ok);
+    {
+      int r = tid / upr, u = tid - r * upr;
+      const int total = (NK * upr) / NT;  // NK is a multiple of 32, so NK * upr is a multiple of 128
+      for (int n = 0; n < total; ++n) {
+        const int pos = k0 + r;
+        const bool ok = pos >= 0 && pos < L;
+        const uint32_t off = u * (NK * 16) + r * 16;
+        cp_async16(sb + SM_K + off, ok ? kb + (int64_t)pos * p.sk.l + u * 8 : kb, ok);
+        cp_async16(sb + SM_V + off, ok ? vb + (int64_t)pos * p.sv.l + u * 8 : vb, ok);
+        r += dq; u += dr;
+        if (u >= upr) { u -= upr; ++r; }
+      }
     }
   }
   cp_async_commit();
+  SWA_TR(0);  // set-up + load issue
+  // TMEM is allocated only now: when more CTAs are resident than TMEM can serve, the extra
+  // CTA blocks here with its loads already in flight.
+  __syncwarp();
+  if (warp == 0) tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
+  SWA_TR(10);  // TMEM allocation
   cp_async_wait_all();
   fence_proxy_async();
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
+  SWA_TR(1);  // load wait
   const uint32_t tmem = *tmem_slot;
   const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
   const uint32_t TM_S = 0, TM_O = (uint32_t)NK;
@@ -110,39 +137,54 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const Params p) {
   __syncwarp();
 
   // ---- softmax of row t over the band; this warp's rows only need W + 32 key columns ----
-  const int t = tid;                       // query row == TMEM lane
   const int c_lo = warp * 32;              // first key column any row of this warp can see
   const int npieces = (W + 32) >> 5;
   // valid columns of row t: [t, t + W]  (column c holds key position k0 + c = t0 + c - W)
-  const int v_lo = max(t, -k0), v_hi = t + W;
+  // Relative to this warp's first column c_lo = 32*warp, row `lane` sees columns [lane, lane + W]:
+  // in the first 32-column piece that is i >= lane, in the last one i <= lane, and everything in
+  // between is visible.  Only the first tile of a sequence also has keys before position 0.
+  const int first_col = -k0 - c_lo;  // columns below this (relative) are before the sequence start
   mbar_wait_bounded(bar_s, 0, abort_flag, p.status, 16u);
   fence_after_sync();
+  SWA_TR(2);  // S MMA
+  // Visibility of the 32 columns of piece pc for this row as a bit mask (bit i = column i),
+  // so the inner loops are branch-free selects.
+  auto piece_mask = [&](int pc) -> uint32_t {
+    int lo = (pc == 0) ? lane : 0;
+    const int hi = (pc == npieces - 1) ? lane : 31;
+    lo = max(lo, first_col - 32 * pc);
+    if (lo > hi) return 0u;
+    return (0xFFFFFFFFu << lo) & (0xFFFFFFFFu >> (31 - hi));
+  };
   float m = -INFINITY;
   for (int pc = 0; pc < npieces; ++pc) {
     uint32_t r[32];
+    SWA_TR(3);
     tmem_ld32(tlane + TM_S + c_lo + 32 * pc, r);
     tmem_ld_wait();
+    SWA_TR(9);  // TMEM load round trips of the max pass
+    const uint32_t mask = piece_mask(pc);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int c = c_lo + 32 * pc + i;
-      if (c >= v_lo && c <= v_hi) m = fmaxf(m, __uint_as_float(r[i]));
-    }
+    for (int i = 0; i < 32; ++i) m = fmaxf(m, (mask & (1u << i)) ? __uint_as_float(r[i]) : -INFINITY);
   }
+  SWA_TR(3);  // max pass
   const float msc = m * p.scale_log2e;
   float sum = 0.f;
   for (int pc = 0; pc < npieces; ++pc) {
     uint32_t r[32];
     tmem_ld32(tlane + TM_S + c_lo + 32 * pc, r);
     tmem_ld_wait();
+    const uint32_t mask = piece_mask(pc);
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       float e[2];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const int c = c_lo + 32 * pc + 2 * i + j;
-        const float val = exp2f(fmaf(__uint_as_float(r[2 * i + j]), p.scale_log2e, -msc));
-        e[j] = (c >= v_lo && c <= v_hi) ? val : 0.f;
+        const int ii = 2 * i + j;
+        float val;
+        asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(val) : "f"(fmaf(__uint_as_float(r[ii]), p.scale_log2e, -msc)));
+        e[j] = (mask & (1u << ii)) ? val : 0.f;
       }
       pk[i] = pack_bf16(e[0], e[1]);
       // the normaliser sums what the MMA will see: the bf16-rounded probabilities
@@ -150,6 +192,7 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const Params p) {
     }
     tmem_st16(tlane + TM_S + ((c_lo + 32 * pc) >> 1), pk);
   }
+  SWA_TR(4);  // exp pass
   // zero the P columns of keys this warp's rows cannot see
   {
     uint32_t z[16];
@@ -162,6 +205,7 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const Params p) {
   tmem_st_wait();
   fence_before_sync();
   __syncthreads();
+  SWA_TR(5);  // zero fill + barrier
 
   // ---- O = P V ----
   if (tid == 0) {
@@ -176,31 +220,59 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const Params p) {
   // ---- epilogue ----
   mbar_wait_bounded(bar_o, 0, abort_flag, p.status, 32u);
   fence_after_sync();
+  SWA_TR(6);  // PV MMA
   {
+    // Each thread parks its normalised row in this warp's 32-row staging tile (the K operand
+    // buffer, free since S was computed); the warp then copies the tile out with every store
+    // instruction covering whole 128-byte lines.
     const float inv = 1.0f / sum;
-    const bool valid = t0 + t < L;
-    __nv_bfloat16* orow = p.o + b * p.so.b + (int64_t)(t0 + t) * p.so.l + h * p.so.h;
+    const int yrow_bytes = hd * 2 + 16;  // the pad keeps the per-row 16-byte stores conflict free
+    uint8_t* ytile = smem + SM_K + (warp * 32) * yrow_bytes;
+    uint8_t* yrow_s = ytile + lane * yrow_bytes;
     for (int i = 0; i < (hd >> 4); ++i) {
       uint32_t r[16];
       tmem_ld16(tlane + TM_O + 16 * i, r);
       tmem_ld_wait();
-      if (valid) {
-        uint4 lo, hi;
-        lo.x = pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
-        lo.y = pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
-        lo.z = pack_bf16(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
-        lo.w = pack_bf16(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
-        hi.x = pack_bf16(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
-        hi.y = pack_bf16(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
-        hi.z = pack_bf16(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
-        hi.w = pack_bf16(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
-        *reinterpret_cast<uint4*>(orow + 16 * i) = lo;
-        *reinterpret_cast<uint4*>(orow + 16 * i + 8) = hi;
+      uint4 lo, hi;
+      lo.x = pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+      lo.y = pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+      lo.z = pack_bf16(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+      lo.w = pack_bf16(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+      hi.x = pack_bf16(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+      hi.y = pack_bf16(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+      hi.z = pack_bf16(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+      hi.w = pack_bf16(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+      *reinterpret_cast<uint4*>(yrow_s + 32 * i) = lo;
+      *reinterpret_cast<uint4*>(yrow_s + 32 * i + 16) = hi;
+    }
+    __syncwarp();
+    SWA_TR(7);  // O -> staging
+    const int tok_w = t0 + warp * 32;
+    __nv_bfloat16* otok = p.o + b * p.so.b + (int64_t)tok_w * p.so.l + h * p.so.h;
+    const int dq = 32 / upr, dr = 32 % upr;
+    int r = lane / upr, cc = lane - r * upr;
+    for (int n0 = 0; n0 < upr; n0 += 4) {
+      uint4 val[4];
+      int rr[4], cq[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        rr[u] = r; cq[u] = cc;
+        if (n0 + u < upr) val[u] = *reinterpret_cast<const uint4*>(ytile + r * yrow_bytes + cc * 16);
+        r += dq; cc += dr;
+        if (cc >= upr) { cc -= upr; ++r; }
       }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (n0 + u < upr && tok_w + rr[u] < L)
+          *reinterpret_cast<uint4*>(otok + (int64_t)rr[u] * p.so.l + cq[u] * 8) = val[u];
     }
   }
+  SWA_TR(8);  // copy-out
   fence_before_sync();
   __syncthreads();
+#ifdef BASED_TC_TRACE
+  if (tid == 0) atomicAdd(&g_swa_trace[15], 1ull);
+#endif
   if (warp == 0) {
     fence_after_sync();
     tmem_dealloc(tmem, p.tmem_cols);
@@ -208,6 +280,17 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const Params p) {
 }
 
 }  // namespace
+
+#ifdef BASED_TC_TRACE
+extern "C" int based_swa_trace_read(unsigned long long* out, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_swa_trace, sizeof(unsigned long long) * 16);
+  if (e == cudaSuccess && reset) {
+    unsigned long long z[16] = {0};
+    e = cudaMemcpyToSymbol(g_swa_trace, z, sizeof(z));
+  }
+  return (int)e;
+}
+#endif
 
 int read_tc_status_swa(unsigned int* out, int reset) {
   unsigned int v = 0;

@@ -210,3 +210,116 @@ def test_swa_decode_equals_prefill(ops):
         t = L + s
         out = ops.swa_decode(qkv[:, t:t + 1, 0], qkv[:, t:t + 1, 1], qkv[:, t:t + 1, 2], cache, t, w)
         assert rel_err(out[:, 0].float().cpu(), full[:, t].float().cpu()) < 2e-2
+
+
+# ------------------------------------------------------------------ full-size, size-independent properties
+def test_prefill_full_size_properties(ops):
+    """BASELINE config-3 shape (B=8, H=16, L=8192, dv=64, bf16), too large for the quadratic oracle
+    as a whole: (1) sampled (batch, head) slices against the chunked fp64 oracle, (2) linearity in v
+    (the normaliser does not depend on v), (3) recurrent == parallel for the last positions,
+    (4) tensor-core and CUDA-core kernels agree."""
+    B, H, L, dv = 8, 16, 8192, 64
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = (torch.randn(B, H, L, 16, device="cuda", generator=g) / 4).bfloat16()
+    k = (torch.randn(B, H, L, 16, device="cuda", generator=g) / 4).bfloat16()
+    v1 = (torch.randn(B, H, L, dv, device="cuda", generator=g) / 4).bfloat16()
+    v2 = (torch.randn(B, H, L, dv, device="cuda", generator=g) / 4).bfloat16()
+    y1, kv1, ks1 = ops.linattn_prefill(q, k, v1, state_dtype=torch.float32)
+    y2, kv2, ks2 = ops.linattn_prefill(q, k, v2, state_dtype=torch.float32)
+    v12 = (v1.float() + v2.float()).bfloat16()
+    y12, kv12, _ = ops.linattn_prefill(q, k, v12, state_dtype=torch.float32)
+    from based_b200 import _capi
+    assert _capi.read_status() == 0
+    # (1) sampled slices vs the oracle
+    for (b, h) in [(0, 0), (3, 7), (7, 15)]:
+        yr, kvr, ksr = O.linattn_chunked(q[b:b + 1, h:h + 1].cpu().double(), k[b:b + 1, h:h + 1].cpu().double(),
+                                         v1[b:b + 1, h:h + 1].cpu().double(), chunk=512)
+        assert rel_err(y1[b:b + 1, h:h + 1].cpu(), yr) < 2e-2
+        assert rel_err(kv1[b:b + 1, h:h + 1].cpu(), kvr) < 2e-2
+        assert rel_err(ks1[b:b + 1, h:h + 1].cpu(), ksr) < 2e-2
+    # (2) linearity in v (bf16 rounding of the inputs/outputs bounds the slack)
+    assert rel_err(y12.float(), y1.float() + y2.float()) < 2e-2
+    assert rel_err(kv12, kv1 + kv2) < 2e-2
+    assert torch.equal(ks1, ks2)  # k_state does not depend on v: bit-identical
+    # (3) one decode step from the state of the first L-1 tokens reproduces the last prefill row
+    _, kvp, ksp = ops.linattn_prefill(q[:, :, :L - 1], k[:, :, :L - 1], v1[:, :, :L - 1], state_dtype=torch.float32)
+    yd = ops.linattn_decode(q[:, :, L - 1:], k[:, :, L - 1:], v1[:, :, L - 1:], kvp, ksp).view(B, H, dv)
+    assert rel_err(yd.float(), y1[:, :, L - 1].float()) < 2e-2
+    assert rel_err(kvp, kv1) < 2e-2
+    # (4) the two prefill kernels agree on a slice
+    ys, kvs, _ = ops.linattn_prefill(q[:1, :2], k[:1, :2], v1[:1, :2], impl="simt", state_dtype=torch.float32)
+    assert rel_err(y1[:1, :2].float(), ys.float()) < 2e-2 and rel_err(kv1[:1, :2], kvs) < 2e-2
+
+
+def test_decode_full_size_properties(ops):
+    """BASELINE config-2 shape (B=256, H=16, fp32 state): sampled units against the oracle after
+    several in-place steps, and determinism (two runs from the same state are bit-identical)."""
+    B, H, dv = 256, 16, 64
+    g = torch.Generator(device="cuda").manual_seed(1)
+    kv0 = 0.02 * torch.randn(B, H, 1, dv, 273, device="cuda", generator=g)
+    ks0 = 1.0 + 0.02 * torch.randn(B, H, 1, 1, 273, device="cuda", generator=g)
+    steps = 5
+    qs = (torch.randn(steps, B, H, 1, 16, device="cuda", generator=g) / 4).bfloat16()
+    kk = (torch.randn(steps, B, H, 1, 16, device="cuda", generator=g) / 4).bfloat16()
+    vs = torch.randn(steps, B, H, 1, dv, device="cuda", generator=g).bfloat16()
+    outs = []
+    for run in range(2):
+        kv, ks = kv0.clone(), ks0.clone()
+        ys = [ops.linattn_decode(qs[s], kk[s], vs[s], kv, ks).clone() for s in range(steps)]
+        outs.append((torch.stack(ys), kv, ks))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    idx = [(0, 0), (100, 5), (255, 15)]
+    for (b, h) in idx:
+        kvr, ksr = kv0[b:b + 1, h:h + 1].cpu().double(), ks0[b:b + 1, h:h + 1].cpu().double()
+        for s in range(steps):
+            yr = O.linattn_recurrent_step(kvr, ksr, qs[s, b:b + 1, h:h + 1].cpu().double(),
+                                          kk[s, b:b + 1, h:h + 1].cpu().double(), vs[s, b:b + 1, h:h + 1].cpu().double())
+            got = outs[0][0][s, b, 0, h * dv:(h + 1) * dv].float().cpu()
+            assert rel_err(got, yr.flatten()) < 2e-2
+        assert rel_err(outs[0][1][b:b + 1, h:h + 1].cpu(), kvr) < 1e-4
+
+
+def test_swa_full_size_properties(ops):
+    """Config-3 sliding-window shape (B=8, L=8192, H=16, hd=64, w=64): sampled heads against the
+    oracle; shift invariance (attention over a window depends only on relative positions, so
+    dropping the first 128 tokens leaves every row past 128 + w unchanged, bit for bit)."""
+    B, L, H, hd, w = 8, 8192, 16, 64, 64
+    g = torch.Generator(device="cuda").manual_seed(2)
+    qkv = (torch.randn(B, L, 3, H, hd, device="cuda", generator=g) / 4).bfloat16()
+    out = ops.swa_prefill(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], w)
+    for (b, h) in [(0, 0), (5, 9)]:
+        sl = qkv[b:b + 1, :1024, :, h:h + 1].cpu().double()
+        ref = O.swa_prefill(sl[:, :, 0], sl[:, :, 1], sl[:, :, 2], w)
+        assert rel_err(out[b:b + 1, :1024, h:h + 1].cpu(), ref) < 2e-2
+    out_shift = ops.swa_prefill(qkv[:, 128:, 0], qkv[:, 128:, 1], qkv[:, 128:, 2], w)
+    assert torch.equal(out_shift[:, w:], out[:, 128 + w:])
+
+
+def test_decode_step_is_cuda_graph_capturable(ops):
+    """The reference replays a captured decode step (based/generation.py:689-739): the kernels must
+    launch on the capturing stream, allocate nothing and update the state in place."""
+    B, H, dv = 4, 4, 64
+    g = torch.Generator(device="cuda").manual_seed(3)
+    kv = 0.02 * torch.randn(B, H, 1, dv, 273, device="cuda", generator=g)
+    ks = 1.0 + 0.02 * torch.randn(B, H, 1, 1, 273, device="cuda", generator=g)
+    kv_ref, ks_ref = kv.clone(), ks.clone()
+    q = (torch.randn(B, H, 1, 16, device="cuda", generator=g) / 4).bfloat16()
+    k = (torch.randn(B, H, 1, 16, device="cuda", generator=g) / 4).bfloat16()
+    v = torch.randn(B, H, 1, dv, device="cuda", generator=g).bfloat16()
+    y = torch.empty(B, 1, H * dv, dtype=torch.bfloat16, device="cuda")
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        ops.linattn_decode(q, k, v, kv, ks, out=y)  # warm-up on the side stream
+    torch.cuda.current_stream().wait_stream(s)
+    kv.copy_(kv_ref); ks.copy_(ks_ref)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.linattn_decode(q, k, v, kv, ks, out=y)
+    kv.copy_(kv_ref); ks.copy_(ks_ref)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        y_eager = ops.linattn_decode(q, k, v, kv_ref, ks_ref)
+    assert torch.equal(y, y_eager) and torch.equal(kv, kv_ref) and torch.equal(ks, ks_ref)
