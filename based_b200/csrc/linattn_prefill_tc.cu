@@ -31,7 +31,7 @@ __device__ unsigned int g_tc_status = 0;  // ORed with a code when a bounded wai
 #ifdef BASED_TC_TRACE
 // Debug build only: per-role cycle counters of CTA 0 (cycles spent in each barrier wait, total
 // cycles), read back with based_tc_trace_read().
-__device__ unsigned long long g_tc_trace[4][32];
+__device__ unsigned long long g_tc_trace[5][32];
 #endif
 
 namespace {
@@ -40,8 +40,10 @@ using namespace tc;
 
 constexpr int C = 128;     // tokens per chunk
 constexpr int DR = 160;    // packed + padded feature count
-constexpr int NT = 384;    // threads per CTA: 4 expansion warps, 4 polynomial/epilogue warps, MMA warp, 3 load warps
-constexpr int W_MMA = 8, W_LOAD = 9;
+// threads per CTA: 4 expansion warps (0-3), 4 polynomial / state-drain warps (4-7), 4 output warps (8-11),
+// the MMA warp (12), 3 load warps (13-15).  A compute warp w reaches TMEM lanes 32*(w%4)..+31.
+constexpr int NT = 512;
+constexpr int W_OUT = 8, W_MMA = 12, W_LOAD = 13;
 
 // Shared memory map (bytes).  One stage = Q [128 tok x 16] K-major (4096) + K (4096) +
 // V' MN-major [NV/8 groups of 8 columns][128 tok][16 B].  The state-update MMA reads V'^T as an
@@ -194,8 +196,12 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + lay.bar + 8 * B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + lay.bar + 8 * B_COUNT + 4);
 #ifdef BASED_TC_TRACE
+  // phase slots are only ever indexed by compile-time constants, so they stay in registers;
+  // the time spent in barrier waits is a single sum (slot 0)
   unsigned long long tr_wait[32];
+#pragma unroll
   for (int i = 0; i < 32; ++i) tr_wait[i] = 0;
+  unsigned long long tr_wsum = 0;
   long long tr_t = 0;
   long long tr_t2 = 0;
 #define TR_BEGIN() tr_t = clock64()
@@ -204,9 +210,12 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
 #define TR2_END(slot) tr_wait[slot] += clock64() - tr_t2
   const long long tr_start = clock64();
   auto wait = [&](int i, uint32_t parity, unsigned int code) {
+#ifdef BASED_EXPERIMENT_FREERUN
+    return;  // timing experiment: every role runs at its own pace, results are garbage
+#endif
     const long long t0 = clock64();
     mbar_wait_bounded(bar(i), parity & 1u, abort_flag, p.status, code);
-    tr_wait[i] += clock64() - t0;
+    tr_wsum += clock64() - t0;
   };
 #else
 #define TR_BEGIN()
@@ -308,9 +317,12 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
 #ifdef BASED_TC_TRACE
       auto mwait = [&](int i, uint32_t parity, unsigned int code) {
         if (mma_only) return;
+#ifdef BASED_EXPERIMENT_FREERUN
+        return;
+#endif
         const long long t0 = clock64();
         mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
-        tr_wait[i] += clock64() - t0;
+        tr_wsum += clock64() - t0;
       };
 #else
       auto mwait = [&](int i, uint32_t parity, unsigned int code) {
@@ -343,34 +355,41 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         mwait(B_P_READY, c, 0x201u);
         if (c > 0) mwait(B_O_FREE, c - 1, 0x202u);
         fence_after_sync();
+        TR_BEGIN();
         if (BASED_EXPERIMENT_MMA_MASK & 1) {
 #pragma unroll
           for (int j = 0; j < C / 16; ++j)
             mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
         }
+        TR_END(26);
         // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
         if (c + 1 < nchunks) {
           mwait(B_FULL + st1, st1_par, 0x203u);
           fence_after_sync();
+          TR_BEGIN();
           if (BASED_EXPERIMENT_MMA_MASK & 2) {
             const uint32_t so = st1 * stage_units;
             mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
           }
           mma_commit(bar(B_S_DONE));
+          TR_END(27);
         }
         // O(c) += phi'(Q_c) State(c-1)
         mwait(B_PQ_READY, c, 0x204u);
         if (c > 0) mwait(B_STB_READY, c - 1, 0x205u);
         fence_after_sync();
+        TR_BEGIN();
         if (c > 0 && (BASED_EXPERIMENT_MMA_MASK & 4)) {
 #pragma unroll
           for (int j = 0; j < DR / 16; ++j)
             mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb + 256 * j, idesc_o_st, 1);
         }
         mma_commit(bar(B_O_DONE));
+        TR_END(28);
         // State^T += V'(c)^T phi'(K_c)
         mwait(B_PK_READY, c, 0x206u);
         fence_after_sync();
+        TR_BEGIN();
         {
           const uint64_t d_pk_c = d_pk + pkb * (40960 >> 4);
 #pragma unroll
@@ -380,13 +399,19 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         mma_commit(bar(B_ST_DONE));
         mma_commit(bar(B_EMPTY + st));
         mma_commit(bar(B_PK_FREE + pkb));
+        TR_END(29);
         st = st1;
         if (++st1 == NS) { st1 = 0; st1_par ^= 1u; }
         if (++pkb == NPK) pkb = 0;
       }
+#ifdef BASED_EXPERIMENT_FREERUN
+      mbar_wait_bounded<false>(bar(B_ST_DONE), (nchunks - 1) & 1u, abort_flag, p.status, 0x2FFu);
+#endif
       if (mma_only) mbar_wait_bounded<false>(bar(B_ST_DONE), (nchunks - 1) & 1u, abort_flag, p.status, 0x2FFu);
 #ifdef BASED_TC_TRACE
       if (bh == 0) {
+        tr_wait[0] = tr_wsum;
+#pragma unroll
         for (int i = 0; i < 32; ++i) g_tc_trace[2][i] = tr_wait[i];
         g_tc_trace[2][31] = clock64() - tr_start;
       }
@@ -442,7 +467,11 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
         constexpr int g = decltype(G)::value;
         if constexpr (g == 0) w0 &= one;
+#ifndef BASED_EXPERIMENT_SKIP_PHIK_STS
         *reinterpret_cast<uint4*>(dst + g * 2048) = make_uint4(w0, w1, w2, w3);
+#else
+        if (w0 == 0x12345678u && w1 == w2 && w3 == 77u) *reinterpret_cast<uint4*>(dst + g * 2048) = make_uint4(w0, w1, w2, w3);
+#endif
       });
       TR_END(19);
       TR_BEGIN();
@@ -451,45 +480,9 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       TR_END(20);
       if (lane == 0) mbar_arrive(bar(B_PK_READY));
     }
-  } else {
-    // ================================================================ polynomial / epilogue / state-drain warps
+  } else if (warp >= W_OUT && warp < W_MMA) {
+    // ================================================================ output warps: O -> y
     __nv_bfloat16* yb = p.y + b * p.sy.b + h * p.sy.h;
-    // P(c) = causal(1 + s/4 + s^2/32), evaluated in bf16x2 (two FMAs per pair), in place over S.
-    // Column pieces right of this warp's diagonal block are all masked: zeros, no load; only the
-    // diagonal piece needs the per-element mask.
-    auto make_p = [&](int c) {
-      wait(B_S_DONE, c, 0x400u);
-      fence_after_sync();
-      TR_BEGIN();
-      constexpr uint32_t k1 = 0x3F803F80u, kq = 0x3E803E80u, k32 = 0x3D003D00u;  // (1,1) (1/4,1/4) (1/32,1/32)
-#pragma unroll 1
-      for (int piece = 0; piece <= qd; ++piece) {
-        uint32_t sreg[32], pk[16];
-        tmem_ld32(tlane + TM_S + piece * 32, sreg);
-        tmem_ld_wait();
-        const int rel = t - piece * 32;  // columns 0..rel of this piece are visible (rel >= 31 left of the diagonal)
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
-          const uint32_t pv = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
-          const uint32_t mask = (2 * i + 1 <= rel) ? 0xFFFFFFFFu : ((2 * i <= rel) ? 0x0000FFFFu : 0u);
-          pk[i] = pv & mask;
-        }
-        tmem_st16(tlane + TM_S + piece * 16, pk);
-      }
-      {
-        uint32_t z[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) z[i] = 0;
-#pragma unroll 1
-        for (int piece = qd + 1; piece < 4; ++piece) tmem_st16(tlane + TM_S + piece * 16, z);
-      }
-      tmem_st_wait();
-      fence_before_sync();
-      __syncwarp();
-      TR_END(21);
-      if (lane == 0) mbar_arrive(bar(B_P_READY));
-    };
     auto cvt16 = [&](const uint32_t (&r)[16], float sc, uint4& lo, uint4& hi) {
       lo.x = pack_bf16(__uint_as_float(r[0]) * sc, __uint_as_float(r[1]) * sc);
       lo.y = pack_bf16(__uint_as_float(r[2]) * sc, __uint_as_float(r[3]) * sc);
@@ -500,10 +493,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       hi.z = pack_bf16(__uint_as_float(r[12]) * sc, __uint_as_float(r[13]) * sc);
       hi.w = pack_bf16(__uint_as_float(r[14]) * sc, __uint_as_float(r[15]) * sc);
     };
-    make_p(0);
     for (int c = 0; c < nchunks; ++c) {
-      const bool last = c + 1 == nchunks;
-      if (!last) make_p(c + 1);
       // ---- epilogue: y = O[:, :dv] / (O[:, dv] + eps), 32 columns per round trip ----
       wait(B_O_DONE, c, 0x401u);
       fence_after_sync();
@@ -570,6 +560,59 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         __syncwarp();  // the tile is rewritten by other lanes in the next chunk
       }
       TR_END(22);
+    }
+  } else {
+    // ================================================================ polynomial / state-drain warps
+    // P(c) = causal(1 + s/4 + s^2/32), evaluated in bf16x2 (two FMAs per pair), in place over S.
+    // Column pieces right of this warp's diagonal block are all masked: zeros, no load; only the
+    // diagonal piece needs the per-element mask.
+    auto make_p = [&](int c) {
+      wait(B_S_DONE, c, 0x400u);
+      fence_after_sync();
+      TR_BEGIN();
+      constexpr uint32_t k1 = 0x3F803F80u, kq = 0x3E803E80u, k32 = 0x3D003D00u;  // (1,1) (1/4,1/4) (1/32,1/32)
+#pragma unroll 1
+      for (int piece = 0; piece <= qd; ++piece) {
+        uint32_t sreg[32], pk[16];
+        tmem_ld32(tlane + TM_S + piece * 32, sreg);
+        tmem_ld_wait();
+        const int rel = t - piece * 32;  // columns 0..rel of this piece are visible (rel >= 31 left of the diagonal)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+          const uint32_t pv = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
+          const uint32_t mask = (2 * i + 1 <= rel) ? 0xFFFFFFFFu : ((2 * i <= rel) ? 0x0000FFFFu : 0u);
+          pk[i] = pv & mask;
+        }
+        tmem_st16(tlane + TM_S + piece * 16, pk);
+      }
+      {
+        uint32_t z[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) z[i] = 0;
+#pragma unroll 1
+        for (int piece = qd + 1; piece < 4; ++piece) tmem_st16(tlane + TM_S + piece * 16, z);
+      }
+      tmem_st_wait();
+      fence_before_sync();
+      __syncwarp();
+      TR_END(21);
+      if (lane == 0) mbar_arrive(bar(B_P_READY));
+    };
+    auto cvt16 = [&](const uint32_t (&r)[16], float sc, uint4& lo, uint4& hi) {
+      lo.x = pack_bf16(__uint_as_float(r[0]) * sc, __uint_as_float(r[1]) * sc);
+      lo.y = pack_bf16(__uint_as_float(r[2]) * sc, __uint_as_float(r[3]) * sc);
+      lo.z = pack_bf16(__uint_as_float(r[4]) * sc, __uint_as_float(r[5]) * sc);
+      lo.w = pack_bf16(__uint_as_float(r[6]) * sc, __uint_as_float(r[7]) * sc);
+      hi.x = pack_bf16(__uint_as_float(r[8]) * sc, __uint_as_float(r[9]) * sc);
+      hi.y = pack_bf16(__uint_as_float(r[10]) * sc, __uint_as_float(r[11]) * sc);
+      hi.z = pack_bf16(__uint_as_float(r[12]) * sc, __uint_as_float(r[13]) * sc);
+      hi.w = pack_bf16(__uint_as_float(r[14]) * sc, __uint_as_float(r[15]) * sc);
+    };
+    make_p(0);
+    for (int c = 0; c < nchunks; ++c) {
+      const bool last = c + 1 == nchunks;
+      if (!last) make_p(c + 1);
       // ---- state: fp32 TMEM -> bf16 smem operand for the next chunk, or fp32 staging at the end ----
       wait(B_ST_DONE, c, 0x402u);
       fence_after_sync();
@@ -586,7 +629,11 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
           uint4 a0, a1, b0, b1;
           cvt16(r0, 1.0f, a0, a1);
           cvt16(r1, 1.0f, b0, b1);
+#ifdef BASED_EXPERIMENT_SKIP_STB_STS
+          if (t < NV && a0.x == 0x12345678u && a1.y == 77u) {
+#else
           if (t < NV) {  // rows >= NV of the B operand are never read (N = NV)
+#endif
             uint8_t* dst = smem + lay.stb + (4 * i) * 2048 + t * 16;
             *reinterpret_cast<uint4*>(dst) = a0;
             *reinterpret_cast<uint4*>(dst + 2048) = a1;
@@ -620,8 +667,10 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   }
 
 #ifdef BASED_TC_TRACE
-  if (bh == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == W_LOAD)) {
-    const int role = warp == 0 ? 0 : warp == 4 ? 1 : 3;
+  if (bh == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == W_LOAD || warp == W_OUT)) {
+    const int role = warp == 0 ? 0 : warp == 4 ? 1 : warp == W_OUT ? 4 : 3;
+    tr_wait[0] = tr_wsum;
+#pragma unroll
     for (int i = 0; i < 32; ++i) g_tc_trace[role][i] = tr_wait[i];
     g_tc_trace[role][31] = clock64() - tr_start;
   }
@@ -660,7 +709,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
 
 #ifdef BASED_TC_TRACE
 extern "C" int based_tc_trace_read(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 4 * 32);
+  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 5 * 32);
 }
 #endif
 

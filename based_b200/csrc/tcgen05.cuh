@@ -131,14 +131,17 @@ __device__ __forceinline__ void mbar_arrive(uint32_t saddr) {
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}\n" ::"r"(saddr) : "memory");
 }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t saddr, uint32_t parity) {
+// One try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes
+// or about `hint_ns` have passed, so a waiting warp does not spend issue slots or shared-memory
+// bandwidth on polling.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t saddr, uint32_t parity, uint32_t hint_ns = 20000u) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}\n"
       : "=r"(ok)
-      : "r"(saddr), "r"(parity)
+      : "r"(saddr), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }

@@ -116,9 +116,17 @@ def cpu_decode_baseline(B, steps, warmup, seed=0):
     return B * steps / dt, dt
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU legs are meant to use every host core."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(1, n))
+    return n
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
+    use_all_host_threads()
     Bs = 32
     tput, dt = cpu_decode_baseline(Bs, args.steps, args.warmup)
     cores = torch.get_num_threads()
@@ -305,6 +313,7 @@ def main():
             line["prefill"] = lin
             line["swa"] = swa
         if world == 1 and not args.no_cpu:
+            use_all_host_threads()
             tput, dt = cpu_decode_baseline(B_DEC, 20, 2)
             line["cpu_baseline"] = {"value": tput, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": "20 full-batch recurrent steps (B=256,H=16) of the CPU restatement of "
