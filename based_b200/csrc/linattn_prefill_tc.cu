@@ -374,32 +374,29 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
           mma_commit(bar(B_S_DONE));
           TR_END(27);
         }
-        // O(c) += phi'(Q_c) State(c-1)
+        // O(c) += phi'(Q_c) State(c-1) and State^T += V'(c)^T phi'(K_c), issued alternately: the two
+        // accumulation chains are independent, so one fills the other's latency gaps.  The drain that
+        // rewrites the bf16 state waits for the commit below, i.e. for the readout to be complete.
         mwait(B_PQ_READY, c, 0x204u);
         if (c > 0) mwait(B_STB_READY, c - 1, 0x205u);
-        fence_after_sync();
-        TR_BEGIN();
-        if (c > 0 && (BASED_EXPERIMENT_MMA_MASK & 4)) {
-#pragma unroll
-          for (int j = 0; j < DR / 16; ++j)
-            mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb + 256 * j, idesc_o_st, 1);
-        }
-        mma_commit(bar(B_O_DONE));
-        TR_END(28);
-        // State^T += V'(c)^T phi'(K_c)
         mwait(B_PK_READY, c, 0x206u);
         fence_after_sync();
         TR_BEGIN();
         {
           const uint64_t d_pk_c = d_pk + pkb * (40960 >> 4);
 #pragma unroll
-          for (int j = 0; j < ((BASED_EXPERIMENT_MMA_MASK & 8) ? C / 16 : 0); ++j)
-            mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (c > 0 || j > 0) ? 1u : 0u);
+          for (int j = 0; j < DR / 16; ++j) {
+            if (c > 0 && (BASED_EXPERIMENT_MMA_MASK & 4))
+              mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb + 256 * j, idesc_o_st, 1);
+            if (j < C / 16 && (BASED_EXPERIMENT_MMA_MASK & 8))
+              mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (c > 0 || j > 0) ? 1u : 0u);
+          }
         }
+        mma_commit(bar(B_O_DONE));
         mma_commit(bar(B_ST_DONE));
         mma_commit(bar(B_EMPTY + st));
         mma_commit(bar(B_PK_FREE + pkb));
-        TR_END(29);
+        TR_END(28);
         st = st1;
         if (++st1 == NS) { st1 = 0; st1_par ^= 1u; }
         if (++pkb == NPK) pkb = 0;

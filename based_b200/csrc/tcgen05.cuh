@@ -153,12 +153,12 @@ template <bool kWarpSync = true>
 __device__ __forceinline__ void mbar_wait_bounded(uint32_t saddr, uint32_t parity, volatile int* abort_flag,
                                                   unsigned int* status, unsigned int code,
                                                   long long max_cycles = 2000000000LL) {
-  bool done = (*abort_flag != 0) || mbar_try_wait(saddr, parity);
-  if (!done) {
+  // fast path: one probe without suspension; the abort flag is only consulted when that fails
+  if (!mbar_try_wait(saddr, parity, 0u)) {
     const long long t0 = clock64();
     while (true) {
-      if (mbar_try_wait(saddr, parity)) break;
       if (*abort_flag) break;
+      if (mbar_try_wait(saddr, parity)) break;
       if (clock64() - t0 > max_cycles) {
         *abort_flag = 1;
         if (status) atomicOr(status, code);
