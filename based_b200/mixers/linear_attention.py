@@ -13,6 +13,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
+from ..sharding import all_reduce_sum_, head_slice
 
 
 class FeatureMap(nn.Module):
@@ -59,6 +60,7 @@ class LinearAttention(nn.Module):
         layer_idx: int = None,
         parallel_implementation: str = "quadratic",
         state_dtype: torch.dtype = None,
+        process_group=None,
         device=None,
         dtype=None,
         **kwargs,
@@ -79,8 +81,17 @@ class LinearAttention(nn.Module):
         self.l_max = l_max
         self.eps = eps
         self.parallel_implementation = parallel_implementation
+        self.head_dim = self.d_model // num_heads if head_dim is None else head_dim
+        # extension (the reference mixer has no tensor parallelism): with a process group this rank owns
+        # num_heads / world heads — its slices of proj_q/k/v (column-parallel) and of out_proj (row-parallel)
+        # and of the recurrent state — and forward() ends with one all-reduce of the output
+        self.process_group = process_group
+        self.num_heads_total = num_heads
+        if process_group is not None:
+            import torch.distributed as dist
+            h0, h1 = head_slice(num_heads, dist.get_rank(process_group), dist.get_world_size(process_group))
+            num_heads = h1 - h0
         self.num_heads = num_heads
-        self.head_dim = self.d_model // self.num_heads if head_dim is None else head_dim
         self.feature_dim = feature_dim
         self.feature_map = feature_map
         # extension: dtype of freshly created prefill states; None = the activations' dtype,
@@ -131,7 +142,7 @@ class LinearAttention(nn.Module):
             kv_state=kv_state, k_state=k_state)
         b, h, l, dv = y.shape
         y = y.permute(0, 2, 1, 3).reshape(b, l, h * dv)  # 'b h l d -> b l (h d)': a view
-        out = self.out_proj(y.to(x.dtype))
+        out = all_reduce_sum_(self.out_proj(y.to(x.dtype)), self.process_group)
         if want_state:
             return out, kv_state, k_state
         return out
@@ -144,7 +155,7 @@ class LinearAttention(nn.Module):
         assert l == 1, f"q.shape is {q.shape} but should be ({b}, {h}, 1, {d})"
         eps = 1e-6 if "fla" in self.parallel_implementation else 1e-12
         y = ops.linattn_decode(q, k, v, kv_state, k_state, eps=eps)
-        return self.out_proj(y)
+        return all_reduce_sum_(self.out_proj(y), self.process_group)
 
     def expanded_size(self):
         return self.feature_dim ** 2 + self.feature_dim + 1

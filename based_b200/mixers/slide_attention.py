@@ -11,6 +11,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
+from ..sharding import all_reduce_sum_, head_slice
 
 
 class RotaryEmbedding(nn.Module):
@@ -68,6 +69,7 @@ class SlidingAttention(nn.Module):
         return_residual=False,
         checkpointing=False,
         window_size=128,
+        process_group=None,
         device=None,
         dtype=None,
     ) -> None:
@@ -88,17 +90,28 @@ class SlidingAttention(nn.Module):
         self.dropout_p = dropout
         # (left, right) window as the reference stores it: the constructor argument is halved
         self.window = (window_size // 2, 0)
-        self.num_heads = num_heads
-        self.num_heads_kv = num_heads
         assert self.embed_dim % num_heads == 0, "embed_dim must be divisible by num_heads"
         self.head_dim = self.embed_dim // num_heads
+        # extension (the reference class takes no process group): head-sharded tensor parallelism,
+        # Wqkv column-parallel, out_proj row-parallel, one all-reduce of the output
+        self.process_group = process_group
+        self.num_heads_total = num_heads
+        if process_group is not None:
+            import torch.distributed as dist
+            h0, h1 = head_slice(num_heads, dist.get_rank(process_group), dist.get_world_size(process_group))
+            num_heads = h1 - h0
+        self.num_heads = num_heads
+        self.num_heads_kv = num_heads
+        self.tp_rank0 = process_group is None or h0 == 0
         self.softmax_scale = softmax_scale
         if self.rotary_emb_dim > 0:
             self.rotary_emb = RotaryEmbedding(self.rotary_emb_dim, base=rotary_emb_base,
                                               scale_base=rotary_emb_scale_base,
                                               interleaved=rotary_emb_interleaved, device=device)
-        self.Wqkv = nn.Linear(embed_dim, 3 * embed_dim, bias=qkv_proj_bias, **factory_kwargs)
-        self.out_proj = nn.Linear(embed_dim, embed_dim, bias=out_proj_bias, **factory_kwargs)
+        local = self.num_heads * self.head_dim
+        self.Wqkv = nn.Linear(embed_dim, 3 * local, bias=qkv_proj_bias, **factory_kwargs)
+        # row-parallel: the bias must be added once, so only the rank owning head 0 keeps it
+        self.out_proj = nn.Linear(local, embed_dim, bias=out_proj_bias and self.tp_rank0, **factory_kwargs)
 
     def allocate_inference_cache(self, batch_size, max_seqlen, dtype=None):
         dtype = self.out_proj.weight.dtype if dtype is None else dtype
@@ -154,6 +167,6 @@ class SlidingAttention(nn.Module):
                 cos, sin = self.rotary_emb._cos_cached, self.rotary_emb._sin_cached
             context = ops.swa_decode(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], cache, lens, w, self.softmax_scale,
                                      rotary_cos=cos, rotary_sin=sin)
-        context = context.to(in_dtype).reshape(batch, seqlen, self.embed_dim)
-        out = self.out_proj(context)
+        context = context.to(in_dtype).reshape(batch, seqlen, self.num_heads * self.head_dim)
+        out = all_reduce_sum_(self.out_proj(context), self.process_group)
         return out if not self.return_residual else (out, x)

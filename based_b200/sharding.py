@@ -1,4 +1,4 @@
-"""Batch x heads sharding across ranks (one process per GPU).
+"""Sharding across ranks (one process per GPU): batch x heads shards, and head-sharded tensor parallelism.
 
 Every (batch, head) pair is independent in all kernels of this path, so N GPUs need no
 data-path collective: each rank takes a contiguous slice of the batch (the unit the full
@@ -33,3 +33,54 @@ def sum_over_ranks(values, device) -> list:
     if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return t.tolist()
+
+
+# --------------------------------------------------------------------------- head-sharded tensor parallelism
+# The reference mixers have no tensor-parallel support (LinearAttention takes no process group,
+# based/models/mixers/linear_attention.py:78-90).  This variant follows the reference's own
+# RowParallelLinear (based/ops/fused_dense.py:205-246): q/k/v projections column-parallel (each rank owns
+# num_heads / world heads and their slice of the recurrent state), out_proj row-parallel, and ONE all-reduce of
+# the [B, L, d_model] output (NCCL over NVLink on GPUs).  Nothing inside the kernels crosses ranks.
+
+def head_slice(num_heads: int, rank: int, world: int) -> Tuple[int, int]:
+    if num_heads % world != 0:
+        raise ValueError(f"num_heads={num_heads} is not divisible by the tensor-parallel size {world}")
+    per = num_heads // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_linear_attention_state_dict(full: dict, num_heads: int, feature_dim: int, head_dim: int,
+                                      rank: int, world: int, prefix: str = "") -> dict:
+    """Slice a full LinearAttention state_dict (reference parameter names) for one tensor-parallel rank."""
+    h0, h1 = head_slice(num_heads, rank, world)
+    out = {}
+    out[prefix + "proj_q.weight"] = full[prefix + "proj_q.weight"][h0 * feature_dim:h1 * feature_dim].clone()
+    out[prefix + "proj_k.weight"] = full[prefix + "proj_k.weight"][h0 * feature_dim:h1 * feature_dim].clone()
+    out[prefix + "proj_v.weight"] = full[prefix + "proj_v.weight"][h0 * head_dim:h1 * head_dim].clone()
+    out[prefix + "out_proj.weight"] = full[prefix + "out_proj.weight"][:, h0 * head_dim:h1 * head_dim].clone()
+    return out
+
+
+def shard_sliding_attention_state_dict(full: dict, num_heads: int, head_dim: int, rank: int, world: int,
+                                       prefix: str = "") -> dict:
+    """Slice a full SlidingAttention state_dict (Wqkv rows are ordered (three, head, dim),
+    based/models/mixers/slide_attention.py:546) for one tensor-parallel rank."""
+    h0, h1 = head_slice(num_heads, rank, world)
+    w = full[prefix + "Wqkv.weight"]
+    d_model = w.shape[1]
+    w3 = w.view(3, num_heads, head_dim, d_model)[:, h0:h1].reshape(3 * (h1 - h0) * head_dim, d_model)
+    out = {prefix + "Wqkv.weight": w3.clone(),
+           prefix + "out_proj.weight": full[prefix + "out_proj.weight"][:, h0 * head_dim:h1 * head_dim].clone()}
+    if prefix + "Wqkv.bias" in full:
+        b = full[prefix + "Wqkv.bias"].view(3, num_heads, head_dim)[:, h0:h1].reshape(-1)
+        out[prefix + "Wqkv.bias"] = b.clone()
+    if prefix + "out_proj.bias" in full and h0 == 0:
+        out[prefix + "out_proj.bias"] = full[prefix + "out_proj.bias"].clone()  # row-parallel: added once, by the rank owning head 0
+    return out
+
+
+def all_reduce_sum_(t: torch.Tensor, group=None) -> torch.Tensor:
+    """In-place sum over the tensor-parallel group (identity for a group of one / no group)."""
+    if group is not None and dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    return t

@@ -63,3 +63,59 @@ def test_shard_range_covers_everything():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         shard_range(4, 2, 2)
+
+
+def _tp_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from based_b200.sharding import all_reduce_sum_, shard_linear_attention_state_dict, shard_sliding_attention_state_dict
+    from conftest import load_golden
+    from oracle import based_oracle as O
+    g = load_golden("linattn_mixer.npz")
+    d_model, H, d, dv, B, L, steps = [int(x) for x in g["meta"]]
+    full = {"proj_q.weight": g["wq"], "proj_k.weight": g["wk"], "proj_v.weight": g["wv"], "out_proj.weight": g["wo"]}
+    sd = shard_linear_attention_state_dict(full, H, d, dv, rank, world)
+    x = g["x"][:, :L]
+    out, kv, ks = O.linattn_mixer_forward(x, sd["proj_q.weight"], sd["proj_k.weight"], sd["proj_v.weight"],
+                                          sd["out_proj.weight"], H // world, d, dv)
+    all_reduce_sum_(out, dist.group.WORLD)
+    err = ((out - g["y_prefill"]).abs().max() / g["y_prefill"].abs().max()).item()
+    h0 = rank * (H // world)
+    st_err = ((kv - g["kv_state_prefill"][:, h0:h0 + H // world]).abs().max()).item()
+    # sliding-window weights: the (three, head, dim) row order of Wqkv
+    torch.manual_seed(0)
+    Hs, hd, D = 4, 8, 32
+    w = torch.randn(3 * D, D); wo = torch.randn(D, D); bo = torch.randn(D)
+    ssd = shard_sliding_attention_state_dict({"Wqkv.weight": w, "out_proj.weight": wo, "out_proj.bias": bo}, Hs, hd, rank, world)
+    xs = torch.randn(2, 5, D)
+    qkv_full = (xs @ w.T).view(2, 5, 3, Hs, hd)
+    qkv_loc = (xs @ ssd["Wqkv.weight"].T).view(2, 5, 3, Hs // world, hd)
+    hs0 = rank * (Hs // world)
+    ok_qkv = torch.allclose(qkv_loc, qkv_full[:, :, :, hs0:hs0 + Hs // world], atol=1e-5)
+    ctx_full = qkv_full[:, :, 2].reshape(2, 5, D)            # any per-head function of qkv; take v
+    ctx_loc = qkv_loc[:, :, 2].reshape(2, 5, -1)
+    o_loc = ctx_loc @ ssd["out_proj.weight"].T + (ssd["out_proj.bias"] if "out_proj.bias" in ssd else 0)
+    all_reduce_sum_(o_loc, dist.group.WORLD)
+    ok_out = torch.allclose(o_loc, ctx_full @ wo.T + bo, atol=1e-4)
+    q.put((rank, err, st_err, ok_qkv, ok_out))
+    dist.destroy_process_group()
+
+
+def test_tensor_parallel_sharding_gloo():
+    """Head-sharded tensor parallelism on CPU ranks: sharded projections + one all-reduce of the
+    output reproduce the unsharded mixer (the reference's own outputs), each rank holding its
+    heads' slice of the recurrent state."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=180) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, st_err, ok_qkv, ok_out in res:
+        assert err < 2e-5 and st_err < 1e-4 and ok_qkv and ok_out
