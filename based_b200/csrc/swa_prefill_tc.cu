@@ -14,10 +14,13 @@
 //   O = P V              (M128, N = head_dim, K = NK)          -> TMEM
 //   out = O / rowsum
 // TMEM lanes are private to the warp that owns the rows, so the S -> P rewrite needs no
-// block-wide barrier.  With window 64 and head_dim 64 a CTA needs 256 TMEM columns and 64 KB
-// of shared memory, so two CTAs share an SM and overlap each other's load / MMA / softmax.
+// block-wide barrier.  Q, K, V tiles arrive by TMA (128-byte swizzle, zero fill outside the
+// sequence) and the output tile leaves by TMA, so no thread spends instructions on copies.
+// With window 64 and head_dim 64 a CTA needs 256 TMEM columns and 65 KB of shared memory: three
+// CTAs fit an SM; TMEM serves two, the third waits in tcgen05.alloc with its loads in flight.
 #include "common.cuh"
 #include "tcgen05.cuh"
+#include "tma.cuh"
 
 namespace based {
 
@@ -39,98 +42,83 @@ constexpr int TQ = 128;  // queries per tile
 constexpr int NT = 128;  // threads per CTA
 
 struct Params {
-  const __nv_bfloat16 *q, *k, *v;
-  __nv_bfloat16* o;
+  CUtensorMap mq, mk, mv, mo;  // [B][H][L][hd] views, box = (<= 64 columns) x (rows), 128-byte swizzle
   int L, H, hd, W, tiles_per_seq, tmem_cols;
-  Strides3 sq, sk, sv, so;
   float scale_log2e;
   unsigned int* status;
 };
 
-__global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const Params p) {
-  extern __shared__ __align__(1024) uint8_t smem[];
+__global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constant__ Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  // the swizzled tiles need a 1024-byte aligned base
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sb = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int hd = p.hd, W = p.W, NK = TQ + W, L = p.L;
+  const int hd = p.hd, W = p.W, NK = TQ + W;
   int tile = blockIdx.x;
   const int ti = tile % p.tiles_per_seq; tile /= p.tiles_per_seq;
   const int h = tile % p.H, b = tile / p.H;
   const int t0 = ti * TQ;          // first query of the tile
   const int k0 = t0 - W;           // position of key column 0 (may be negative)
 
-  // shared memory: Q K-major [hd/8 units][128 rows][16 B]; K K-major [hd/8][NK][16 B];
-  // V MN-major [hd/8 groups][NK keys][16 B]
-  const uint32_t q_bytes = (uint32_t)hd * 256, kv_bytes = (uint32_t)hd * NK * 2;
-  const uint32_t SM_Q = 0, SM_K = q_bytes, SM_V = q_bytes + kv_bytes, SM_BAR = q_bytes + 2 * kv_bytes;
-  const uint32_t bar_s = sb + SM_BAR, bar_o = sb + SM_BAR + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_BAR + 20);
+  // shared memory: per 64-column atom a of the head dimension, a 128-byte-swizzled tile with
+  // 128-byte rows: Q[a] 128 rows, K[a] and V[a] NK rows.  The output tile reuses Q's space.
+  const int natom = (hd + 63) >> 6;
+  const uint32_t q_atom = TQ * 128, kv_atom = (uint32_t)NK * 128;
+  const uint32_t SM_Q = 0, SM_K = natom * q_atom, SM_V = SM_K + natom * kv_atom, SM_BAR = SM_V + natom * kv_atom;
+  const uint32_t bar_qk = sb + SM_BAR, bar_v = sb + SM_BAR + 8, bar_s = sb + SM_BAR + 16, bar_o = sb + SM_BAR + 24;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_BAR + 36);
 
 #ifdef BASED_TC_TRACE
   long long tr_t = clock64();
 #endif
   if (tid == 0) {
+    mbar_init(bar_qk, 1);
+    mbar_init(bar_v, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     *abort_flag = 0;
     fence_mbar_init();
-  }
-
-  // ---- loads: 16-byte pieces straight into the operand layouts, zero-filled outside [0, L) ----
-  const int upr = hd >> 3;  // 16-byte units per row
-  {
-    // piece i = tid + 128 n  ->  row i / upr, unit i % upr, advanced incrementally
-    const int dq = NT / upr, dr = NT % upr;
-    const __nv_bfloat16* qb = p.q + b * p.sq.b + h * p.sq.h;
-    {
-      int r = tid / upr, u = tid - r * upr;
-      for (int n = 0; n < upr; ++n) {  // 128 rows x upr units / 128 threads
-        const bool ok = t0 + r < L;
-        cp_async16(sb + SM_Q + u * 2048 + r * 16, ok ? qb + (int64_t)(t0 + r) * p.sq.l + u * 8 : qb, ok);
-        r += dq; u += dr;
-        if (u >= upr) { u -= upr; ++r; }
-      }
+    fence_proxy_async();
+    // ---- loads: one TMA tile per operand and column atom; rows outside [0, L) read as zero ----
+    // every box is 64 columns wide (columns past hd are out of bounds: zero-filled, and counted)
+    tma::mbar_expect_tx(bar_qk, (uint32_t)natom * 128u * (TQ + NK));
+    tma::mbar_expect_tx(bar_v, (uint32_t)natom * 128u * NK);
+    for (int a = 0; a < natom; ++a) {
+      tma::load_4d(sb + SM_Q + a * q_atom, &p.mq, bar_qk, 64 * a, t0, h, b);
+      tma::load_4d(sb + SM_K + a * kv_atom, &p.mk, bar_qk, 64 * a, k0, h, b);
     }
-    const __nv_bfloat16* kb = p.k + b * p.sk.b + h * p.sk.h;
-    const __nv_bfloat16* vb = p.v + b * p.sv.b + h * p.sv.h;
-    {
-      int r = tid / upr, u = tid - r * upr;
-      const int total = (NK * upr) / NT;  // NK is a multiple of 32, so NK * upr is a multiple of 128
-      for (int n = 0; n < total; ++n) {
-        const int pos = k0 + r;
-        const bool ok = pos >= 0 && pos < L;
-        const uint32_t off = u * (NK * 16) + r * 16;
-        cp_async16(sb + SM_K + off, ok ? kb + (int64_t)pos * p.sk.l + u * 8 : kb, ok);
-        cp_async16(sb + SM_V + off, ok ? vb + (int64_t)pos * p.sv.l + u * 8 : vb, ok);
-        r += dq; u += dr;
-        if (u >= upr) { u -= upr; ++r; }
-      }
-    }
+    for (int a = 0; a < natom; ++a) tma::load_4d(sb + SM_V + a * kv_atom, &p.mv, bar_v, 64 * a, k0, h, b);
   }
-  cp_async_commit();
   SWA_TR(0);  // set-up + load issue
   // TMEM is allocated only now: when more CTAs are resident than TMEM can serve, the extra
   // CTA blocks here with its loads already in flight.
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
   SWA_TR(10);  // TMEM allocation
-  cp_async_wait_all();
-  fence_proxy_async();
   fence_before_sync();
-  __syncthreads();
+  __syncthreads();  // barriers initialised, TMEM base published
   fence_after_sync();
-  SWA_TR(1);  // load wait
   const uint32_t tmem = *tmem_slot;
   const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
   const uint32_t TM_S = 0, TM_O = (uint32_t)NK;
 
-  // ---- S = Q K^T ----
+  // ---- S = Q K^T as soon as Q and K have landed (V may still be in flight) ----
   if (tid == 0) {
+    mbar_wait_bounded<false>(bar_qk, 0, abort_flag, p.status, 64u);
+    fence_after_sync();
+    SWA_TR(1);  // load wait
     const uint32_t idesc = make_idesc_bf16(128, NK, 0, 0);
-    for (int ks = 0; ks < (hd >> 4); ++ks) {
-      const uint64_t da = make_smem_desc(sb + SM_Q + ks * 4096, 2048, 128);
-      const uint64_t db = make_smem_desc(sb + SM_K + ks * (NK * 32), NK * 16, 128);
-      mma_ss(tmem + TM_S, da, db, idesc, ks > 0);
+    int first = 1;
+    for (int a = 0; a < natom; ++a) {
+      const int ksteps = (min(64, hd - 64 * a)) >> 4;
+      for (int ks = 0; ks < ksteps; ++ks) {  // a K-step of 16 elements = 32 bytes inside the swizzled row
+        const uint64_t da = make_smem_desc_sw128(sb + SM_Q + a * q_atom + ks * 32, 16, 1024);
+        const uint64_t db = make_smem_desc_sw128(sb + SM_K + a * kv_atom + ks * 32, 16, 1024);
+        mma_ss(tmem + TM_S, da, db, idesc, first ? 0u : 1u);
+        first = 0;
+      }
     }
     mma_commit(bar_s);
   }
@@ -209,10 +197,13 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const Params p) {
 
   // ---- O = P V ----
   if (tid == 0) {
+    mbar_wait_bounded<false>(bar_v, 0, abort_flag, p.status, 128u);
     fence_after_sync();
+    // V tiles are MN-major: 64-column atoms kv_atom apart (LBO), groups of 8 keys 1024 B apart (SBO)
     const uint32_t idesc = make_idesc_bf16(128, hd, 0, 1);
     for (int ks = 0; ks < (NK >> 4); ++ks)
-      mma_ts(tmem + TM_O, tmem + TM_S + 8 * ks, make_smem_desc(sb + SM_V + ks * 256, 128, NK * 16), idesc, ks > 0);
+      mma_ts(tmem + TM_O, tmem + TM_S + 8 * ks, make_smem_desc_sw128(sb + SM_V + ks * 2048, kv_atom, 1024), idesc,
+             ks > 0);
     mma_commit(bar_o);
   }
   __syncwarp();
@@ -222,13 +213,11 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const Params p) {
   fence_after_sync();
   SWA_TR(6);  // PV MMA
   {
-    // Each thread parks its normalised row in this warp's 32-row staging tile (the K operand
-    // buffer, free since S was computed); the warp then copies the tile out with every store
-    // instruction covering whole 128-byte lines.
+    // Each thread writes its normalised row into the output tile (Q's space, free since S was
+    // computed) in the 128-byte-swizzled layout; one thread then hands the tile to the TMA unit,
+    // which clips rows past the end of the sequence.
     const float inv = 1.0f / sum;
-    const int yrow_bytes = hd * 2 + 16;  // the pad keeps the per-row 16-byte stores conflict free
-    uint8_t* ytile = smem + SM_K + (warp * 32) * yrow_bytes;
-    uint8_t* yrow_s = ytile + lane * yrow_bytes;
+    const int t = tid;
     for (int i = 0; i < (hd >> 4); ++i) {
       uint32_t r[16];
       tmem_ld16(tlane + TM_O + 16 * i, r);
@@ -242,29 +231,17 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const Params p) {
       hi.y = pack_bf16(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
       hi.z = pack_bf16(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
       hi.w = pack_bf16(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
-      *reinterpret_cast<uint4*>(yrow_s + 32 * i) = lo;
-      *reinterpret_cast<uint4*>(yrow_s + 32 * i + 16) = hi;
+      uint8_t* atom = smem + SM_Q + (i >> 2) * q_atom;  // 16 columns = 2 chunks; 4 such pieces per 64-column atom
+      *reinterpret_cast<uint4*>(atom + tma::sw128_offset(t, 2 * (i & 3))) = lo;
+      *reinterpret_cast<uint4*>(atom + tma::sw128_offset(t, 2 * (i & 3) + 1)) = hi;
     }
-    __syncwarp();
+    fence_proxy_async();  // generic-proxy writes -> visible to the TMA unit
     SWA_TR(7);  // O -> staging
-    const int tok_w = t0 + warp * 32;
-    __nv_bfloat16* otok = p.o + b * p.so.b + (int64_t)tok_w * p.so.l + h * p.so.h;
-    const int dq = 32 / upr, dr = 32 % upr;
-    int r = lane / upr, cc = lane - r * upr;
-    for (int n0 = 0; n0 < upr; n0 += 4) {
-      uint4 val[4];
-      int rr[4], cq[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        rr[u] = r; cq[u] = cc;
-        if (n0 + u < upr) val[u] = *reinterpret_cast<const uint4*>(ytile + r * yrow_bytes + cc * 16);
-        r += dq; cc += dr;
-        if (cc >= upr) { cc -= upr; ++r; }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (n0 + u < upr && tok_w + rr[u] < L)
-          *reinterpret_cast<uint4*>(otok + (int64_t)rr[u] * p.so.l + cq[u] * 8) = val[u];
+    __syncthreads();
+    if (tid == 0) {
+      for (int a = 0; a < natom; ++a) tma::store_4d(&p.mo, sb + SM_Q + a * q_atom, 64 * a, t0, h, b);
+      bulk_commit();
+      bulk_wait_read_all();  // shared memory must stay intact until the TMA unit has read it
     }
   }
   SWA_TR(8);  // copy-out
@@ -312,23 +289,27 @@ int launch_swa_prefill_tc(const void* q, const void* k, const void* v, void* o, 
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return BASED_ERR_IMPL;
   const int64_t all[] = {sq.b, sq.h, sq.l, sk.b, sk.h, sk.l, sv.b, sv.h, sv.l, so.b, so.h, so.l};
   for (int64_t s : all)
-    if (s % 8 != 0) return BASED_ERR_IMPL;
+    if (s % 8 != 0 || s <= 0) return BASED_ERR_IMPL;  // TMA strides: positive multiples of 16 bytes
   const int NK = TQ + window_left;
   const int tiles_per_seq = (L + TQ - 1) / TQ;
   const long long tiles = (long long)B * H * tiles_per_seq;
   if (tiles > 2147483647LL) return BASED_ERR_TOO_LARGE;
   Params p;
-  p.q = static_cast<const __nv_bfloat16*>(q);
-  p.k = static_cast<const __nv_bfloat16*>(k);
-  p.v = static_cast<const __nv_bfloat16*>(v);
-  p.o = static_cast<__nv_bfloat16*>(o);
+  // tensor maps over [B][H][L][hd] (dims innermost first: hd, L, H, B); a batch or head extent of 1
+  // may come with any stride, so give those a harmless one
+  auto fix = [&](int64_t s, int extent) { return extent == 1 ? (int64_t)8 : s; };
+  if (tma::encode_bf16_4d_sw128(&p.mq, q, hd, L, H, B, sq.l, fix(sq.h, H), fix(sq.b, B), 64, TQ) ||
+      tma::encode_bf16_4d_sw128(&p.mk, k, hd, L, H, B, sk.l, fix(sk.h, H), fix(sk.b, B), 64, NK) ||
+      tma::encode_bf16_4d_sw128(&p.mv, v, hd, L, H, B, sv.l, fix(sv.h, H), fix(sv.b, B), 64, NK) ||
+      tma::encode_bf16_4d_sw128(&p.mo, o, hd, L, H, B, so.l, fix(so.h, H), fix(so.b, B), 64, TQ))
+    return BASED_ERR_IMPL;
   p.L = L; p.H = H; p.hd = hd; p.W = window_left; p.tiles_per_seq = tiles_per_seq;
   p.tmem_cols = (NK + hd <= 256) ? 256 : 512;
-  p.sq = sq; p.sk = sk; p.sv = sv; p.so = so;
   p.scale_log2e = scale * 1.4426950408889634f;
   cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_tc_status_swa);
   if (e != cudaSuccess) return (int)e;
-  const int smem = hd * 256 + 2 * hd * NK * 2 + 64;
+  const int natom = (hd + 63) / 64;
+  const int smem = natom * (TQ + 2 * NK) * 128 + 64 + 1024;  // + slack to align the tiles to 1024 bytes
   e = cudaFuncSetAttribute(swa_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;
   swa_prefill_tc_kernel<<<(unsigned)tiles, NT, smem, stream>>>(p);

@@ -28,6 +28,16 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
+// Same for the 128-byte-swizzled canonical layouts (what a TMA tile load with 128-byte swizzle
+// produces; tile base 1024-byte aligned, rows of 128 bytes):
+//   K-major  operand: 8-row groups SBO (= 1024 B) apart, LBO unused (16); a K-step of 16 elements
+//                     advances the start address by 32 bytes inside the row
+//   MN-major operand: groups of 8 k-rows SBO (= 1024 B) apart, 64-element column atoms LBO apart;
+//                     a K-step of 16 rows advances the start address by 2048 bytes
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return make_smem_desc(saddr, lbo_bytes, sbo_bytes) | (2ull << 61);
+}
+
 // kind::f16 instruction descriptor: bf16 A and B, fp32 accumulator.
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4)                        // accumulator format F32
