@@ -27,6 +27,7 @@ const char* based_error_string(int code) {
     case BASED_ERR_ALIGN: return "pointer or stride not aligned as required";
     case BASED_ERR_IMPL: return "requested implementation cannot run these arguments";
     case BASED_ERR_TOO_LARGE: return "size exceeds a fixed capacity";
+    case BASED_ERR_SCRATCH: return "workspace is NULL, misaligned or too small";
     default: break;
   }
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
@@ -41,27 +42,48 @@ int based_read_status(unsigned int* out, int reset) {
   return rc;
 }
 
-int based_linattn_prefill(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
-                          int B, int H, int L, int d, int dv, const int64_t q_strides[3],
-                          const int64_t k_strides[3], const int64_t v_strides[3], const int64_t y_strides[3],
-                          int io_dtype, int state_dtype, float eps, int impl, void* stream) {
+}  // extern "C"
+
+namespace {
+
+// Checks shared by the whole-sequence entry points.  Returns kDone when the call is already complete
+// (nothing to compute), 0 to go on, a negative code to reject.
+constexpr int kDone = 0x40000000;  // not a cudaError_t value
+int prefill_preamble(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state, int B,
+                     int H, int L, int d, int dv, const int64_t* q_strides, const int64_t* k_strides,
+                     const int64_t* v_strides, const int64_t* y_strides, int io_dtype, int state_dtype,
+                     cudaStream_t st) {
   if (!q || !k || !v || !y || !q_strides || !k_strides || !v_strides || !y_strides) return BASED_ERR_NULL;
   if ((kv_state == nullptr) != (k_state == nullptr)) return BASED_ERR_NULL;
   if (!dtype_ok(io_dtype) || !dtype_ok(state_dtype)) return BASED_ERR_DTYPE;
   if (B < 0 || H < 0 || L < 0 || d != kFeatureDim || dv < 16 || dv > 128 || dv % 16 != 0) return BASED_ERR_SHAPE;
   if ((int64_t)B * H > 2147483647LL) return BASED_ERR_TOO_LARGE;
-  if (B == 0 || H == 0) return BASED_OK;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (B == 0 || H == 0) return kDone;
   if (L == 0) {
     // empty sequence: the states are the empty sums
     if (kv_state) {
       const size_t es = dtype_size(state_dtype);
       cudaError_t e = cudaMemsetAsync(kv_state, 0, (size_t)B * H * dv * kExpandedDim * es, st);
       if (e == cudaSuccess) e = cudaMemsetAsync(k_state, 0, (size_t)B * H * kExpandedDim * es, st);
-      return (int)e;
+      return e == cudaSuccess ? kDone : (int)e;
     }
-    return BASED_OK;
+    return kDone;
   }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int based_linattn_prefill(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
+                          int B, int H, int L, int d, int dv, const int64_t q_strides[3],
+                          const int64_t k_strides[3], const int64_t v_strides[3], const int64_t y_strides[3],
+                          int io_dtype, int state_dtype, float eps, int impl, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int pre = prefill_preamble(q, k, v, y, kv_state, k_state, B, H, L, d, dv, q_strides, k_strides, v_strides,
+                                   y_strides, io_dtype, state_dtype, st);
+  if (pre != 0) return pre == kDone ? BASED_OK : pre;
   // AUTO: the tensor-core kernel when it accepts the arguments (bf16 I/O, its alignment
   // rules), else the CUDA-core kernel.  Both are GPU kernels; there is no host path.
   const bool autosel = impl == BASED_IMPL_AUTO;
@@ -69,13 +91,38 @@ int based_linattn_prefill(const void* q, const void* k, const void* v, void* y, 
   if (impl == BASED_IMPL_TCGEN05) {
     if (io_dtype != BASED_BF16) return BASED_ERR_IMPL;
     const int rc = launch_linattn_prefill_tc(q, k, v, y, kv_state, k_state, B, H, L, dv, s3(q_strides),
-                                             s3(k_strides), s3(v_strides), s3(y_strides), state_dtype, eps, st);
+                                             s3(k_strides), s3(v_strides), s3(y_strides), state_dtype, eps, 1,
+                                             nullptr, 0, st);
     if (!(autosel && rc == BASED_ERR_IMPL)) return rc;
     impl = BASED_IMPL_SIMT;
   }
   if (impl != BASED_IMPL_SIMT) return BASED_ERR_IMPL;
   return launch_linattn_prefill_simt(q, k, v, y, kv_state, k_state, B, H, L, dv, s3(q_strides), s3(k_strides),
                                      s3(v_strides), s3(y_strides), io_dtype, state_dtype, eps, st);
+}
+
+int based_linattn_prefill_segments(int B, int H, int L) {
+  if (B <= 0 || H <= 0 || L <= 0) return 1;
+  return linattn_prefill_tc_auto_segments(B, H, L);
+}
+
+size_t based_linattn_prefill_scratch_bytes(int B, int H, int L, int dv, int nseg) {
+  if (B <= 0 || H <= 0 || L <= 0 || dv <= 0 || nseg <= 1) return 0;
+  return linattn_prefill_tc_scratch_bytes(B, H, L, dv, nseg);
+}
+
+int based_linattn_prefill_split(const void* q, const void* k, const void* v, void* y, void* kv_state,
+                                void* k_state, int B, int H, int L, int d, int dv, const int64_t q_strides[3],
+                                const int64_t k_strides[3], const int64_t v_strides[3],
+                                const int64_t y_strides[3], int state_dtype, float eps, int nseg, void* scratch,
+                                size_t scratch_bytes, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (nseg < 1) return BASED_ERR_SHAPE;
+  const int pre = prefill_preamble(q, k, v, y, kv_state, k_state, B, H, L, d, dv, q_strides, k_strides, v_strides,
+                                   y_strides, BASED_BF16, state_dtype, st);
+  if (pre != 0) return pre == kDone ? BASED_OK : pre;
+  return launch_linattn_prefill_tc(q, k, v, y, kv_state, k_state, B, H, L, dv, s3(q_strides), s3(k_strides),
+                                   s3(v_strides), s3(y_strides), state_dtype, eps, nseg, scratch, scratch_bytes, st);
 }
 
 int based_linattn_decode(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,

@@ -74,7 +74,7 @@ constexpr uint32_t TM_COLS = 512;
 
 // mbarrier slots (8 bytes each) from Smem::bar
 enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_P_READY, B_O_DONE, B_ST_DONE, B_PQ_READY, B_PK_READY,
-           B_STB_READY, B_O_FREE, B_PK_FREE, B_PK_FREE1, B_COUNT };
+           B_STB_READY, B_O_FREE, B_PK_FREE, B_PK_FREE1, B_INIT, B_FIN, B_COUNT };
 
 template <int G0, int G1, typename F>
 __device__ __forceinline__ void static_for(F&& f) {
@@ -179,7 +179,18 @@ struct Params {
   Strides3 sq, sk, sv, sy;
   float eps;
   unsigned int* status;
+  // Sequence split.  The sequence is cut into nseg segments of seg_chunks chunks and the grid is
+  // (batch x head) x grid_segs CTAs, one segment each.
+  //   mode 0: grid_segs = nseg = 1, the whole sequence in one CTA.
+  //   mode 1: segments 0 .. nseg-2 only accumulate their own state^T (packed features, fp32) and
+  //           write it to seg_state[bh][seg][dv+1][160]; no outputs.
+  //   mode 2: every segment computes its outputs; segment s > 0 starts from seg_state[bh][s-1],
+  //           which by then holds the sum over the segments before it (see segment_scan_kernel);
+  //           the last segment writes kv_state / k_state.
+  int mode, nseg, grid_segs, seg_chunks;
+  float* seg_state;
 };
+constexpr int MODE_WHOLE = 0, MODE_SEG_STATE = 1, MODE_SEG_OUTPUT = 2;
 
 __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -187,10 +198,17 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qd = warp & 3;       // TMEM lane quadrant this warp can reach
   const int t = qd * 32 + lane;  // token within the chunk == TMEM lane (compute warps)
-  const int bh = blockIdx.x, b = bh / p.H, h = bh - b * p.H;
-  const int dv = p.dv, NV = dv + 16, L = p.L;
+  const int bh = blockIdx.x / p.grid_segs, seg = blockIdx.x - bh * p.grid_segs;
+  const int b = bh / p.H, h = bh - b * p.H;
+  const int dv = p.dv, NV = dv + 16;
   const Smem lay(dv);
-  const int nchunks = (L + C - 1) / C;
+  // This CTA's tokens: tok_base .. tok_base + L - 1 (L counts from the segment's first token).
+  const int tok_base = seg * p.seg_chunks * C;
+  const int L = p.L - tok_base;
+  const int nchunks = min(p.seg_chunks, (L + C - 1) / C);
+  const int mode = p.mode;
+  const bool has_init = mode == MODE_SEG_OUTPUT && seg > 0;
+  const bool write_state = mode != MODE_SEG_STATE && seg == p.nseg - 1 && p.kv_state != nullptr;
 
   auto bar = [&](int i) { return sb + lay.bar + 8 * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + lay.bar + 8 * B_COUNT);
@@ -210,9 +228,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
 #define TR2_END(slot) tr_wait[slot] += clock64() - tr_t2
   const long long tr_start = clock64();
   auto wait = [&](int i, uint32_t parity, unsigned int code) {
-#ifdef BASED_EXPERIMENT_FREERUN
-    return;  // timing experiment: every role runs at its own pace, results are garbage
-#endif
     const long long t0 = clock64();
     mbar_wait_bounded(bar(i), parity & 1u, abort_flag, p.status, code);
     tr_wsum += clock64() - t0;
@@ -240,6 +255,8 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
     mbar_init(bar(B_O_FREE), 4);
     mbar_init(bar(B_PK_FREE), 1);
     mbar_init(bar(B_PK_FREE + 1), 1);
+    mbar_init(bar(B_INIT), 4);
+    mbar_init(bar(B_FIN), 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -258,25 +275,15 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   const uint32_t tmem = *tmem_slot;
   const uint32_t tlane = tmem + ((uint32_t)(qd * 32) << 16);  // this warp's lane window, column 0
 
-#ifndef BASED_EXPERIMENT_MMA_MASK
-#define BASED_EXPERIMENT_MMA_MASK 15
-#endif
-#ifdef BASED_EXPERIMENT_MMA_ONLY
-  // Timing experiment: only the MMA warp runs, without waiting for operands (results are garbage).
-  const bool mma_only = true;
-#else
-  const bool mma_only = false;
-#endif
-  if (mma_only && warp != W_MMA) {
-    // nothing
-  } else if (warp >= W_LOAD) {
+  if (warp >= W_LOAD) {
     // ================================================================ loaders: cp.async, 16-byte pieces.
     // Load warp w owns buffer w and the chunks j = w (mod the buffer count): wait until the buffer is free,
     // issue the chunk, wait for it to land, publish it.  Three chunks are in flight per CTA.
     const int st = warp - W_LOAD, NS = lay.nstage;
-    const __nv_bfloat16* qb = p.q + b * p.sq.b + h * p.sq.h;
-    const __nv_bfloat16* kb = p.k + b * p.sk.b + h * p.sk.h;
-    const __nv_bfloat16* vb = p.v + b * p.sv.b + h * p.sv.h;
+    const __nv_bfloat16* qb = p.q + b * p.sq.b + h * p.sq.h + (int64_t)tok_base * p.sq.l;
+    const __nv_bfloat16* kb = p.k + b * p.sk.b + h * p.sk.h + (int64_t)tok_base * p.sk.l;
+    const __nv_bfloat16* vb = p.v + b * p.sv.b + h * p.sv.h + (int64_t)tok_base * p.sv.l;
+    const bool need_q = mode != MODE_SEG_STATE;
     const uint32_t base = sb + st * lay.stage_bytes;
     // q/k: piece i = lane + 32 n  ->  token (lane >> 1) + 16 n, half lane & 1
     const int qk_tk = lane >> 1, qk_half = lane & 1;
@@ -292,7 +299,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
           const bool ok = tok0 + qk_tk + 16 * n < L;
-          cp_async16(base + qk_off + n * 512, ok ? qp + (int64_t)(16 * n) * p.sq.l : qb, ok);
+          if (need_q) cp_async16(base + qk_off + n * 512, ok ? qp + (int64_t)(16 * n) * p.sq.l : qb, ok);
           cp_async16(base + 4096 + qk_off + n * 512, ok ? kp + (int64_t)(16 * n) * p.sk.l : kb, ok);
         }
       }
@@ -316,10 +323,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
     if (lane == 0) {
 #ifdef BASED_TC_TRACE
       auto mwait = [&](int i, uint32_t parity, unsigned int code) {
-        if (mma_only) return;
-#ifdef BASED_EXPERIMENT_FREERUN
-        return;
-#endif
         const long long t0 = clock64();
         mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
         tr_wsum += clock64() - t0;
@@ -345,6 +348,24 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       int st = 0, st1 = (1 % NS);
       uint32_t st1_par = (NS == 1) ? 1u : 0u;
       int pkb = 0;
+      if (mode == MODE_SEG_STATE) {
+        // state only: St += V'(c)^T phi'(K_c) for every chunk of the segment
+        uint32_t st_par = 0;
+        for (int c = 0; c < nchunks; ++c) {
+          mwait(B_FULL + st, st_par, 0x210u);
+          mwait(B_PK_READY, c, 0x211u);
+          fence_after_sync();
+          const uint64_t dv_c = d_v + st * stage_units, d_pk_c = d_pk + pkb * (40960 >> 4);
+#pragma unroll
+          for (int j = 0; j < C / 16; ++j)
+            mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (c > 0 || j > 0) ? 1u : 0u);
+          mma_commit(bar(B_EMPTY + st));
+          mma_commit(bar(B_PK_FREE + pkb));
+          if (++st == NS) { st = 0; st_par ^= 1u; }
+          if (++pkb == NPK) pkb = 0;
+        }
+        mma_commit(bar(B_FIN));
+      } else {
       mwait(B_FULL + 0, 0, 0x200u);
       fence_after_sync();
       mma_ss(tmem + TM_S, d_q, d_k, idesc_s, 0);
@@ -356,21 +377,17 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         if (c > 0) mwait(B_O_FREE, c - 1, 0x202u);
         fence_after_sync();
         TR_BEGIN();
-        if (BASED_EXPERIMENT_MMA_MASK & 1) {
 #pragma unroll
-          for (int j = 0; j < C / 16; ++j)
-            mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
-        }
+        for (int j = 0; j < C / 16; ++j)
+          mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
         TR_END(26);
         // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
         if (c + 1 < nchunks) {
           mwait(B_FULL + st1, st1_par, 0x203u);
           fence_after_sync();
           TR_BEGIN();
-          if (BASED_EXPERIMENT_MMA_MASK & 2) {
-            const uint32_t so = st1 * stage_units;
-            mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
-          }
+          const uint32_t so = st1 * stage_units;
+          mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
           mma_commit(bar(B_S_DONE));
           TR_END(27);
         }
@@ -379,6 +396,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         // rewrites the bf16 state waits for the commit below, i.e. for the readout to be complete.
         mwait(B_PQ_READY, c, 0x204u);
         if (c > 0) mwait(B_STB_READY, c - 1, 0x205u);
+        else if (has_init) mwait(B_INIT, 0, 0x207u);  // state^T and its bf16 copy were preloaded
         mwait(B_PK_READY, c, 0x206u);
         fence_after_sync();
         TR_BEGIN();
@@ -386,10 +404,10 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
           const uint64_t d_pk_c = d_pk + pkb * (40960 >> 4);
 #pragma unroll
           for (int j = 0; j < DR / 16; ++j) {
-            if (c > 0 && (BASED_EXPERIMENT_MMA_MASK & 4))
+            if (c > 0 || has_init)
               mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb + 256 * j, idesc_o_st, 1);
-            if (j < C / 16 && (BASED_EXPERIMENT_MMA_MASK & 8))
-              mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (c > 0 || j > 0) ? 1u : 0u);
+            if (j < C / 16)
+              mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (c > 0 || j > 0 || has_init) ? 1u : 0u);
           }
         }
         mma_commit(bar(B_O_DONE));
@@ -401,10 +419,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         if (++st1 == NS) { st1 = 0; st1_par ^= 1u; }
         if (++pkb == NPK) pkb = 0;
       }
-#ifdef BASED_EXPERIMENT_FREERUN
-      mbar_wait_bounded<false>(bar(B_ST_DONE), (nchunks - 1) & 1u, abort_flag, p.status, 0x2FFu);
-#endif
-      if (mma_only) mbar_wait_bounded<false>(bar(B_ST_DONE), (nchunks - 1) & 1u, abort_flag, p.status, 0x2FFu);
+      }
 #ifdef BASED_TC_TRACE
       if (bh == 0) {
         tr_wait[0] = tr_wsum;
@@ -425,6 +440,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         const uint4 a = *reinterpret_cast<const uint4*>(stg), bq = *reinterpret_cast<const uint4*>(stg + 128);
         X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
       }
+      if (mode != MODE_SEG_STATE) {
       if (c > 0) wait(B_O_DONE, c - 1, 0x301u);  // the previous phi'(Q) has been consumed
       fence_after_sync();
       TR_BEGIN();
@@ -447,6 +463,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       __syncwarp();
       TR_END(18);
       if (lane == 0) mbar_arrive(bar(B_PQ_READY));
+      }
       {
         const uint4 a = *reinterpret_cast<const uint4*>(stg + 4096), bq = *reinterpret_cast<const uint4*>(stg + 4096 + 128);
         X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
@@ -464,11 +481,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
         constexpr int g = decltype(G)::value;
         if constexpr (g == 0) w0 &= one;
-#ifndef BASED_EXPERIMENT_SKIP_PHIK_STS
         *reinterpret_cast<uint4*>(dst + g * 2048) = make_uint4(w0, w1, w2, w3);
-#else
-        if (w0 == 0x12345678u && w1 == w2 && w3 == 77u) *reinterpret_cast<uint4*>(dst + g * 2048) = make_uint4(w0, w1, w2, w3);
-#endif
       });
       TR_END(19);
       TR_BEGIN();
@@ -479,7 +492,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
     }
   } else if (warp >= W_OUT && warp < W_MMA) {
     // ================================================================ output warps: O -> y
-    __nv_bfloat16* yb = p.y + b * p.sy.b + h * p.sy.h;
+    __nv_bfloat16* yb = p.y + b * p.sy.b + h * p.sy.h + (int64_t)tok_base * p.sy.l;
     auto cvt16 = [&](const uint32_t (&r)[16], float sc, uint4& lo, uint4& hi) {
       lo.x = pack_bf16(__uint_as_float(r[0]) * sc, __uint_as_float(r[1]) * sc);
       lo.y = pack_bf16(__uint_as_float(r[2]) * sc, __uint_as_float(r[3]) * sc);
@@ -490,7 +503,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       hi.z = pack_bf16(__uint_as_float(r[12]) * sc, __uint_as_float(r[13]) * sc);
       hi.w = pack_bf16(__uint_as_float(r[14]) * sc, __uint_as_float(r[15]) * sc);
     };
-    for (int c = 0; c < nchunks; ++c) {
+    for (int c = 0; c < (mode == MODE_SEG_STATE ? 0 : nchunks); ++c) {
       // ---- epilogue: y = O[:, :dv] / (O[:, dv] + eps), 32 columns per round trip ----
       wait(B_O_DONE, c, 0x401u);
       fence_after_sync();
@@ -530,7 +543,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         const int cpr = dv >> 3;                     // 16-byte pieces per row
         const int tok_w = c * C + qd * 32;           // first token of this warp's tile
         __nv_bfloat16* ytok = yb + (int64_t)tok_w * p.sy.l;
-#ifndef BASED_EXPERIMENT_SKIP_YSTORE
         // piece idx = lane + 32 n -> (row idx / cpr, piece idx % cpr), advanced incrementally;
         // four loads are issued before their four stores so their latencies overlap
         {
@@ -553,7 +565,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
                 *reinterpret_cast<uint4*>(ytok + (int64_t)rr[u] * p.sy.l + cq[u] * 8) = val[u];
           }
         }
-#endif
         __syncwarp();  // the tile is rewritten by other lanes in the next chunk
       }
       TR_END(22);
@@ -606,7 +617,56 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       hi.z = pack_bf16(__uint_as_float(r[12]) * sc, __uint_as_float(r[13]) * sc);
       hi.w = pack_bf16(__uint_as_float(r[14]) * sc, __uint_as_float(r[15]) * sc);
     };
+    // final fp32 state^T -> shared memory at offset 0 (every MMA and every other warp's use of
+    // shared memory is over by then).  The TMEM loads are warp-collective, so every lane issues
+    // them; only rows < NV are kept.
+    auto stage_state = [&]() {
+      float* stg = reinterpret_cast<float*>(smem) + t * STAGE_STRIDE_F;
+#pragma unroll 1
+      for (int i = 0; i < 10; ++i) {
+        uint32_t r[16];
+        tmem_ld16(tlane + TM_ST + 16 * i, r);
+        tmem_ld_wait();
+        if (t < NV) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            *reinterpret_cast<uint4*>(stg + 16 * i + 4 * e) = make_uint4(r[4 * e], r[4 * e + 1], r[4 * e + 2], r[4 * e + 3]);
+        }
+      }
+    };
+    if (mode == MODE_SEG_STATE) {
+      wait(B_FIN, 0, 0x410u);
+      fence_after_sync();
+      stage_state();
+    } else {
     make_p(0);
+    if (has_init) {
+      // Preload state^T (fp32, TMEM) and its bf16 operand copy with the sum over the earlier segments.
+      const float* src = p.seg_state + ((size_t)bh * (p.nseg - 1) + (seg - 1)) * (size_t)((dv + 1) * DR) + (size_t)t * DR;
+      const bool row = t <= dv;
+#pragma unroll 1
+      for (int i = 0; i < 10; ++i) {
+        uint32_t r[16];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint4 x = row ? __ldg(reinterpret_cast<const uint4*>(src + 16 * i + 4 * e)) : make_uint4(0, 0, 0, 0);
+          r[4 * e] = x.x; r[4 * e + 1] = x.y; r[4 * e + 2] = x.z; r[4 * e + 3] = x.w;
+        }
+        tmem_st16(tlane + TM_ST + 16 * i, r);
+        if (t < NV) {
+          uint4 a0, a1;
+          cvt16(r, 1.0f, a0, a1);
+          uint8_t* dst = smem + lay.stb + (2 * i) * 2048 + t * 16;
+          *reinterpret_cast<uint4*>(dst) = a0;
+          *reinterpret_cast<uint4*>(dst + 2048) = a1;
+        }
+      }
+      tmem_st_wait();
+      fence_proxy_async();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_INIT));
+    }
     for (int c = 0; c < nchunks; ++c) {
       const bool last = c + 1 == nchunks;
       if (!last) make_p(c + 1);
@@ -626,11 +686,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
           uint4 a0, a1, b0, b1;
           cvt16(r0, 1.0f, a0, a1);
           cvt16(r1, 1.0f, b0, b1);
-#ifdef BASED_EXPERIMENT_SKIP_STB_STS
-          if (t < NV && a0.x == 0x12345678u && a1.y == 77u) {
-#else
           if (t < NV) {  // rows >= NV of the B operand are never read (N = NV)
-#endif
             uint8_t* dst = smem + lay.stb + (4 * i) * 2048 + t * 16;
             *reinterpret_cast<uint4*>(dst) = a0;
             *reinterpret_cast<uint4*>(dst + 2048) = a1;
@@ -643,23 +699,10 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         __syncwarp();
         TR_END(23);
         if (lane == 0) mbar_arrive(bar(B_STB_READY));
-      } else if (p.kv_state != nullptr) {
-        // every MMA and every other warp's use of shared memory is over: stage at offset 0.
-        // The TMEM loads are warp-collective, so every lane issues them; only rows < NV are kept.
-        float* stg = reinterpret_cast<float*>(smem) + t * STAGE_STRIDE_F;
-#pragma unroll 1
-        for (int i = 0; i < 10; ++i) {
-          uint32_t r[16];
-          tmem_ld16(tlane + TM_ST + 16 * i, r);
-          tmem_ld_wait();
-          if (t < NV) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              *reinterpret_cast<uint4*>(stg + 16 * i + 4 * e) =
-                  make_uint4(r[4 * e], r[4 * e + 1], r[4 * e + 2], r[4 * e + 3]);
-          }
-        }
+      } else if (write_state) {
+        stage_state();
       }
+    }
     }
   }
 
@@ -675,7 +718,15 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   // ------------------------------------------------------------------ final state, reference layout
   fence_before_sync();
   __syncthreads();
-  if (p.kv_state != nullptr) {
+  if (mode == MODE_SEG_STATE) {
+    // packed fp32 rows 0..dv, as they are
+    const float* stg = reinterpret_cast<const float*>(smem);
+    float* dst = p.seg_state + ((size_t)bh * (p.nseg - 1) + seg) * (size_t)((dv + 1) * DR);
+    for (int e = tid; e < (dv + 1) * (DR / 4); e += NT) {
+      const int n = e / (DR / 4), f4 = e - n * (DR / 4);
+      reinterpret_cast<float4*>(dst)[e] = *reinterpret_cast<const float4*>(stg + n * STAGE_STRIDE_F + 4 * f4);
+    }
+  } else if (write_state) {
     const float* stg = reinterpret_cast<const float*>(smem);
     const int total = (dv + 1) * kExpandedDim;
     for (int e = tid; e < total; e += NT) {
@@ -702,6 +753,19 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   }
 }
 
+// In place over the segments of one (batch, head): x[s] <- x[0] + ... + x[s], so that slot s holds
+// the state at the start of segment s + 1.  grid = (ceil(per / 256), batch x head).
+__global__ void __launch_bounds__(256) segment_scan_kernel(float* __restrict__ x, int nslots, int per) {
+  const int e = blockIdx.x * 256 + threadIdx.x;
+  if (e >= per) return;
+  float* col = x + (size_t)blockIdx.y * nslots * per + e;
+  float acc = col[0];
+  for (int s = 1; s < nslots; ++s) {
+    acc += col[(size_t)s * per];
+    col[(size_t)s * per] = acc;
+  }
+}
+
 }  // namespace
 
 #ifdef BASED_TC_TRACE
@@ -722,9 +786,39 @@ int read_tc_status(unsigned int* out, int reset) {
   return (int)e;
 }
 
+// Segment plan for a split of about `want` segments: whole chunks per segment, no empty segment.
+static void plan_segments(int L, int want, int* nseg, int* seg_chunks) {
+  const int chunks = (L + C - 1) / C;
+  want = want < 1 ? 1 : (want > chunks ? chunks : want);
+  *seg_chunks = (chunks + want - 1) / want;
+  *nseg = (chunks + *seg_chunks - 1) / *seg_chunks;
+}
+
+int linattn_prefill_tc_auto_segments(int B, int H, int L) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return 1;
+  const int64_t bh = (int64_t)B * H;
+  const int chunks = (L + C - 1) / C;
+  if (bh <= 0 || bh * 2 > sms || chunks < 8) return 1;  // the grid already fills the machine, or nothing to split
+  int want = (int)(sms / bh);
+  if (want > chunks / 4) want = chunks / 4;             // at least four chunks per segment
+  int nseg, seg_chunks;
+  plan_segments(L, want, &nseg, &seg_chunks);
+  return nseg;
+}
+
+size_t linattn_prefill_tc_scratch_bytes(int B, int H, int L, int dv, int nseg) {
+  int n, sc;
+  plan_segments(L, nseg, &n, &sc);
+  return (size_t)B * H * (n - 1) * (dv + 1) * DR * sizeof(float);
+}
+
 int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
                               int B, int H, int L, int dv, Strides3 sq, Strides3 sk, Strides3 sv, Strides3 sy,
-                              int state_dtype, float eps, cudaStream_t stream) {
+                              int state_dtype, float eps, int nseg, void* scratch, size_t scratch_bytes,
+                              cudaStream_t stream) {
   // Requirements of this kernel; the caller may fall back to the CUDA-core kernel on ERR_IMPL.
   if (dv > 112) return BASED_ERR_IMPL;  // V' = dv + 16 columns must fit the 128 TMEM lanes
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(y)) return BASED_ERR_IMPL;
@@ -747,7 +841,31 @@ int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void*
   const Smem lay(dv);
   e = cudaFuncSetAttribute(linattn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total);
   if (e != cudaSuccess) return (int)e;
-  linattn_prefill_tc_kernel<<<B * H, NT, lay.total, stream>>>(p);
+  int seg_chunks;
+  plan_segments(L, nseg, &nseg, &seg_chunks);
+  p.nseg = nseg;
+  p.seg_chunks = seg_chunks;
+  p.seg_state = static_cast<float*>(scratch);
+  if (nseg == 1) {
+    p.mode = MODE_WHOLE;
+    p.grid_segs = 1;
+    linattn_prefill_tc_kernel<<<B * H, NT, lay.total, stream>>>(p);
+    return (int)cudaGetLastError();
+  }
+  // Three launches: per-segment states, their running sum, then the outputs of every segment.
+  if ((int64_t)B * H * nseg > 0x7fffffff) return BASED_ERR_SHAPE;
+  if (scratch == nullptr || !aligned16(scratch) ||
+      scratch_bytes < (size_t)B * H * (nseg - 1) * (dv + 1) * DR * sizeof(float))
+    return BASED_ERR_SCRATCH;
+  const int per = (dv + 1) * DR;
+  p.mode = MODE_SEG_STATE;
+  p.grid_segs = nseg - 1;
+  linattn_prefill_tc_kernel<<<B * H * (nseg - 1), NT, lay.total, stream>>>(p);
+  if (nseg > 2)
+    segment_scan_kernel<<<dim3((per + 255) / 256, B * H), 256, 0, stream>>>(p.seg_state, nseg - 1, per);
+  p.mode = MODE_SEG_OUTPUT;
+  p.grid_segs = nseg;
+  linattn_prefill_tc_kernel<<<B * H * nseg, NT, lay.total, stream>>>(p);
   return (int)cudaGetLastError();
 }
 

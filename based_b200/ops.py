@@ -42,6 +42,7 @@ def linattn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: f
                     return_state: bool = True, state_dtype: Optional[torch.dtype] = None,
                     out: Optional[torch.Tensor] = None, impl: str = "auto",
                     kv_state: Optional[torch.Tensor] = None, k_state: Optional[torch.Tensor] = None,
+                    nseg: Optional[int] = None, scratch: Optional[torch.Tensor] = None,
                     ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Causal Taylor linear attention over a whole sequence.
 
@@ -51,6 +52,12 @@ def linattn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: f
     ``'b h l d -> b l (h d)'`` rearrange is free), ``kv_state [B, H, 1, dv, 273]`` and
     ``k_state [B, H, 1, 1, 273]`` (linear_attention.py:220-222), or ``None`` for the states
     when ``return_state`` is false.  ``kv_state``/``k_state`` may be given to be filled in place.
+
+    ``nseg`` splits the SEQUENCE into that many segments that run on different SMs (bf16, tensor-core
+    kernel only): ``None`` lets the library choose (it splits only when ``B*H`` is below half the SM
+    count and ``L >= 1024``), ``1`` never splits.  The split needs a workspace of
+    ``based_linattn_prefill_scratch_bytes`` bytes; ``scratch`` (a CUDA uint8/float tensor at least that
+    large) may be given to reuse one, else it is taken from torch's caching allocator.
     """
     _need_cuda(q, k, v)
     B, H, L, d = q.shape
@@ -77,8 +84,30 @@ def linattn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, eps: f
             kv_state.zero_()
             k_state.zero_()
         return out, (kv_state if return_state else None), (k_state if return_state else None)
+    lib = _capi.lib()
+    can_split = q.dtype == torch.bfloat16 and dv <= 112 and impl in ("auto", "tcgen05")
+    if nseg is not None and nseg > 1 and not can_split:
+        raise ValueError("nseg > 1 needs bf16 inputs, dv <= 112 and the tensor-core kernel")
     with torch.cuda.device(q.device):
-        code = _capi.lib().based_linattn_prefill(
+        if nseg is None:
+            nseg = lib.based_linattn_prefill_segments(B, H, L) if can_split else 1
+        if nseg > 1:
+            need = lib.based_linattn_prefill_scratch_bytes(B, H, L, dv, nseg)
+            if scratch is None:
+                scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+            elif scratch.device != q.device or not scratch.is_contiguous():
+                raise ValueError("scratch must be a contiguous tensor on the inputs' device")
+            code = lib.based_linattn_prefill_split(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                kv_state.data_ptr() if return_state else None, k_state.data_ptr() if return_state else None,
+                B, H, L, d, dv,
+                _capi.strides(*q.stride()[:3]), _capi.strides(*k.stride()[:3]),
+                _capi.strides(*v.stride()[:3]), _capi.strides(*out.stride()[:3]),
+                _dt(sdt), float(eps), int(nseg), scratch.data_ptr(), scratch.numel() * scratch.element_size(),
+                _stream())
+            _capi.check(code, "based_linattn_prefill_split")
+            return out, (kv_state if return_state else None), (k_state if return_state else None)
+        code = lib.based_linattn_prefill(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
             kv_state.data_ptr() if return_state else None, k_state.data_ptr() if return_state else None,
             B, H, L, d, dv,

@@ -21,6 +21,7 @@
 #ifndef BASED_B200_H
 #define BASED_B200_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -34,6 +35,7 @@ extern "C" {
 #define BASED_ERR_ALIGN (-4)     /* pointer or stride not aligned as required */
 #define BASED_ERR_IMPL (-5)      /* requested implementation cannot run these arguments */
 #define BASED_ERR_TOO_LARGE (-6) /* size exceeds a fixed capacity */
+#define BASED_ERR_SCRATCH (-7)   /* caller-provided workspace is NULL, misaligned or too small */
 
 /* dtype codes */
 #define BASED_F32 0
@@ -85,6 +87,36 @@ int based_linattn_prefill(const void* q, const void* k, const void* v, void* y,
                           const int64_t q_strides[3], const int64_t k_strides[3],
                           const int64_t v_strides[3], const int64_t y_strides[3],
                           int io_dtype, int state_dtype, float eps, int impl, void* stream);
+
+/*
+ * The same computation with the SEQUENCE split into `nseg` segments, for long sequences with few
+ * (batch x head) pairs, where based_linattn_prefill would occupy only B*H of the GPU's SMs.
+ * Three launches on `stream`: each segment's own state sum_t phi(k_t) [v_t, 1]^T (fp32), the
+ * running sum of those over the segments, and then every segment's outputs starting from the
+ * state before it.  The reference has no counterpart: its chunked forms
+ * (based/models/mixers/linear_attention.py:154-167) walk the sequence serially per head.
+ *
+ *   bf16 q, k, v, y only (the tcgen05 kernel); dv a multiple of 16 in [16, 112];
+ *   every stride a multiple of 8 elements, q/k/v/y 16-byte aligned (else BASED_ERR_IMPL).
+ *   nseg      requested segment count (>= 1).  Segments hold a whole number of 128-token chunks,
+ *             so the count actually used is ceil(chunks / ceil(chunks / nseg)) <= nseg;
+ *             nseg == 1 is exactly based_linattn_prefill with TCGEN05.
+ *   scratch   device workspace of at least based_linattn_prefill_scratch_bytes(B, H, L, dv, nseg)
+ *             bytes, 16-byte aligned; every byte the kernels read is written by them first, so it
+ *             needs no initialisation.  It must not be shared by calls that can overlap.
+ *             May be NULL when the size is 0.
+ * based_linattn_prefill_segments returns the count this library would pick for the current
+ * device (1 = do not split: B*H already covers at least half of the SMs, or L < 1024).
+ */
+int based_linattn_prefill_segments(int B, int H, int L);
+size_t based_linattn_prefill_scratch_bytes(int B, int H, int L, int dv, int nseg);
+int based_linattn_prefill_split(const void* q, const void* k, const void* v, void* y,
+                                void* kv_state, void* k_state,
+                                int B, int H, int L, int d, int dv,
+                                const int64_t q_strides[3], const int64_t k_strides[3],
+                                const int64_t v_strides[3], const int64_t y_strides[3],
+                                int state_dtype, float eps, int nseg,
+                                void* scratch, size_t scratch_bytes, void* stream);
 
 /*
  * One recurrent decode step; updates kv_state and k_state IN PLACE.

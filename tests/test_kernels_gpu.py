@@ -53,6 +53,59 @@ def test_linattn_prefill_vs_oracle(ops, impl, dtype, L, dv):
     assert rel_err(ks.cpu(), ks_ref) < tol
 
 
+@pytest.mark.parametrize("B,H,L,dv,nseg", [(1, 2, 1024, 64, 2), (1, 2, 1024 + 77, 64, 3), (2, 1, 4096, 64, 8),
+                                            (1, 1, 2048, 32, 4), (1, 1, 2048 + 5, 112, 5), (1, 3, 300, 64, 64),
+                                            (1, 1, 128, 64, 4)])
+def test_linattn_prefill_sequence_split_vs_oracle(ops, B, H, L, dv, nseg):
+    """The sequence-split form (three launches) against the oracle and the single-launch kernel."""
+    from based_b200 import _capi
+    q, k, v = _qkv(B, H, L, dv, torch.bfloat16, seed=L + dv + nseg)
+    y_ref, kv_ref, ks_ref = O.linattn_chunked(q.double(), k.double(), v.double(), chunk=128)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    y, kv, ks = ops.linattn_prefill(qc, kc, vc, state_dtype=torch.float32, nseg=nseg)
+    y1, kv1, ks1 = ops.linattn_prefill(qc, kc, vc, state_dtype=torch.float32, nseg=1)
+    torch.cuda.synchronize()
+    assert _capi.read_status() == 0
+    tol = TOL[torch.bfloat16]
+    assert rel_err(y.cpu(), y_ref) < tol
+    assert rel_err(kv.cpu(), kv_ref) < tol
+    assert rel_err(ks.cpu(), ks_ref) < tol
+    # the split only changes the order of fp32 additions in the state
+    assert rel_err(y.float(), y1.float()) < 1e-2
+    assert rel_err(kv, kv1) < 1e-5
+    # outputs only, no state requested
+    y2, none_kv, none_ks = ops.linattn_prefill(qc, kc, vc, return_state=False, nseg=nseg)
+    assert none_kv is None and none_ks is None
+    assert torch.equal(y2, y)
+
+
+def test_linattn_prefill_split_chosen_by_library_and_workspace_checks(ops):
+    from based_b200 import _capi
+    lib = _capi.lib()
+    B, H, L, dv = 1, 2, 8192, 64
+    auto = lib.based_linattn_prefill_segments(B, H, L)
+    assert auto > 1                                     # two (batch, head) pairs leave the machine idle
+    assert lib.based_linattn_prefill_segments(64, 16, L) == 1
+    assert lib.based_linattn_prefill_segments(B, H, 512) == 1
+    need = lib.based_linattn_prefill_scratch_bytes(B, H, L, dv, auto)
+    assert need > 0 and lib.based_linattn_prefill_scratch_bytes(B, H, L, dv, 1) == 0
+    q, k, v = _qkv(B, H, L, dv, torch.bfloat16, seed=11)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    y_auto, kv_auto, _ = ops.linattn_prefill(qc, kc, vc, state_dtype=torch.float32)          # library's choice
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    y_ws, kv_ws, _ = ops.linattn_prefill(qc, kc, vc, state_dtype=torch.float32, nseg=auto, scratch=ws)
+    assert torch.equal(y_auto, y_ws) and torch.equal(kv_auto, kv_ws)
+    y_ref, kv_ref, _ = O.linattn_chunked(q.double(), k.double(), v.double(), chunk=128)
+    assert rel_err(y_auto.cpu(), y_ref) < TOL[torch.bfloat16]
+    assert rel_err(kv_auto.cpu(), kv_ref) < TOL[torch.bfloat16]
+    with pytest.raises(_capi.BasedLibraryError):        # workspace one byte short
+        ops.linattn_prefill(qc, kc, vc, nseg=auto, scratch=ws[: need - 16])
+    with pytest.raises(ValueError):                     # fp32 I/O has no split form
+        ops.linattn_prefill(qc.float(), kc.float(), vc.float(), nseg=2)
+    torch.cuda.synchronize()
+    assert _capi.read_status() == 0
+
+
 def test_linattn_prefill_golden_fp32(ops):
     """Golden vectors the reference itself produced (quadratic branch, fp64 run)."""
     g = load_golden("linattn_qkv_f64.npz")
