@@ -27,6 +27,8 @@ SIGNATURES = {
     "based_linattn_prefill_scratch_bytes": (ctypes.c_size_t, [c_int] * 5),
     "based_linattn_prefill_split": (c_int, [c_void_p] * 6 + [c_int] * 5 + [_I64P] * 4
                                     + [c_int, c_float, c_int, c_void_p, ctypes.c_size_t, c_void_p]),
+    "based_linattn_prefill_split_static": (c_int, [c_void_p] * 6 + [c_int] * 5 + [_I64P] * 4
+                                           + [c_int, c_float, c_int, c_void_p]),
     "based_linattn_decode": (c_int, [c_void_p] * 6 + [c_int] * 4 + [_I64P] * 4 + [c_int, c_int, c_float, c_void_p]),
     "based_swa_prefill": (c_int, [c_void_p] * 4 + [c_int] * 4 + [_I64P] * 4 + [c_int, c_float, c_int, c_int, c_void_p]),
     "based_rotary_apply": (c_int, [c_void_p] + [c_int] * 4 + [_I64P, c_void_p, c_void_p, c_int, POINTER(c_int32), c_int,

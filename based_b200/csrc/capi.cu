@@ -125,6 +125,20 @@ int based_linattn_prefill_split(const void* q, const void* k, const void* v, voi
                                    s3(v_strides), s3(y_strides), state_dtype, eps, nseg, scratch, scratch_bytes, st);
 }
 
+int based_linattn_prefill_split_static(const void* q, const void* k, const void* v, void* y, void* kv_state,
+                                       void* k_state, int B, int H, int L, int d, int dv,
+                                       const int64_t q_strides[3], const int64_t k_strides[3],
+                                       const int64_t v_strides[3], const int64_t y_strides[3], int state_dtype,
+                                       float eps, int nseg, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (nseg < 1) return BASED_ERR_SHAPE;
+  const int pre = prefill_preamble(q, k, v, y, kv_state, k_state, B, H, L, d, dv, q_strides, k_strides, v_strides,
+                                   y_strides, BASED_BF16, state_dtype, st);
+  if (pre != 0) return pre == kDone ? BASED_OK : pre;
+  return launch_linattn_prefill_tc_static(q, k, v, y, kv_state, k_state, B, H, L, dv, s3(q_strides), s3(k_strides),
+                                          s3(v_strides), s3(y_strides), state_dtype, eps, nseg, st);
+}
+
 int based_linattn_decode(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
                          int B, int H, int d, int dv, const int64_t q_strides[2], const int64_t k_strides[2],
                          const int64_t v_strides[2], const int64_t y_strides[2], int io_dtype, int state_dtype,

@@ -64,6 +64,10 @@ int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void*
                               int B, int H, int L, int dv, Strides3 sq, Strides3 sk, Strides3 sv, Strides3 sy,
                               int state_dtype, float eps, int nseg, void* scratch, size_t scratch_bytes,
                               cudaStream_t stream);
+int launch_linattn_prefill_tc_static(const void* q, const void* k, const void* v, void* y, void* kv_state,
+                                     void* k_state, int B, int H, int L, int dv, Strides3 sq, Strides3 sk,
+                                     Strides3 sv, Strides3 sy, int state_dtype, float eps, int nseg,
+                                     cudaStream_t stream);
 int linattn_prefill_tc_auto_segments(int B, int H, int L);
 size_t linattn_prefill_tc_scratch_bytes(int B, int H, int L, int dv, int nseg);
 

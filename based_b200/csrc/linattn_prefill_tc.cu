@@ -22,11 +22,17 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
+#include <mutex>
 #include <type_traits>
 
 namespace based {
 
 __device__ unsigned int g_tc_status = 0;  // ORed with a code when a bounded wait expires
+
+// Built-in workspace of the allocation-free sequence-split entry point: per-segment states,
+// (batch x head) x (segments - 1) x (dv + 1) x 160 floats.  Every word the kernels read was
+// written earlier in the same call, so nothing here has to start at zero.
+static __device__ __align__(256) unsigned char g_static_scratch[BASED_STATIC_SCRATCH_BYTES];
 
 #ifdef BASED_TC_TRACE
 // Debug build only: per-role cycle counters of CTA 0 (cycles spent in each barrier wait, total
@@ -867,6 +873,36 @@ int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void*
   p.grid_segs = nseg;
   linattn_prefill_tc_kernel<<<B * H * nseg, NT, lay.total, stream>>>(p);
   return (int)cudaGetLastError();
+}
+
+int launch_linattn_prefill_tc_static(const void* q, const void* k, const void* v, void* y, void* kv_state,
+                                     void* k_state, int B, int H, int L, int dv, Strides3 sq, Strides3 sk,
+                                     Strides3 sv, Strides3 sy, int state_dtype, float eps, int nseg,
+                                     cudaStream_t stream) {
+  if (linattn_prefill_tc_scratch_bytes(B, H, L, dv, nseg) > (size_t)BASED_STATIC_SCRATCH_BYTES)
+    return BASED_ERR_TOO_LARGE;
+  // The symbol's address, resolved once per device (each device has its own copy of the array).
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* addr[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return BASED_ERR_TOO_LARGE;
+  void* scratch;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (addr[dev] == nullptr) {
+      e = cudaGetSymbolAddress(&addr[dev], g_static_scratch);
+      if (e != cudaSuccess) {
+        addr[dev] = nullptr;
+        return (int)e;
+      }
+    }
+    scratch = addr[dev];
+  }
+  return launch_linattn_prefill_tc(q, k, v, y, kv_state, k_state, B, H, L, dv, sq, sk, sv, sy, state_dtype, eps, nseg,
+                                   scratch, BASED_STATIC_SCRATCH_BYTES, stream);
 }
 
 }  // namespace based

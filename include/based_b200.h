@@ -119,6 +119,33 @@ int based_linattn_prefill_split(const void* q, const void* k, const void* v, voi
                                 void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * based_linattn_prefill_split without a workspace argument and without any allocation: the
+ * per-segment states live in an array built into the library, BASED_STATIC_SCRATCH_BYTES
+ * (8 MiB) of device memory per GPU, reserved when the library's module is loaded.  No
+ * counterpart in the reference; it serves callers that must not allocate, e.g. inside a
+ * captured stream or a serving loop with a fixed memory plan.
+ *
+ *  - Arguments and results are those of based_linattn_prefill_split (bit-identical outputs).
+ *  - A call whose based_linattn_prefill_scratch_bytes(B, H, L, dv, nseg) exceeds
+ *    BASED_STATIC_SCRATCH_BYTES returns BASED_ERR_TOO_LARGE before any launch.
+ *  - Nothing in the array has to start at zero and no call leaves state behind in it: every
+ *    word a call reads, it has written first.
+ *  - The first call on each device looks up the array's address (cudaGetSymbolAddress, return
+ *    code checked) and keeps it; make that first call before any stream capture begins.  Later
+ *    calls only launch kernels and may be captured.
+ *  - All calls on one device share the one array: two calls that can run at the same time
+ *    (different streams, or graphs replayed concurrently) race on it.  Order them on one stream,
+ *    or give the overlapping ones their own workspace through based_linattn_prefill_split.
+ */
+#define BASED_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int based_linattn_prefill_split_static(const void* q, const void* k, const void* v, void* y,
+                                       void* kv_state, void* k_state,
+                                       int B, int H, int L, int d, int dv,
+                                       const int64_t q_strides[3], const int64_t k_strides[3],
+                                       const int64_t v_strides[3], const int64_t y_strides[3],
+                                       int state_dtype, float eps, int nseg, void* stream);
+
+/*
  * One recurrent decode step; updates kv_state and k_state IN PLACE.
  *
  * Replaces TaylorExp.forward on q and k (linear_attention.py:139) followed by
