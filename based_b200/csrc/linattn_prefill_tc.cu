@@ -19,8 +19,7 @@
 // weight 1/(4 sqrt2) on the diagonal and 1/4 off it, 153 features padded to 160.  phi'(q).phi'(k)
 // equals phi(q).phi(k) of the 273-feature map exactly; the 273-wide reference layout is restored
 // only when the final state is written.
-#include "common.cuh"
-#include "tcgen05.cuh"
+#include "linattn_tc_shared.cuh"
 
 #include <mutex>
 #include <type_traits>
@@ -43,13 +42,8 @@ __device__ unsigned long long g_tc_trace[5][32];
 namespace {
 
 using namespace tc;
+using namespace tcp;
 
-constexpr int C = 128;     // tokens per chunk
-constexpr int DR = 160;    // packed + padded feature count
-// threads per CTA: 4 expansion warps (0-3), 4 polynomial / state-drain warps (4-7), 4 output warps (8-11),
-// the MMA warp (12), 3 load warps (13-15).  A compute warp w reaches TMEM lanes 32*(w%4)..+31.
-constexpr int NT = 512;
-constexpr int W_OUT = 8, W_MMA = 12, W_LOAD = 13;
 
 // Shared memory map (bytes).  One stage = Q [128 tok x 16] K-major (4096) + K (4096) +
 // V' MN-major [NV/8 groups of 8 columns][128 tok][16 B].  The state-update MMA reads V'^T as an
@@ -69,7 +63,6 @@ struct Smem {
     total = bar + 256;
   }
 };
-constexpr int STAGE_STRIDE_F = 164;  // floats per row of the final fp32 staging (conflict-free 16 B stores)
 
 // TMEM columns (32-bit each), 512 allocated
 constexpr uint32_t TM_ST = 0;     // state^T accumulator: lanes = V' column, 160 feature columns, fp32
@@ -82,121 +75,6 @@ constexpr uint32_t TM_COLS = 512;
 enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_P_READY, B_O_DONE, B_ST_DONE, B_PQ_READY, B_PK_READY,
            B_STB_READY, B_O_FREE, B_PK_FREE, B_PK_FREE1, B_INIT, B_FIN, B_COUNT };
 
-template <int G0, int G1, typename F>
-__device__ __forceinline__ void static_for(F&& f) {
-  if constexpr (G0 < G1) {
-    f(std::integral_constant<int, G0>{});
-    static_for<G0 + 1, G1>(f);
-  }
-}
-
-// ---------------------------------------------------------------- packed feature map, bf16x2 arithmetic
-// Feature order of phi' (160 features = 80 bf16x2 words; u = x/2, c = 1/sqrt2):
-//   0        : 1            (features 1..7 are zero padding)
-//   8  + i   : u_i                                  i = 0..15      (= x_i / 2)
-//   24 + a   : c * u_a^2                            a = 0..15      (= x_a^2 / (4 sqrt2))
-//   40 + m   : u_{2m} u_{2m+1}                      m = 0..7
-//   48 + 4*blk(m,n) + 2*(a&1) + (b&1) : u_a u_b     a in pair m, b in pair n, m < n,
-//                                                   blk(m,n) = 7m - m(m-1)/2 + (n - m - 1)
-// Off-diagonal products appear once with weight 1/4 = sqrt2 * 1/(4 sqrt2), so that
-// phi'(q).phi'(k) = 1 + s + s^2/2 (s = q.k/4) exactly as for the 273-feature map.
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("fma.rn.bf16x2 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-// pair-block number blk = 0..27 -> (m, n), m < n
-__host__ __device__ constexpr int blk_m(int blk) {
-  int m = 0;
-  while (blk >= 7 - m) { blk -= 7 - m; ++m; }
-  return m;
-}
-__host__ __device__ constexpr int blk_n(int blk) {
-  int m = 0;
-  while (blk >= 7 - m) { blk -= 7 - m; ++m; }
-  return m + 1 + blk;
-}
-constexpr uint32_t kHalf2 = 0x3F003F00u;    // (0.5, 0.5)
-constexpr uint32_t kRsqrt2_2 = 0x3F353F35u; // (0.70703125, 0.70703125): bf16(1/sqrt2)
-constexpr uint32_t kOneLo = 0x00003F80u;    // (1.0, 0)
-
-// Expands one token: X = the 16 raw bf16 values as 8 packed words.  emit(G, w0, w1, w2, w3) is
-// called for G = 0..19 in order with the four words of feature group G (features 8G .. 8G+7).
-template <typename Emit>
-__device__ __forceinline__ void expand_packed(const uint32_t (&X)[8], Emit&& emit) {
-  uint32_t U[8];
-#pragma unroll
-  for (int m = 0; m < 8; ++m) U[m] = mul_bf16x2(X[m], kHalf2);
-  emit(std::integral_constant<int, 0>{}, kOneLo, 0u, 0u, 0u);
-  emit(std::integral_constant<int, 1>{}, U[0], U[1], U[2], U[3]);
-  emit(std::integral_constant<int, 2>{}, U[4], U[5], U[6], U[7]);
-  {
-    uint32_t d[8];
-#pragma unroll
-    for (int m = 0; m < 8; ++m) d[m] = mul_bf16x2(mul_bf16x2(U[m], U[m]), kRsqrt2_2);
-    emit(std::integral_constant<int, 3>{}, d[0], d[1], d[2], d[3]);
-    emit(std::integral_constant<int, 4>{}, d[4], d[5], d[6], d[7]);
-  }
-  {
-    uint32_t w[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j)  // (u_{4j} u_{4j+1}, u_{4j+2} u_{4j+3})
-      w[j] = mul_bf16x2(__byte_perm(U[2 * j], U[2 * j + 1], 0x5410), __byte_perm(U[2 * j], U[2 * j + 1], 0x7632));
-    emit(std::integral_constant<int, 5>{}, w[0], w[1], w[2], w[3]);
-  }
-  // cross blocks (m < n), two blocks (four words) per group
-  static_for<0, 14>([&](auto GG) {
-    constexpr int g = decltype(GG)::value;
-    constexpr int m0 = blk_m(2 * g), n0 = blk_n(2 * g), m1 = blk_m(2 * g + 1), n1 = blk_n(2 * g + 1);
-    const uint32_t w0 = mul_bf16x2(__byte_perm(U[m0], 0, 0x1010), U[n0]);
-    const uint32_t w1 = mul_bf16x2(__byte_perm(U[m0], 0, 0x3232), U[n0]);
-    const uint32_t w2 = mul_bf16x2(__byte_perm(U[m1], 0, 0x1010), U[n1]);
-    const uint32_t w3 = mul_bf16x2(__byte_perm(U[m1], 0, 0x3232), U[n1]);
-    emit(std::integral_constant<int, 6 + g>{}, w0, w1, w2, w3);
-  });
-}
-
-// Index of full feature f (0..272) in the packed vector, and whether it is an off-diagonal
-// second-order term (whose packed value is sqrt2 times the full-map value).
-__device__ __forceinline__ int packed_index(int f, bool& offdiag) {
-  offdiag = false;
-  if (f == 0) return 0;
-  if (f < 17) return 8 + (f - 1);
-  const int g = f - 17, i = g >> 4, j = g & 15;
-  const int a = min(i, j), b = max(i, j);
-  if (a == b) return 24 + a;
-  offdiag = true;
-  const int m = a >> 1, n = b >> 1;
-  if (m == n) return 40 + m;
-  const int blk = 7 * m - (m * (m - 1)) / 2 + (n - m - 1);
-  return 48 + 4 * blk + 2 * (a & 1) + (b & 1);
-}
-
-struct Params {
-  const __nv_bfloat16 *q, *k, *v;
-  __nv_bfloat16* y;
-  void *kv_state, *k_state;
-  int H, L, dv, state_bf16;
-  Strides3 sq, sk, sv, sy;
-  float eps;
-  unsigned int* status;
-  // Sequence split.  The sequence is cut into nseg segments of seg_chunks chunks and the grid is
-  // (batch x head) x grid_segs CTAs, one segment each.
-  //   mode 0: grid_segs = nseg = 1, the whole sequence in one CTA.
-  //   mode 1: segments 0 .. nseg-2 only accumulate their own state^T (packed features, fp32) and
-  //           write it to seg_state[bh][seg][dv+1][160]; no outputs.
-  //   mode 2: every segment computes its outputs; segment s > 0 starts from seg_state[bh][s-1],
-  //           which by then holds the sum over the segments before it (see segment_scan_kernel);
-  //           the last segment writes kv_state / k_state.
-  int mode, nseg, grid_segs, seg_chunks;
-  float* seg_state;
-};
-constexpr int MODE_WHOLE = 0, MODE_SEG_STATE = 1, MODE_SEG_OUTPUT = 2;
 
 __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -331,7 +209,17 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       auto mwait = [&](int i, uint32_t parity, unsigned int code) {
         const long long t0 = clock64();
         mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
-        tr_wsum += clock64() - t0;
+        const unsigned long long dt = clock64() - t0;
+        tr_wsum += dt;
+        switch (code & 15u) {  // constant slot numbers keep the counters in registers
+          case 1: tr_wait[1] += dt; break;   // P_READY
+          case 2: tr_wait[2] += dt; break;   // O_FREE
+          case 3: tr_wait[3] += dt; break;   // FULL (next chunk)
+          case 4: tr_wait[4] += dt; break;   // PQ_READY
+          case 5: tr_wait[5] += dt; break;   // STB_READY
+          case 6: tr_wait[6] += dt; break;   // PK_READY
+          default: break;
+        }
       };
 #else
       auto mwait = [&](int i, uint32_t parity, unsigned int code) {
@@ -682,7 +570,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       if (!last) {
         TR_BEGIN();
 #pragma unroll 1
-        for (int i = 0; i < 5; ++i) {  // 32 feature columns per round trip
+        for (int i = 0; i < (qd * 32 < NV ? 5 : 0); ++i) {  // 32 feature columns per round trip; warp-uniform skip of a quadrant without state rows
           uint32_t r0[16], r1[16];
           TR2_BEGIN();
           tmem_ld16(tlane + TM_ST + 32 * i, r0);
@@ -852,11 +740,14 @@ int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void*
   p.nseg = nseg;
   p.seg_chunks = seg_chunks;
   p.seg_state = static_cast<float*>(scratch);
+  auto launch_outputs = [&](int grid) -> int {
+    linattn_prefill_tc_kernel<<<grid, NT, lay.total, stream>>>(p);
+    return (int)cudaGetLastError();
+  };
   if (nseg == 1) {
     p.mode = MODE_WHOLE;
     p.grid_segs = 1;
-    linattn_prefill_tc_kernel<<<B * H, NT, lay.total, stream>>>(p);
-    return (int)cudaGetLastError();
+    return launch_outputs(B * H);
   }
   // Three launches: per-segment states, their running sum, then the outputs of every segment.
   if ((int64_t)B * H * nseg > 0x7fffffff) return BASED_ERR_SHAPE;
@@ -871,8 +762,7 @@ int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void*
     segment_scan_kernel<<<dim3((per + 255) / 256, B * H), 256, 0, stream>>>(p.seg_state, nseg - 1, per);
   p.mode = MODE_SEG_OUTPUT;
   p.grid_segs = nseg;
-  linattn_prefill_tc_kernel<<<B * H * nseg, NT, lay.total, stream>>>(p);
-  return (int)cudaGetLastError();
+  return launch_outputs(B * H * nseg);
 }
 
 int launch_linattn_prefill_tc_static(const void* q, const void* k, const void* v, void* y, void* kv_state,

@@ -28,9 +28,10 @@ inline EncodeTiledFn encode_fn() {
 }
 
 // bf16 tensor [d3][d2][d1][d0] with d0 contiguous; strides of d1, d2, d3 in ELEMENTS (multiples of 8);
-// box = box0 x box1 x 1 x 1 with 128-byte swizzle (box0 * 2 bytes <= 128).  Returns 0 on success.
-inline int encode_bf16_4d_sw128(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
-                                int64_t s1, int64_t s2, int64_t s3, uint32_t box0, uint32_t box1) {
+// box = box0 x box1 x 1 x 1, with 128-byte swizzle (box0 * 2 bytes <= 128) or, when sw128 is false,
+// rows of box0 elements packed back to back.  Returns 0 on success.
+inline int encode_bf16_4d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
+                          int64_t s1, int64_t s2, int64_t s3, uint32_t box0, uint32_t box1, bool sw128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -1;
   const cuuint64_t dims[4] = {d0, d1, d2, d3};
@@ -38,9 +39,13 @@ inline int encode_bf16_4d_sw128(CUtensorMap* map, const void* base, uint64_t d0,
   const cuuint32_t box[4] = {box0, box1, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, sw128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+inline int encode_bf16_4d_sw128(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
+                                int64_t s1, int64_t s2, int64_t s3, uint32_t box0, uint32_t box1) {
+  return encode_bf16_4d(map, base, d0, d1, d2, d3, s1, s2, s3, box0, box1, true);
 }
 
 // ---------------------------------------------------------------- device
