@@ -213,4 +213,33 @@ int based_swa_decode(const void* q, const void* k_new, const void* v_new, void* 
                            static_cast<cudaStream_t>(stream));
 }
 
+int based_gated_conv_prefill(const void* u1, const void* u2, void* v, void* state, const void* weight,
+                             const void* bias, int B, int L, int di, int k, const int64_t u1_strides[2],
+                             const int64_t u2_strides[2], const int64_t v_strides[2], int io_dtype, int w_dtype,
+                             void* stream) {
+  if (!u1 || !u2 || !v || !weight || !u1_strides || !u2_strides || !v_strides) return BASED_ERR_NULL;
+  if (!dtype_ok(io_dtype) || !dtype_ok(w_dtype)) return BASED_ERR_DTYPE;
+  if (B < 0 || L < 0 || di <= 0 || k < 1 || k > 4) return BASED_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (B == 0) return BASED_OK;
+  if (L == 0) {  // nothing to compute; the state of an empty prompt is all zeros
+    if (state) return (int)cudaMemsetAsync(state, 0, (size_t)B * di * k * dtype_size(io_dtype), st);
+    return BASED_OK;
+  }
+  return launch_gated_conv_prefill(u1, u2, v, state, weight, bias, B, L, di, k, s2(u1_strides), s2(u2_strides),
+                                   s2(v_strides), io_dtype, w_dtype, st);
+}
+
+int based_gated_conv_step(const void* u1, const void* u2, void* y, void* state, const void* weight, const void* bias,
+                          int B, int di, int k, int64_t u1_batch_stride, int64_t u2_batch_stride,
+                          int64_t y_batch_stride, int io_dtype, int w_dtype, void* stream) {
+  if (!u1 || !u2 || !y || !state || !weight) return BASED_ERR_NULL;
+  if (!dtype_ok(io_dtype) || !dtype_ok(w_dtype)) return BASED_ERR_DTYPE;
+  if (B < 0 || di <= 0 || k < 1 || k > 4) return BASED_ERR_SHAPE;
+  if ((int64_t)B * di > 2147483647LL) return BASED_ERR_TOO_LARGE;
+  if (B == 0) return BASED_OK;
+  return launch_gated_conv_step(u1, u2, y, state, weight, bias, B, di, k, u1_batch_stride, u2_batch_stride,
+                                y_batch_stride, io_dtype, w_dtype, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -71,6 +71,13 @@ int launch_linattn_prefill_tc_static(const void* q, const void* k, const void* v
 int linattn_prefill_tc_auto_segments(int B, int H, int L);
 size_t linattn_prefill_tc_scratch_bytes(int B, int H, int L, int dv, int nseg);
 
+int launch_gated_conv_prefill(const void* u1, const void* u2, void* v, void* state, const void* weight,
+                              const void* bias, int B, int L, int di, int k, Strides2 s1, Strides2 s2, Strides2 sv,
+                              int io_dtype, int w_dtype, cudaStream_t stream);
+int launch_gated_conv_step(const void* u1, const void* u2, void* y, void* state, const void* weight, const void* bias,
+                           int B, int di, int k, int64_t s1, int64_t s2, int64_t sy, int io_dtype, int w_dtype,
+                           cudaStream_t stream);
+
 int read_tc_status(unsigned int* out, int reset);      // linear-attention prefill kernel
 int read_tc_status_swa(unsigned int* out, int reset);  // sliding-window prefill kernel
 

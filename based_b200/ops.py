@@ -255,3 +255,73 @@ def rotary_apply_(x: torch.Tensor, rotary_cos: torch.Tensor, rotary_sin: torch.T
             2 * rotary_cos.shape[-1], off_ptr, off_scalar, _dt(x.dtype), _stream())
     _capi.check(code, "based_rotary_apply")
     return x
+
+
+def gated_conv_prefill(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
+                       state: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(causal_depthwise_conv(u1) + bias) * u2`` with ``u1, u2`` the halves of ``u [B, L, 2*di]``.
+
+    ``weight [di, k]`` (or ``[di, 1, k]`` as nn.Conv1d stores it), ``bias [di]`` or None, both in one
+    dtype (float32 or bfloat16).  ``state [B, di, k]`` (dtype of ``u``), when given, receives the
+    last k inputs of the convolution (convolution.py:63-67).  Returns ``v [B, L, di]``.
+    """
+    _need_cuda(u, weight, bias, state)
+    B, L, two_di = u.shape
+    di = two_di // 2
+    weight = weight.reshape(weight.shape[0], -1)
+    k = weight.shape[1]
+    if weight.shape[0] != di or two_di != 2 * di:
+        raise ValueError("u must be [B, L, 2*di] and weight [di, k]")
+    _inner_contig(u, "u")
+    weight = weight.contiguous()
+    if bias is not None:
+        bias = bias.to(weight.dtype).contiguous()
+    if out is None:
+        out = torch.empty(B, L, di, dtype=u.dtype, device=u.device)
+    else:
+        _inner_contig(out, "out")
+    if state is not None and (state.shape != (B, di, k) or state.dtype != u.dtype or not state.is_contiguous()):
+        raise ValueError("state must be a contiguous [B, di, k] tensor of u's dtype")
+    if B == 0 or L == 0:
+        if state is not None:
+            state.zero_()
+        return out
+    u1, u2 = u[..., :di], u[..., di:]
+    with torch.cuda.device(u.device):
+        code = _capi.lib().based_gated_conv_prefill(
+            u1.data_ptr(), u2.data_ptr(), out.data_ptr(), state.data_ptr() if state is not None else None,
+            weight.data_ptr(), bias.data_ptr() if bias is not None else None, B, L, di, k,
+            _capi.strides(*u1.stride()[:2]), _capi.strides(*u2.stride()[:2]), _capi.strides(*out.stride()[:2]),
+            _dt(u.dtype), _dt(weight.dtype), _stream())
+    _capi.check(code, "based_gated_conv_prefill")
+    return out
+
+
+def gated_conv_step(u: torch.Tensor, state: torch.Tensor, weight: torch.Tensor,
+                    bias: Optional[torch.Tensor] = None, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One decode step of :func:`gated_conv_prefill`; ``state [B, di, k]`` is updated IN PLACE
+    (convolution.py:104-107).  ``u [B, 2*di]`` or ``[B, 1, 2*di]``; returns ``[B, di]``."""
+    _need_cuda(u, state, weight, bias)
+    if u.dim() == 3:
+        u = u[:, 0]
+    B, two_di = u.shape
+    di = two_di // 2
+    weight = weight.reshape(weight.shape[0], -1).contiguous()
+    k = weight.shape[1]
+    _inner_contig(u, "u")
+    if bias is not None:
+        bias = bias.to(weight.dtype).contiguous()
+    if state.shape != (B, di, k) or state.dtype != u.dtype or not state.is_contiguous():
+        raise ValueError("state must be a contiguous [B, di, k] tensor of u's dtype")
+    if out is None:
+        out = torch.empty(B, di, dtype=u.dtype, device=u.device)
+    if B == 0:
+        return out
+    u1, u2 = u[:, :di], u[:, di:]
+    with torch.cuda.device(u.device):
+        code = _capi.lib().based_gated_conv_step(
+            u1.data_ptr(), u2.data_ptr(), out.data_ptr(), state.data_ptr(), weight.data_ptr(),
+            bias.data_ptr() if bias is not None else None, B, di, k, u1.stride(0), u2.stride(0), out.stride(0),
+            _dt(u.dtype), _dt(weight.dtype), _stream())
+    _capi.check(code, "based_gated_conv_step")
+    return out

@@ -1,7 +1,8 @@
 /*
  * based_b200 — C ABI of the B200 (sm_100a) kernels for the Based hot path:
- * Taylor-feature-map linear attention (prefill + recurrent decode step) and
- * sliding-window softmax attention (prefill + decode step).
+ * Taylor-feature-map linear attention (prefill + recurrent decode step),
+ * sliding-window softmax attention (prefill + decode step) and the gated short
+ * convolution of the BaseConv mixer (prefill + decode step).
  *
  * Conventions shared by every entry point
  * ---------------------------------------
@@ -219,6 +220,47 @@ int based_swa_decode(const void* q, const void* k_new, const void* v_new, void* 
                      const int64_t q_strides[2], const int64_t k_strides[2],
                      const int64_t v_strides[2], const int64_t o_strides[2],
                      int window_left, float softmax_scale, int io_dtype, void* stream);
+
+/*
+ * Gated short causal convolution of the BaseConv mixer, whole sequence:
+ *   v[b, l, c] = silu(sum_j weight[c, j] * u1[b, l - (k-1) + j, c] + bias[c]) * u2[b, l, c]
+ * with zeros before the start of the sequence.
+ *
+ * Replaces ShortConvolution.forward (based/models/mixers/convolution.py:47-86: depthwise
+ * nn.Conv1d, padding k-1, truncated to the sequence; state fill :63-67) plus the silu and the
+ * gate of BaseConv.forward (:205-211), the site where the reference optionally calls the
+ * external causal_conv1d_fn (:76-83).
+ *
+ *   u1, u2, v  [B, L, di]; *_strides = (batch, seq) element strides, channel stride 1
+ *              (u1 and u2 are normally the two halves of in_proj's output [B, L, 2*di])
+ *   weight     [di, k] (conv.weight with its singleton dim dropped), bias [di] or NULL;
+ *              both of dtype w_dtype
+ *   state      [B, di, k] contiguous in io_dtype, or NULL: receives the last k inputs u1,
+ *              oldest first, zeros in front when L < k (what the decode step continues from)
+ *   k in [1, 4]; di a multiple of 8 (bf16) / 4 (fp32); u1, u2, v 16-byte aligned with
+ *   strides that are multiples of 8 / 4 elements.
+ */
+int based_gated_conv_prefill(const void* u1, const void* u2, void* v, void* state,
+                             const void* weight, const void* bias,
+                             int B, int L, int di, int k,
+                             const int64_t u1_strides[2], const int64_t u2_strides[2],
+                             const int64_t v_strides[2],
+                             int io_dtype, int w_dtype, void* stream);
+
+/*
+ * One decode step of the same op; updates `state` IN PLACE (shift left by one, append u1).
+ *
+ * Replaces ShortConvolution.step (convolution.py:88-109) plus silu and gate (:208-211).
+ * The reference's torch step (:104-107) does not add the convolution bias; it has none with
+ * the default conv_bias=False.  Here a non-NULL bias is added, as in the whole-sequence call.
+ *
+ *   u1, u2, y [B, di] with the given batch strides (channel stride 1); state [B, di, k].
+ */
+int based_gated_conv_step(const void* u1, const void* u2, void* y, void* state,
+                          const void* weight, const void* bias,
+                          int B, int di, int k,
+                          int64_t u1_batch_stride, int64_t u2_batch_stride, int64_t y_batch_stride,
+                          int io_dtype, int w_dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -298,3 +298,75 @@ def swa_decode_step(
             q[b : b + 1], kk.to(q.dtype), vv.to(q.dtype), window_left, softmax_scale
         )
     return out
+
+
+# --------------------------------------------------------------------------
+# BaseConv: gated short causal convolution
+#   based/models/mixers/convolution.py:16-217; pinned by tests/golden/baseconv.npz
+def gated_conv_prefill(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``v = silu(causal_depthwise_conv(u1)) * u2`` with ``u1, u2 = split(u)`` over the last dim.
+
+    u ``[B, L, 2*di]`` (the output of in_proj, convolution.py:205-206), weight ``[di, k]``
+    (``conv.weight`` squeezed, :37-44), bias ``[di]`` or None.  The convolution is
+    nn.Conv1d with groups = channels and padding k-1 truncated to L (:84), i.e.
+    ``c[b, l, ch] = sum_j weight[ch, j] * u1[b, l - (k-1) + j, ch]`` with zeros before the
+    start; then silu (:208-210) and the gate (:211).
+    """
+    B, L, two_di = u.shape
+    di, k = weight.shape
+    assert two_di == 2 * di
+    u1, u2 = u[..., :di], u[..., di:]
+    c = torch.zeros(B, L, di, dtype=u.dtype)
+    for j in range(k):
+        shift = k - 1 - j  # tap j looks `shift` tokens back
+        if shift < L:
+            c[:, shift:, :] += weight[:, j].to(u.dtype) * u1[:, : L - shift, :]
+    if bias is not None:
+        c = c + bias.to(u.dtype)
+    return torch.nn.functional.silu(c) * u2
+
+
+def conv_state_from_prompt(u1: torch.Tensor, k: int) -> torch.Tensor:
+    """State ``[B, di, k]`` after a prompt: the last k inputs of the convolution, oldest first,
+    zeros in front when the prompt is shorter than k (convolution.py:63-67, allocation :111-119)."""
+    B, L, di = u1.shape
+    state = torch.zeros(B, di, k, dtype=u1.dtype)
+    n = min(k, L)
+    state[..., k - n:] = u1[:, L - n:, :].transpose(1, 2)
+    return state
+
+
+def gated_conv_step(u_t: torch.Tensor, state: torch.Tensor, weight: torch.Tensor,
+                    bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One decode step; ``state [B, di, k]`` is updated IN PLACE.
+
+    u_t ``[B, 2*di]``.  The state is shifted left by one, the new input goes last, the
+    output is the dot product with the taps (convolution.py:104-107), then silu and the
+    gate (:208-211).  The reference's step ignores the convolution bias on this path
+    (:106); with the default ``conv_bias=False`` there is none.  ``bias`` is applied
+    here when given so that step and prefill agree.
+    """
+    di, k = weight.shape
+    u1, u2 = u_t[..., :di], u_t[..., di:]
+    state.copy_(torch.roll(state, shifts=-1, dims=-1))
+    state[:, :, -1] = u1
+    c = (state * weight.to(state.dtype)).sum(-1)
+    if bias is not None:
+        c = c + bias.to(c.dtype)
+    return torch.nn.functional.silu(c).to(u_t.dtype) * u2
+
+
+def baseconv_forward(params: dict, x: torch.Tensor, state: Optional[torch.Tensor] = None,
+                     step: bool = False) -> torch.Tensor:
+    """BaseConv.forward (convolution.py:197-213): in_proj, gated convolution, out_proj.
+    ``params``: in_w, in_b, conv_w ``[di, 1, k]``, out_w, out_b.  With ``state`` given and
+    ``step`` false the state is filled from the prompt; with ``step`` true x is ``[B, 1, d]``."""
+    w = params["conv_w"].reshape(params["conv_w"].shape[0], -1)
+    u = x @ params["in_w"].T + params["in_b"]
+    if step:
+        v = gated_conv_step(u[:, 0], state, w).unsqueeze(1)
+    else:
+        v = gated_conv_prefill(u, w)
+        if state is not None:
+            state.copy_(conv_state_from_prompt(u[..., : w.shape[0]], w.shape[1]))
+    return v @ params["out_w"].T + params["out_b"]

@@ -42,7 +42,8 @@ def import_reference(ref_root):
 
 
 def t2n(t):
-    return t.detach().to(torch.float64 if t.dtype == torch.float64 else torch.float32).numpy()
+    # clone: states are updated in place later, and .numpy() would alias them
+    return t.detach().to(torch.float64 if t.dtype == torch.float64 else torch.float32).clone().numpy()
 
 
 def feature_map_case(TaylorExp):
@@ -128,6 +129,44 @@ def config1_samples(LinearAttention, TaylorExp, InferenceParams):
              y_abs_mean=np.float64(y.abs().mean().item()))
 
 
+def baseconv_case(ref_root, InferenceParams):
+    """Reference BaseConv (based/models/mixers/convolution.py:174-217): train path, prefill with
+    state, three decode steps, and a prompt shorter than the kernel."""
+    import contextlib
+    import io
+
+    with contextlib.redirect_stdout(io.StringIO()):
+        from based.models.mixers.convolution import BaseConv
+    torch.manual_seed(11)
+    d, L, B = 64, 37, 2
+    m = BaseConv(d_model=d, l_max=128, kernel_size=3, layer_idx=0).double()
+    x = torch.randn(B, L, d, dtype=torch.float64)
+    out = {"in_w": t2n(m.in_proj.weight), "in_b": t2n(m.in_proj.bias), "conv_w": t2n(m.conv.conv.weight),
+           "out_w": t2n(m.out_proj.weight), "out_b": t2n(m.out_proj.bias), "x": t2n(x)}
+    out["y_train"] = t2n(m(x))
+    # the op the kernel replaces, isolated: u = in_proj(x) -> v = silu(conv(u1)) * u2
+    u = m.in_proj(x)
+    u1, u2 = torch.split(u, m.d_inner, dim=-1)
+    out["u"] = t2n(u)
+    out["v"] = t2n(torch.nn.functional.silu(m.conv(u1)) * u2)
+    ip = InferenceParams(max_seqlen=128, max_batch_size=B)
+    out["y_prefill"] = t2n(m(x, inference_params=ip))
+    out["state_prefill"] = t2n(ip.key_value_memory_dict[0]["conv"])
+    for i in range(3):
+        ip.seqlen_offset = L + i
+        xt = torch.randn(B, 1, d, dtype=torch.float64)
+        out[f"x_step{i}"] = t2n(xt)
+        out[f"y_step{i}"] = t2n(m(xt, inference_params=ip))
+        out[f"state_step{i}"] = t2n(ip.key_value_memory_dict[0]["conv"])
+    # prompt of 2 tokens with kernel_size 3: the state keeps a leading zero
+    ip2 = InferenceParams(max_seqlen=128, max_batch_size=B)
+    xs = torch.randn(B, 2, d, dtype=torch.float64)
+    out["x_short"] = t2n(xs)
+    out["y_short"] = t2n(m(xs, inference_params=ip2))
+    out["state_short"] = t2n(ip2.key_value_memory_dict[0]["conv"])
+    np.savez(os.path.join(HERE, "baseconv.npz"), **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("BASED_REFERENCE"))
@@ -141,6 +180,7 @@ def main():
         qkv_level_case(LA, TE, IP, "linattn_qkv_f32_dv112.npz", B=1, H=2, L=130, dv=112, steps=2, dtype=torch.float32)
         mixer_level_case(LA, TE, IP)
         config1_samples(LA, TE, IP)
+        baseconv_case(args.ref, IP)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -64,3 +64,19 @@ def test_inference_params_mirror():
     ip.reset(20, 4)
     assert (ip.max_seqlen, ip.max_batch_size, ip.seqlen_offset) == (20, 4, 0)
     assert ip.key_value_memory_dict == {}
+
+
+def test_baseconv_mirror_keeps_the_reference_interface():
+    """Parameter names / shapes and cache layout of based/models/mixers/convolution.py:174-217; no CPU path."""
+    import pytest
+    import torch
+    from based_b200.mixers import BaseConv
+    m = BaseConv(d_model=64, l_max=128, kernel_size=3, layer_idx=4)
+    sd = {k: tuple(v.shape) for k, v in m.state_dict().items()}
+    assert sd == {"in_proj.weight": (128, 64), "in_proj.bias": (128,), "out_proj.weight": (64, 64),
+                  "out_proj.bias": (64,), "conv.conv.weight": (64, 1, 3)}
+    cache = m.allocate_inference_cache(batch_size=3, max_seqlen=128)
+    assert set(cache) == {"conv"} and cache["conv"].shape == (3, 64, 3)
+    assert m.conv.layer_idx == (4, "conv")
+    with pytest.raises(RuntimeError):  # CPU tensors are refused, there is no fallback
+        m(torch.randn(1, 5, 64))

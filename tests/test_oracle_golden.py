@@ -124,3 +124,24 @@ def test_swa_decode_matches_flash_attn():
         assert rel_err(out.float(), g["d_out"][s]) < 1e-2, s
         lens = lens + 1
     assert rel_err(cache.float(), g["d_cache_out"]) < 1e-2
+
+
+def test_baseconv_oracle_matches_reference_golden():
+    """Gated short convolution: train path, prefill + state, three steps, a prompt shorter than the kernel."""
+    g = load_golden("baseconv.npz")
+    T = {k: torch.as_tensor(v) for k, v in g.items()}
+    params = {k: T[k] for k in ("in_w", "in_b", "conv_w", "out_w", "out_b")}
+    w = T["conv_w"].reshape(T["conv_w"].shape[0], -1)
+    assert rel_err(O.gated_conv_prefill(T["u"], w), T["v"]) < 1e-12
+    assert rel_err(O.baseconv_forward(params, T["x"]), T["y_train"]) < 1e-12
+    state = torch.zeros_like(T["state_prefill"])
+    assert rel_err(O.baseconv_forward(params, T["x"], state=state), T["y_prefill"]) < 1e-12
+    assert torch.equal(state, T["state_prefill"])
+    for i in range(3):
+        y = O.baseconv_forward(params, T[f"x_step{i}"], state=state, step=True)
+        assert rel_err(y, T[f"y_step{i}"]) < 1e-12
+        assert torch.equal(state, T[f"state_step{i}"])
+    short = torch.zeros_like(T["state_short"])
+    assert rel_err(O.baseconv_forward(params, T["x_short"], state=short), T["y_short"]) < 1e-12
+    assert torch.equal(short, T["state_short"])
+    assert (short[..., 0] == 0).all()
