@@ -6,9 +6,9 @@
 // separate torch ops (or hands to the external causal_conv1d kernels, :9-13, :76-83).
 //
 // HBM-bound elementwise work: per (token, channel) one u1 and one u2 element in, one out.  A
-// thread owns one 16-byte vector of channels and walks a tile of tokens with the k-1 previous
-// inputs in registers, so u1 is read once (plus k-1 halo rows per tile); a warp's accesses are
-// 512 contiguous bytes per row.
+// thread owns four consecutive tokens of one 16-byte vector of channels; a warp's accesses are
+// 512 contiguous bytes per row, and the k-1 rows before a thread's first token are rows its
+// neighbour loads as well (L1/L2 hits).
 #include "common.cuh"
 
 namespace based {
@@ -19,9 +19,8 @@ struct Vec;  // 16 bytes of T
 template <>
 struct Vec<float> {
   static constexpr int N = 4;
-  static __device__ __forceinline__ void load(const float* p, float (&x)[4]) {
-    const float4 v = *reinterpret_cast<const float4*>(p);
-    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+  static __device__ __forceinline__ void unpack(const uint4& v, float (&x)[4]) {
+    x[0] = __uint_as_float(v.x); x[1] = __uint_as_float(v.y); x[2] = __uint_as_float(v.z); x[3] = __uint_as_float(v.w);
   }
   static __device__ __forceinline__ void store(float* p, const float (&x)[4]) {
     *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
@@ -30,8 +29,7 @@ struct Vec<float> {
 template <>
 struct Vec<__nv_bfloat16> {
   static constexpr int N = 8;
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&x)[8]) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p);
+  static __device__ __forceinline__ void unpack(const uint4& v, float (&x)[8]) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -63,7 +61,7 @@ __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return
 __device__ __forceinline__ float load_w(const void* w, int w_bf16, int i) {
   return w_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(w)[i]) : static_cast<const float*>(w)[i];
 }
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 struct ConvParams {
   const void *u1, *u2, *weight, *bias;
@@ -72,85 +70,100 @@ struct ConvParams {
   Strides2 s1, s2, sv;  // .b = batch stride, .h = token stride (elements)
 };
 
-constexpr int TL = 32;  // tokens per block
-constexpr int NTH = 128;
+constexpr int TT = 4;     // consecutive tokens per thread
+constexpr int TY = 2;     // token groups per block (threadIdx.y)
+constexpr int NTH = 128;  // channel vectors per block (threadIdx.x)
 
-// grid = (ceil(di / (N * NTH)), ceil(L / TL), B)
+// The N * K taps of N consecutive channels, [channel][tap] as the weight tensor stores them.
+template <int N, int K>
+__device__ __forceinline__ void load_taps(const void* weight, int w_bf16, int ch, float (&w)[N][K]) {
+  if (w_bf16 && (N * K * 2) % 16 == 0) {  // whole 16-byte vectors (ch is a multiple of N)
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(weight) + (int64_t)ch * K);
+    float flat[N * K];
+#pragma unroll
+    for (int q = 0; q < N * K / 8; ++q) {
+      const uint4 x = __ldg(src + q);
+      const uint32_t r[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        flat[8 * q + 2 * e] = __uint_as_float(r[e] << 16);
+        flat[8 * q + 2 * e + 1] = __uint_as_float(r[e] & 0xFFFF0000u);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+#pragma unroll
+      for (int j = 0; j < K; ++j) w[i][j] = flat[i * K + j];
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+#pragma unroll
+      for (int j = 0; j < K; ++j) w[i][j] = load_w(weight, w_bf16, (ch + i) * K + j);
+  }
+}
+
+// One thread per (TT consecutive tokens, 16-byte vector of channels).  All its loads -- the K-1
+// rows before its first token, TT rows of u1, TT rows of u2 -- are issued before any arithmetic
+// and stay packed in registers until used, so a thread keeps 2 TT + K - 1 16-byte loads in flight
+// with a small register count; there is no loop-carried state.
+// grid = (ceil(di / (N * NTH)), ceil(L / (TT * TY)), B), block = (NTH, TY)
 template <typename T, int K>
-__global__ void __launch_bounds__(NTH) gated_conv_prefill_kernel(const ConvParams p) {
+__global__ void __launch_bounds__(NTH * TY, 3) gated_conv_prefill_kernel(const ConvParams p) {
   constexpr int N = Vec<T>::N;
   const int ch = (blockIdx.x * NTH + threadIdx.x) * N;
-  if (ch >= p.di) return;
-  const int b = blockIdx.z, l0 = blockIdx.y * TL, l1 = min(l0 + TL, p.L);
+  const int l0 = (blockIdx.y * TY + threadIdx.y) * TT, b = blockIdx.z;
+  if (ch >= p.di || l0 >= p.L) return;
   const T* u1 = static_cast<const T*>(p.u1) + b * p.s1.b + ch;
   const T* u2 = static_cast<const T*>(p.u2) + b * p.s2.b + ch;
-  T* v = static_cast<T*>(p.v) + b * p.sv.b + ch;
+  // rows[r] = packed input of token l0 - (K-1) + r (zeros outside the sequence); gate[t] of token l0 + t
+  uint4 rows[K - 1 + TT], gate[TT];
+#pragma unroll
+  for (int r = 0; r < K - 1 + TT; ++r) {
+    const int l = l0 - (K - 1) + r;
+    rows[r] = (l >= 0 && l < p.L) ? *reinterpret_cast<const uint4*>(u1 + (int64_t)l * p.s1.h) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int t = 0; t < TT; ++t)
+    gate[t] = (l0 + t < p.L) ? *reinterpret_cast<const uint4*>(u2 + (int64_t)(l0 + t) * p.s2.h) : make_uint4(0, 0, 0, 0);
   float w[N][K], bias[N];
+  load_taps<N, K>(p.weight, p.w_bf16, ch, w);
 #pragma unroll
-  for (int i = 0; i < N; ++i) {
+  for (int i = 0; i < N; ++i) bias[i] = p.bias ? load_w(p.bias, p.w_bf16, ch + i) : 0.f;
+  T* v = static_cast<T*>(p.v) + b * p.sv.b + ch;
 #pragma unroll
-    for (int j = 0; j < K; ++j) w[i][j] = load_w(p.weight, p.w_bf16, (ch + i) * K + j);
-    bias[i] = p.bias ? load_w(p.bias, p.w_bf16, ch + i) : 0.f;
-  }
-  // hist[j] = input of token l - (K-1) + j; the halo before the tile (zeros before the sequence)
-  float hist[K][N];
+  for (int t = 0; t < TT; ++t) {
+    if (l0 + t < p.L) {
+      float c[N], x[N];
 #pragma unroll
-  for (int j = 0; j < K - 1; ++j) {
-    const int l = l0 - (K - 1) + j;
-    if (l >= 0) {
-      Vec<T>::load(u1 + (int64_t)l * p.s1.h, hist[j]);
-    } else {
+      for (int i = 0; i < N; ++i) c[i] = bias[i];
 #pragma unroll
-      for (int i = 0; i < N; ++i) hist[j][i] = 0.f;
-    }
-  }
-  constexpr int U = 4;  // tokens per round: their loads are issued together
-  for (int l = l0; l < l1; l += U) {
-    float a[U][N], g[U][N];
+      for (int j = 0; j < K; ++j) {
+        Vec<T>::unpack(rows[t + j], x);
 #pragma unroll
-    for (int r = 0; r < U; ++r) {
-      if (l + r < l1) {
-        Vec<T>::load(u1 + (int64_t)(l + r) * p.s1.h, a[r]);
-        Vec<T>::load(u2 + (int64_t)(l + r) * p.s2.h, g[r]);
+        for (int i = 0; i < N; ++i) c[i] = fmaf(w[i][j], x[i], c[i]);
       }
-    }
+      Vec<T>::unpack(gate[t], x);
 #pragma unroll
-    for (int r = 0; r < U; ++r) {
-      if (l + r < l1) {
-#pragma unroll
-        for (int i = 0; i < N; ++i) hist[K - 1][i] = a[r][i];
-        float o[N];
-#pragma unroll
-        for (int i = 0; i < N; ++i) {
-          float c = bias[i];
-#pragma unroll
-          for (int j = 0; j < K; ++j) c = fmaf(w[i][j], hist[j][i], c);
-          o[i] = silu(c) * g[r][i];
-        }
-        Vec<T>::store(v + (int64_t)(l + r) * p.sv.h, o);
-#pragma unroll
-        for (int j = 0; j < K - 1; ++j)
-#pragma unroll
-          for (int i = 0; i < N; ++i) hist[j][i] = hist[j + 1][i];
-      }
+      for (int i = 0; i < N; ++i) c[i] = silu(c[i]) * x[i];
+      Vec<T>::store(v + (int64_t)(l0 + t) * p.sv.h, c);
     }
   }
-  // the block with the last token leaves the state: the last K inputs, oldest first, zeros when
-  // the sequence is shorter than K
-  if (p.state != nullptr && l1 == p.L) {
+  // the thread that holds the last token leaves the state: the last K inputs, oldest first
+  // (zeros when L < K); rows[] already has them
+  if (p.state != nullptr && l0 + TT >= p.L) {
     T* st = static_cast<T*>(p.state) + ((int64_t)b * p.di + ch) * K;
+    const int tl = p.L - 1 - l0;  // this thread's index of the last token, 0 .. TT-1
 #pragma unroll
-    for (int j = 0; j < K; ++j) {
-      const int l = p.L - K + j;
-      float x[N];
-      if (l >= 0) {
-        Vec<T>::load(u1 + (int64_t)l * p.s1.h, x);
-      } else {
+    for (int t = 0; t < TT; ++t) {
+      if (t == tl) {
 #pragma unroll
-        for (int i = 0; i < N; ++i) x[i] = 0.f;
+        for (int j = 0; j < K; ++j) {
+          float x[N];
+          Vec<T>::unpack(rows[t + j], x);
+#pragma unroll
+          for (int i = 0; i < N; ++i) st[i * K + j] = from_f<T>(x[i]);
+        }
       }
-#pragma unroll
-      for (int i = 0; i < N; ++i) st[i * K + j] = from_f<T>(x[i]);
     }
   }
 }
@@ -180,12 +193,12 @@ __global__ void __launch_bounds__(256) gated_conv_step_kernel(const ConvParams p
 template <typename T>
 int launch_prefill_t(const ConvParams& p, int k, cudaStream_t stream) {
   constexpr int N = Vec<T>::N;
-  const dim3 grid((p.di / N + NTH - 1) / NTH, (p.L + TL - 1) / TL, p.B);
+  const dim3 grid((p.di / N + NTH - 1) / NTH, (p.L + TT * TY - 1) / (TT * TY), p.B), block(NTH, TY);
   switch (k) {
-    case 1: gated_conv_prefill_kernel<T, 1><<<grid, NTH, 0, stream>>>(p); break;
-    case 2: gated_conv_prefill_kernel<T, 2><<<grid, NTH, 0, stream>>>(p); break;
-    case 3: gated_conv_prefill_kernel<T, 3><<<grid, NTH, 0, stream>>>(p); break;
-    case 4: gated_conv_prefill_kernel<T, 4><<<grid, NTH, 0, stream>>>(p); break;
+    case 1: gated_conv_prefill_kernel<T, 1><<<grid, block, 0, stream>>>(p); break;
+    case 2: gated_conv_prefill_kernel<T, 2><<<grid, block, 0, stream>>>(p); break;
+    case 3: gated_conv_prefill_kernel<T, 3><<<grid, block, 0, stream>>>(p); break;
+    case 4: gated_conv_prefill_kernel<T, 4><<<grid, block, 0, stream>>>(p); break;
     default: return BASED_ERR_SHAPE;
   }
   return (int)cudaGetLastError();
@@ -214,7 +227,7 @@ int launch_gated_conv_prefill(const void* u1, const void* u2, void* v, void* sta
   const int64_t all[] = {s1.b, s1.h, s2.b, s2.h, sv.b, sv.h};
   for (int64_t s : all)
     if (s % N != 0) return BASED_ERR_ALIGN;  // 16-byte vector accesses on every row
-  if (B > 65535 || (L + TL - 1) / TL > 65535) return BASED_ERR_TOO_LARGE;
+  if (B > 65535 || (L + TT * TY - 1) / (TT * TY) > 65535) return BASED_ERR_TOO_LARGE;
   ConvParams p{u1, u2, weight, bias, v, state, B, L, di, w_dtype == BASED_BF16, s1, s2, sv};
   return io_dtype == BASED_BF16 ? launch_prefill_t<__nv_bfloat16>(p, k, stream) : launch_prefill_t<float>(p, k, stream);
 }

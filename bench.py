@@ -158,6 +158,31 @@ def time_kernel(fn, iters, warmup=3):
     return e0.elapsed_time(e1) / iters  # ms
 
 
+def time_graph(fn, iters, replays=3):
+    """Device time per call of a launch too short to time through Python: `iters` calls captured in
+    one CUDA graph on a side stream, the graph replayed between two events."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (iters * replays)  # ms
+
+
 def prefill_sweep(ops, peaks, lengths):
     """Prefill sweep: B=8, H=16, d=16, dv=64, bf16, q/k/v ~ N(0,1)/4; linear attention and window-64 SWA."""
     out_lin, out_swa = [], []
@@ -197,6 +222,24 @@ def prefill_sweep(ops, peaks, lengths):
                         "tensor_frac": units * SWA_FLOP_PER_TOKEN_HEAD / (t * 1e-3) / (peaks["bf16_tflops"] * 1e12)})
         del q, k, v, y, qkv, o
     return out_lin, out_swa
+
+
+def gated_conv_bench(ops, peaks):
+    """BaseConv's gated short convolution at the 360M model's layer size and the generation benchmark's
+    prompt (B=16, L=2048, d_inner=1024, k=3, bf16): algorithmic bytes = 3 elements per (token, channel)."""
+    B, L, di, k = 16, 2048, 1024, 3
+    g = torch.Generator(device="cuda").manual_seed(3)
+    u = torch.randn(B, L, 2 * di, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(di, k, device="cuda", generator=g) * 0.5).bfloat16()
+    out = torch.empty(B, L, di, dtype=torch.bfloat16, device="cuda")
+    state = torch.empty(B, di, k, dtype=torch.bfloat16, device="cuda")
+    t = time_graph(lambda: ops.gated_conv_prefill(u, w, state=state, out=out), 20)
+    nbytes = B * L * di * 3 * 2
+    u_t, y_t = u[:, 0], out[:, 0]
+    ts = time_graph(lambda: ops.gated_conv_step(u_t, state, w, out=y_t), 50)
+    return {"B": B, "L": L, "d_inner": di, "k": k, "ms": t, "tok_per_s": B * L / (t * 1e-3),
+            "hbm_frac": nbytes / (t * 1e-3) / (peaks["hbm_gbs"] * 1e9), "bytes": nbytes,
+            "l2": "working set 201 MB > L2", "timing": "CUDA graph of 20 launches", "step_us": ts * 1e3}
 
 
 def small_batch_prefill(ops, L):
@@ -357,6 +400,7 @@ def main():
             line["prefill"] = lin
             line["swa"] = swa
             line["prefill_small_batch"] = small_batch_prefill(ops, max(lengths))
+            line["gated_conv"] = gated_conv_bench(ops, peaks)
         if world == 1 and not args.no_cpu:
             use_all_host_threads()
             tput, dt = cpu_decode_baseline(B_DEC, 20, 2)
