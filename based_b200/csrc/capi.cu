@@ -242,4 +242,27 @@ int based_gated_conv_step(const void* u1, const void* u2, void* y, void* state, 
                                 y_batch_stride, io_dtype, w_dtype, static_cast<cudaStream_t>(stream));
 }
 
+int based_add_rmsnorm(const void* x, const void* residual, const void* weight, const void* bias, void* out,
+                      void* residual_out, int64_t M, int D, int64_t x_row_stride, int64_t residual_row_stride,
+                      int64_t out_row_stride, int64_t residual_out_row_stride, float eps, int io_dtype, int res_dtype,
+                      int w_dtype, void* stream) {
+  if (!x || !weight || !out) return BASED_ERR_NULL;
+  if (!dtype_ok(io_dtype) || !dtype_ok(res_dtype) || !dtype_ok(w_dtype)) return BASED_ERR_DTYPE;
+  if (M < 0 || D <= 0) return BASED_ERR_SHAPE;
+  if (M == 0) return BASED_OK;
+  return launch_add_rmsnorm(x, residual, weight, bias, out, residual_out, M, D, x_row_stride, residual_row_stride,
+                            out_row_stride, residual_out_row_stride, eps, io_dtype, res_dtype, w_dtype,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int based_gated_act(const void* y, const void* gate, void* out, int64_t M, int F, int64_t y_row_stride,
+                    int64_t gate_row_stride, int64_t out_row_stride, int act, int io_dtype, void* stream) {
+  if (!y || !gate || !out) return BASED_ERR_NULL;
+  if (!dtype_ok(io_dtype)) return BASED_ERR_DTYPE;
+  if (M < 0 || F <= 0 || (act != BASED_ACT_SILU && act != BASED_ACT_SIGMOID)) return BASED_ERR_SHAPE;
+  if (M == 0) return BASED_OK;
+  return launch_gated_act(y, gate, out, M, F, y_row_stride, gate_row_stride, out_row_stride, act, io_dtype,
+                          static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

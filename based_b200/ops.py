@@ -325,3 +325,62 @@ def gated_conv_step(u: torch.Tensor, state: torch.Tensor, weight: torch.Tensor,
             _dt(u.dtype), _dt(weight.dtype), _stream())
     _capi.check(code, "based_gated_conv_step")
     return out
+
+
+def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                residual: Optional[torch.Tensor] = None, *, eps: float = 1e-6, prenorm: bool = False,
+                residual_in_fp32: bool = False):
+    """``z = x + residual``; ``out = rmsnorm(z) * weight (+ bias)`` in one pass; with ``prenorm`` returns
+    ``(out, z)`` like rms_norm_fn (layer_norm.py:926-953).  ``z`` is fp32 when ``residual_in_fp32`` or
+    when ``residual`` already is, else x's dtype.  x ``[..., D]``."""
+    _need_cuda(x, weight, bias, residual)
+    D = x.shape[-1]
+    x2 = x.reshape(-1, D)
+    _inner_contig(x2, "x")
+    M = x2.shape[0]
+    res2 = None
+    if residual is not None:
+        if residual.shape != x.shape:
+            raise ValueError("residual must have x's shape")
+        res2 = residual.reshape(-1, D)
+        _inner_contig(res2, "residual")
+    res_dtype = torch.float32 if (residual_in_fp32 or (residual is not None and residual.dtype == torch.float32)) else x.dtype
+    if res2 is not None and res2.dtype != res_dtype:
+        res2 = res2.to(res_dtype)
+    weight = weight.contiguous()
+    if bias is not None:
+        bias = bias.to(weight.dtype).contiguous()
+    out = torch.empty(M, D, dtype=x.dtype, device=x.device)
+    res_out = torch.empty(M, D, dtype=res_dtype, device=x.device) if prenorm else None
+    if M > 0:
+        with torch.cuda.device(x.device):
+            code = _capi.lib().based_add_rmsnorm(
+                x2.data_ptr(), res2.data_ptr() if res2 is not None else None, weight.data_ptr(),
+                bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                res_out.data_ptr() if res_out is not None else None, M, D, x2.stride(0),
+                res2.stride(0) if res2 is not None else 0, out.stride(0), res_out.stride(0) if res_out is not None else 0,
+                float(eps), _dt(x.dtype), _dt(res_dtype), _dt(weight.dtype), _stream())
+        _capi.check(code, "based_add_rmsnorm")
+    out = out.reshape(x.shape)
+    return (out, res_out.reshape(x.shape)) if prenorm else out
+
+
+_ACTS = {"silu": 0, "swiglu": 0, "sigmoid": 1, "glu": 1}
+
+
+def gated_act(y: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """``first_half * act(second_half)`` over the last dim of ``y [..., 2F]`` (mlp.py:141-154)."""
+    _need_cuda(y)
+    F2 = y.shape[-1]
+    F = F2 // 2
+    y2 = y.reshape(-1, F2)
+    _inner_contig(y2, "y")
+    M = y2.shape[0]
+    out = torch.empty(M, F, dtype=y.dtype, device=y.device)
+    if M > 0:
+        a, g = y2[:, :F], y2[:, F:]
+        with torch.cuda.device(y.device):
+            code = _capi.lib().based_gated_act(a.data_ptr(), g.data_ptr(), out.data_ptr(), M, F, a.stride(0),
+                                               g.stride(0), out.stride(0), _ACTS[activation], _dt(y.dtype), _stream())
+        _capi.check(code, "based_gated_act")
+    return out.reshape(*y.shape[:-1], F)

@@ -1,8 +1,9 @@
 /*
  * based_b200 — C ABI of the B200 (sm_100a) kernels for the Based hot path:
  * Taylor-feature-map linear attention (prefill + recurrent decode step),
- * sliding-window softmax attention (prefill + decode step) and the gated short
- * convolution of the BaseConv mixer (prefill + decode step).
+ * sliding-window softmax attention (prefill + decode step), the gated short
+ * convolution of the BaseConv mixer (prefill + decode step), and the residual-add +
+ * RMSNorm and gated-MLP activation that sit between the mixers and the GEMMs.
  *
  * Conventions shared by every entry point
  * ---------------------------------------
@@ -261,6 +262,47 @@ int based_gated_conv_step(const void* u1, const void* u2, void* y, void* state,
                           int B, int di, int k,
                           int64_t u1_batch_stride, int64_t u2_batch_stride, int64_t y_batch_stride,
                           int io_dtype, int w_dtype, void* stream);
+
+/*
+ * Residual add + RMSNorm in one pass over [M, D] rows:
+ *   z = x + residual;  residual_out = z;  out = z / sqrt(mean(z^2) + eps) * weight + bias.
+ *
+ * Replaces RMSNorm.forward / rms_norm_fn with prenorm=True, the Triton kernel that
+ * Block.forward and GPTModel.forward call (based/ops/triton/layer_norm.py:926-953; semantics
+ * restated by rms_norm_ref :74-125; call sites based/models/block.py:134-163,
+ * based/models/gpt.py:696-733).
+ *
+ *   x, out        [M, D] in io_dtype; residual (or NULL), residual_out (or NULL) [M, D] in
+ *                 res_dtype -- BASED_F32 is the reference's residual_in_fp32=True;
+ *                 *_row_stride in elements, inner stride 1
+ *   weight, bias  [D] in w_dtype; bias may be NULL
+ *   The norm is taken of z as residual_out stores it (rounded to bf16 when res_dtype is bf16 and
+ *   residual_out is given).  D a multiple of 8, at most 8192; pointers 16-byte aligned, row
+ *   strides multiples of 8.  fp32 arithmetic.
+ */
+int based_add_rmsnorm(const void* x, const void* residual, const void* weight, const void* bias,
+                      void* out, void* residual_out,
+                      int64_t M, int D,
+                      int64_t x_row_stride, int64_t residual_row_stride,
+                      int64_t out_row_stride, int64_t residual_out_row_stride,
+                      float eps, int io_dtype, int res_dtype, int w_dtype, void* stream);
+
+/* activation selectors of based_gated_act */
+#define BASED_ACT_SILU 0    /* SwiGLU: y * silu(gate) */
+#define BASED_ACT_SIGMOID 1 /* GLU:    y * sigmoid(gate) */
+
+/*
+ * Gated activation of the MLP: out[m, f] = y[m, f] * act(gate[m, f]).
+ *
+ * Replaces `y, gate = y.chunk(2, dim=-1); y = swiglu(gate, y)` (flash-attn's jiterator op) and
+ * F.glu in GatedMlp.forward (based/models/mlp.py:141-154).  y and gate are normally the two
+ * halves of fc1's output [M, 2F]: pass both pointers with the same row stride 2F.
+ *   F a multiple of 8 (bf16) / 4 (fp32); pointers 16-byte aligned; row strides multiples of 8 / 4.
+ */
+int based_gated_act(const void* y, const void* gate, void* out,
+                    int64_t M, int F,
+                    int64_t y_row_stride, int64_t gate_row_stride, int64_t out_row_stride,
+                    int act, int io_dtype, void* stream);
 
 #ifdef __cplusplus
 }

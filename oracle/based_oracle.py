@@ -370,3 +370,39 @@ def baseconv_forward(params: dict, x: torch.Tensor, state: Optional[torch.Tensor
         if state is not None:
             state.copy_(conv_state_from_prompt(u[..., : w.shape[0]], w.shape[1]))
     return v @ params["out_w"].T + params["out_b"]
+
+
+# --------------------------------------------------------------------------
+# Residual add + RMSNorm, gated MLP activation; pinned by tests/golden/norm_mlp.npz
+def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                residual: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                residual_dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``z = x + residual``; ``out = z / sqrt(mean(z^2) + eps) * weight (+ bias)``; returns
+    ``(out, z)`` (the prenorm pair).  Restates rms_norm_ref with ``prenorm=True``
+    (based/ops/triton/layer_norm.py:74-125: the sum :110-113, rstd :114, scaling :115) as
+    Block.forward uses it (based/models/block.py:134-163).  ``z`` is returned in
+    ``residual_dtype`` (default: x's dtype) and the norm sees it as stored, which is what
+    ``residual_in_fp32`` selects in the reference.
+    """
+    rd = residual_dtype or x.dtype
+    z = x.to(torch.float64) if x.dtype == torch.float64 else x.float()
+    if residual is not None:
+        z = z + residual.to(z.dtype)
+    z_st = z.to(rd)
+    zz = z_st.to(z.dtype)
+    rstd = 1.0 / torch.sqrt(zz.square().mean(dim=-1, keepdim=True) + eps)
+    out = zz * rstd * weight.to(z.dtype)
+    if bias is not None:
+        out = out + bias.to(z.dtype)
+    return out.to(x.dtype), z_st
+
+
+def gated_act(y: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """``first_half * act(second_half)`` over the last dim: GatedMlp.forward between fc1 and fc2
+    (based/models/mlp.py:141-154; "silu" is the SwiGLU case :148-153, "sigmoid" is F.glu :146-147)."""
+    a, g = y.chunk(2, dim=-1)
+    if activation == "silu":
+        return a * torch.nn.functional.silu(g)
+    if activation == "sigmoid":
+        return a * torch.sigmoid(g)
+    raise ValueError(activation)

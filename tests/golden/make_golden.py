@@ -167,6 +167,37 @@ def baseconv_case(ref_root, InferenceParams):
     np.savez(os.path.join(HERE, "baseconv.npz"), **out)
 
 
+def norm_mlp_case(ref_root):
+    """Reference rms_norm_ref (based/ops/triton/layer_norm.py:74-125) with residual and prenorm, and
+    GatedMlp (based/models/mlp.py:99-157) with silu (SwiGLU, torch branch) and sigmoid (GLU)."""
+    import contextlib
+    import io
+
+    import torch.nn.functional as F
+
+    with contextlib.redirect_stdout(io.StringIO()):
+        import based.models.mlp as mlp
+        from based.ops.triton.layer_norm import rms_norm_ref
+    mlp.swiglu = None  # flash-attn's CUDA op; the torch branch (mlp.py:151-153) states the same mathematics
+    torch.manual_seed(13)
+    D = 72
+    x = torch.randn(3, 7, D, dtype=torch.float64)
+    res = torch.randn(3, 7, D, dtype=torch.float64)
+    w = torch.randn(D, dtype=torch.float64) * 0.3 + 1.0
+    b = torch.randn(D, dtype=torch.float64) * 0.1
+    out = {"x": t2n(x), "residual": t2n(res), "weight": t2n(w), "bias": t2n(b)}
+    o, r = rms_norm_ref(x, w, None, residual=res, eps=1e-5, prenorm=True)
+    out["out_res"], out["res_out"] = t2n(o), t2n(r)
+    out["out_nores"] = t2n(rms_norm_ref(x, w, None, eps=1e-5))
+    out["out_bias"] = t2n(rms_norm_ref(x, w, b, residual=res, eps=1e-6))
+    for name, act in (("silu", F.silu), ("sigmoid", F.sigmoid)):
+        m = mlp.GatedMlp(32, activation=act, bias1=False, bias2=False, multiple_of=32).double()
+        xm = torch.randn(2, 5, 32, dtype=torch.float64)
+        out[f"mlp_{name}_fc1"], out[f"mlp_{name}_fc2"] = t2n(m.fc1.weight), t2n(m.fc2.weight)
+        out[f"mlp_{name}_x"], out[f"mlp_{name}_y"] = t2n(xm), t2n(m(xm))
+    np.savez(os.path.join(HERE, "norm_mlp.npz"), **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("BASED_REFERENCE"))
@@ -181,6 +212,7 @@ def main():
         mixer_level_case(LA, TE, IP)
         config1_samples(LA, TE, IP)
         baseconv_case(args.ref, IP)
+        norm_mlp_case(args.ref)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

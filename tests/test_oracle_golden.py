@@ -145,3 +145,15 @@ def test_baseconv_oracle_matches_reference_golden():
     assert rel_err(O.baseconv_forward(params, T["x_short"], state=short), T["y_short"]) < 1e-12
     assert torch.equal(short, T["state_short"])
     assert (short[..., 0] == 0).all()
+
+
+def test_rmsnorm_and_gated_mlp_oracle_match_reference_golden():
+    g = {k: torch.as_tensor(v) for k, v in load_golden("norm_mlp.npz").items()}
+    out, z = O.add_rmsnorm(g["x"], g["weight"], None, residual=g["residual"], eps=1e-5)
+    assert rel_err(out, g["out_res"]) < 1e-12 and rel_err(z, g["res_out"]) < 1e-12
+    assert rel_err(O.add_rmsnorm(g["x"], g["weight"], eps=1e-5)[0], g["out_nores"]) < 1e-12
+    assert rel_err(O.add_rmsnorm(g["x"], g["weight"], g["bias"], residual=g["residual"], eps=1e-6)[0],
+                   g["out_bias"]) < 1e-12
+    for act in ("silu", "sigmoid"):
+        h = O.gated_act(g[f"mlp_{act}_x"] @ g[f"mlp_{act}_fc1"].T, act)
+        assert rel_err(h @ g[f"mlp_{act}_fc2"].T, g[f"mlp_{act}_y"]) < 1e-12
