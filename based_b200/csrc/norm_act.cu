@@ -20,9 +20,11 @@ struct V16;  // 16 bytes of T <-> floats
 template <>
 struct V16<float> {
   static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& v, float (&x)[4]) {
+    x[0] = __uint_as_float(v.x); x[1] = __uint_as_float(v.y); x[2] = __uint_as_float(v.z); x[3] = __uint_as_float(v.w);
+  }
   static __device__ __forceinline__ void load(const float* p, float (&x)[4]) {
-    const float4 v = *reinterpret_cast<const float4*>(p);
-    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    unpack(*reinterpret_cast<const uint4*>(p), x);
   }
   static __device__ __forceinline__ void store(float* p, const float (&x)[4]) {
     *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
@@ -31,14 +33,16 @@ struct V16<float> {
 template <>
 struct V16<__nv_bfloat16> {
   static constexpr int N = 8;
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&x)[8]) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p);
+  static __device__ __forceinline__ void unpack(const uint4& v, float (&x)[8]) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       x[2 * i] = __uint_as_float(w[i] << 16);
       x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
     }
+  }
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&x)[8]) {
+    unpack(*reinterpret_cast<const uint4*>(p), x);
   }
   static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&x)[8]) {
     uint4 v;
@@ -153,34 +157,35 @@ __device__ __forceinline__ float act_fn(float g, int act) {
   return act == 0 ? g * s : s;                            // 0: silu, 1: sigmoid
 }
 
-// thread per 16-byte vector of outputs, U vectors per thread in flight; grid-stride over the vectors of a row block
-template <typename T>
-__global__ void __launch_bounds__(256) gated_act_kernel(const ActParams p) {
+// One row per block; thread t owns the 16-byte vectors t, t + 128, ... of the row (VPT of them): a
+// warp's accesses are contiguous, all loads of a thread are issued before any arithmetic.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(NORM_THREADS) gated_act_kernel(const ActParams p) {
   constexpr int N = V16<T>::N;
-  const int vec_per_row = p.F / N;
-  const int64_t total = p.M * vec_per_row;
-  constexpr int U = 4;
-  const int64_t base = ((int64_t)blockIdx.x * 256 + threadIdx.x) * U;
-  float a[U][N], g[U][N];
+  const int nvec = p.F / N;
+  const int64_t row = blockIdx.x;
+  const T* y = static_cast<const T*>(p.y) + row * p.sy;
+  const T* gate = static_cast<const T*>(p.gate) + row * p.sg;
+  T* out = static_cast<T*>(p.out) + row * p.so;
+  uint4 a[VPT], g[VPT];
 #pragma unroll
-  for (int u = 0; u < U; ++u) {
-    const int64_t i = base + u;
-    if (i < total) {
-      const int64_t r = i / vec_per_row;
-      const int c = (int)(i - r * vec_per_row) * N;
-      V16<T>::load(static_cast<const T*>(p.y) + r * p.sy + c, a[u]);
-      V16<T>::load(static_cast<const T*>(p.gate) + r * p.sg + c, g[u]);
+  for (int v = 0; v < VPT; ++v) {
+    const int c = threadIdx.x + v * NORM_THREADS;
+    if (c < nvec) {
+      a[v] = *reinterpret_cast<const uint4*>(y + c * N);
+      g[v] = *reinterpret_cast<const uint4*>(gate + c * N);
     }
   }
 #pragma unroll
-  for (int u = 0; u < U; ++u) {
-    const int64_t i = base + u;
-    if (i < total) {
-      const int64_t r = i / vec_per_row;
-      const int c = (int)(i - r * vec_per_row) * N;
+  for (int v = 0; v < VPT; ++v) {
+    const int c = threadIdx.x + v * NORM_THREADS;
+    if (c < nvec) {
+      float x[N], h[N];
+      V16<T>::unpack(a[v], x);
+      V16<T>::unpack(g[v], h);
 #pragma unroll
-      for (int e = 0; e < N; ++e) a[u][e] *= act_fn(g[u][e], p.act);
-      V16<T>::store(static_cast<T*>(p.out) + r * p.so + c, a[u]);
+      for (int e = 0; e < N; ++e) x[e] *= act_fn(h[e], p.act);
+      V16<T>::store(out + c * N, x);
     }
   }
 }
@@ -212,12 +217,22 @@ int launch_gated_act(const void* y, const void* gate, void* out, int64_t M, int 
   const int N = io_dtype == BASED_BF16 ? 8 : 4;
   if (F % N != 0) return BASED_ERR_SHAPE;
   if (!aligned16(y) || !aligned16(gate) || !aligned16(out) || sy % N || sg % N || so % N) return BASED_ERR_ALIGN;
-  const int64_t total = M * (F / N);
-  const int64_t blocks = (total + 256 * 4 - 1) / (256 * 4);
-  if (blocks > 2147483647LL) return BASED_ERR_TOO_LARGE;
+  if (M > 2147483647LL) return BASED_ERR_TOO_LARGE;
+  const int nvec = F / N, vpt = (nvec + NORM_THREADS - 1) / NORM_THREADS;
+  if (vpt > 16) return BASED_ERR_SHAPE;  // F up to 16384 (bf16) / 8192 (fp32)
   ActParams p{y, gate, out, M, sy, sg, so, F, act};
-  if (io_dtype == BASED_BF16) gated_act_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(p);
-  else gated_act_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  const unsigned grid = (unsigned)M;
+#define BASED_LAUNCH_ACT(T)                                                                      \
+  do {                                                                                           \
+    if (vpt <= 1) gated_act_kernel<T, 1><<<grid, NORM_THREADS, 0, stream>>>(p);                  \
+    else if (vpt <= 2) gated_act_kernel<T, 2><<<grid, NORM_THREADS, 0, stream>>>(p);             \
+    else if (vpt <= 4) gated_act_kernel<T, 4><<<grid, NORM_THREADS, 0, stream>>>(p);             \
+    else if (vpt <= 8) gated_act_kernel<T, 8><<<grid, NORM_THREADS, 0, stream>>>(p);             \
+    else gated_act_kernel<T, 16><<<grid, NORM_THREADS, 0, stream>>>(p);                          \
+  } while (0)
+  if (io_dtype == BASED_BF16) BASED_LAUNCH_ACT(__nv_bfloat16);
+  else BASED_LAUNCH_ACT(float);
+#undef BASED_LAUNCH_ACT
   return (int)cudaGetLastError();
 }
 

@@ -242,6 +242,37 @@ def gated_conv_bench(ops, peaks):
             "l2": "working set 201 MB > L2", "timing": "CUDA graph of 20 launches", "step_us": ts * 1e3}
 
 
+def norm_act_bench(ops, peaks):
+    """Residual add + RMSNorm (bf16 activations, fp32 residual stream in and out) and the SwiGLU activation at
+    the 360M model's sizes: M = 16 x 2048 rows, D = 1024, F = 2816."""
+    M, D, Fh = 16 * 2048, 1024, 2816
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(M, D, device="cuda", generator=g).bfloat16()
+    res = torch.randn(M, D, device="cuda", generator=g)
+    w = torch.ones(D, device="cuda").bfloat16()
+    y = torch.randn(M, 2 * Fh, device="cuda", generator=g).bfloat16()
+    from based_b200 import _capi
+    lib = _capi.lib()
+    out = torch.empty_like(x)
+    res_out = torch.empty_like(res)
+    h = torch.empty(M, Fh, dtype=torch.bfloat16, device="cuda")
+    st = torch.cuda.current_stream
+
+    def norm():
+        _capi.check(lib.based_add_rmsnorm(x.data_ptr(), res.data_ptr(), w.data_ptr(), None, out.data_ptr(),
+                                          res_out.data_ptr(), M, D, D, D, D, D, 1e-5, 1, 0, 1, st().cuda_stream), "norm")
+
+    def act():
+        _capi.check(lib.based_gated_act(y.data_ptr(), y.data_ptr() + 2 * Fh, h.data_ptr(), M, Fh, 2 * Fh, 2 * Fh, Fh,
+                                        0, 1, st().cuda_stream), "act")
+
+    tn, ta = time_graph(norm, 20), time_graph(act, 20)
+    bn, ba = M * D * 12, M * Fh * 6
+    return {"rows": M, "D": D, "F": Fh, "timing": "CUDA graph of 20 launches",
+            "add_rmsnorm": {"ms": tn, "bytes": bn, "hbm_frac": bn / (tn * 1e-3) / (peaks["hbm_gbs"] * 1e9)},
+            "gated_act": {"ms": ta, "bytes": ba, "hbm_frac": ba / (ta * 1e-3) / (peaks["hbm_gbs"] * 1e9)}}
+
+
 def small_batch_prefill(ops, L):
     """One sequence (B=1, H=16, dv=64): one CTA per head against the sequence split the library picks."""
     g = torch.Generator(device="cuda").manual_seed(L + 1)
@@ -401,6 +432,7 @@ def main():
             line["swa"] = swa
             line["prefill_small_batch"] = small_batch_prefill(ops, max(lengths))
             line["gated_conv"] = gated_conv_bench(ops, peaks)
+            line["norm_act"] = norm_act_bench(ops, peaks)
         if world == 1 and not args.no_cpu:
             use_all_host_threads()
             tput, dt = cpu_decode_baseline(B_DEC, 20, 2)

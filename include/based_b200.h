@@ -297,7 +297,7 @@ int based_add_rmsnorm(const void* x, const void* residual, const void* weight, c
  * Replaces `y, gate = y.chunk(2, dim=-1); y = swiglu(gate, y)` (flash-attn's jiterator op) and
  * F.glu in GatedMlp.forward (based/models/mlp.py:141-154).  y and gate are normally the two
  * halves of fc1's output [M, 2F]: pass both pointers with the same row stride 2F.
- *   F a multiple of 8 (bf16) / 4 (fp32); pointers 16-byte aligned; row strides multiples of 8 / 4.
+ *   F a multiple of 8 (bf16) / 4 (fp32), at most 16384 / 8192; pointers 16-byte aligned; row strides multiples of 8 / 4.
  */
 int based_gated_act(const void* y, const void* gate, void* out,
                     int64_t M, int F,
