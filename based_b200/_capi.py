@@ -37,7 +37,7 @@ SIGNATURES = {
                          + [c_int] * 4 + [_I64P] * 4 + [c_int, c_float, c_int, c_void_p]),
     "based_gated_conv_prefill": (c_int, [c_void_p] * 6 + [c_int] * 4 + [_I64P] * 3 + [c_int, c_int, c_void_p]),
     "based_gated_conv_step": (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
-    "based_add_rmsnorm": (c_int, [c_void_p] * 6 + [c_int64, c_int] + [c_int64] * 4 + [c_float, c_int, c_int, c_int, c_void_p]),
+    "based_add_rmsnorm": (c_int, [c_void_p] * 6 + [c_int64, c_int] + [c_int64] * 4 + [c_float, c_int, c_int, c_int, c_int, c_void_p]),
     "based_gated_act": (c_int, [c_void_p] * 3 + [c_int64, c_int] + [c_int64] * 3 + [c_int, c_int, c_void_p]),
 }
 

@@ -245,13 +245,13 @@ int based_gated_conv_step(const void* u1, const void* u2, void* y, void* state, 
 int based_add_rmsnorm(const void* x, const void* residual, const void* weight, const void* bias, void* out,
                       void* residual_out, int64_t M, int D, int64_t x_row_stride, int64_t residual_row_stride,
                       int64_t out_row_stride, int64_t residual_out_row_stride, float eps, int io_dtype, int res_dtype,
-                      int w_dtype, void* stream) {
+                      int w_dtype, int round_input, void* stream) {
   if (!x || !weight || !out) return BASED_ERR_NULL;
   if (!dtype_ok(io_dtype) || !dtype_ok(res_dtype) || !dtype_ok(w_dtype)) return BASED_ERR_DTYPE;
   if (M < 0 || D <= 0) return BASED_ERR_SHAPE;
   if (M == 0) return BASED_OK;
   return launch_add_rmsnorm(x, residual, weight, bias, out, residual_out, M, D, x_row_stride, residual_row_stride,
-                            out_row_stride, residual_out_row_stride, eps, io_dtype, res_dtype, w_dtype,
+                            out_row_stride, residual_out_row_stride, eps, io_dtype, res_dtype, w_dtype, round_input,
                             static_cast<cudaStream_t>(stream));
 }
 

@@ -80,7 +80,7 @@ int launch_gated_conv_step(const void* u1, const void* u2, void* y, void* state,
 
 int launch_add_rmsnorm(const void* x, const void* residual, const void* weight, const void* bias, void* out,
                        void* residual_out, int64_t M, int D, int64_t sx, int64_t sr, int64_t so, int64_t sro, float eps,
-                       int io_dtype, int res_dtype, int w_dtype, cudaStream_t stream);
+                       int io_dtype, int res_dtype, int w_dtype, int round_input, cudaStream_t stream);
 int launch_gated_act(const void* y, const void* gate, void* out, int64_t M, int F, int64_t sy, int64_t sg, int64_t so,
                      int act, int io_dtype, cudaStream_t stream);
 

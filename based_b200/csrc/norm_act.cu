@@ -82,7 +82,7 @@ struct NormParams {
   const void *x, *residual, *weight, *bias;
   void *out, *residual_out;
   int64_t M, sx, sr, so, sro;  // rows and row strides (elements)
-  int D, io_bf16, res_bf16, w_bf16;
+  int D, io_bf16, res_bf16, w_bf16, round_input;
   float eps;
 };
 
@@ -113,6 +113,10 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(const NormPar
 #pragma unroll
           for (int i = 0; i < 8; ++i) z[v][i] = __bfloat162float(__float2bfloat16_rn(z[v][i]));
         }
+      }
+      if (p.round_input && p.io_bf16) {  // the norm sees z cast to the activation dtype
+#pragma unroll
+        for (int i = 0; i < 8; ++i) z[v][i] = __bfloat162float(__float2bfloat16_rn(z[v][i]));
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) ss = fmaf(z[v][i], z[v][i], ss);
@@ -194,7 +198,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_act_kernel(const ActParams
 
 int launch_add_rmsnorm(const void* x, const void* residual, const void* weight, const void* bias, void* out,
                        void* residual_out, int64_t M, int D, int64_t sx, int64_t sr, int64_t so, int64_t sro, float eps,
-                       int io_dtype, int res_dtype, int w_dtype, cudaStream_t stream) {
+                       int io_dtype, int res_dtype, int w_dtype, int round_input, cudaStream_t stream) {
   if (D % 8 != 0 || D > 8 * NORM_THREADS * 8) return BASED_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(out) || !aligned16(weight) || (residual && !aligned16(residual)) ||
       (residual_out && !aligned16(residual_out)) || (bias && !aligned16(bias)))
@@ -202,7 +206,7 @@ int launch_add_rmsnorm(const void* x, const void* residual, const void* weight, 
   if (sx % 8 || so % 8 || (residual && sr % 8) || (residual_out && sro % 8)) return BASED_ERR_ALIGN;
   if (M > 2147483647LL) return BASED_ERR_TOO_LARGE;
   NormParams p{x, residual, weight, bias, out, residual_out, M, sx, sr, so, sro, D,
-               io_dtype == BASED_BF16, res_dtype == BASED_BF16, w_dtype == BASED_BF16, eps};
+               io_dtype == BASED_BF16, res_dtype == BASED_BF16, w_dtype == BASED_BF16, round_input != 0, eps};
   const int groups = D / 8, vpt = (groups + NORM_THREADS - 1) / NORM_THREADS;
   const unsigned grid = (unsigned)M;
   if (vpt <= 1) add_rmsnorm_kernel<1><<<grid, NORM_THREADS, 0, stream>>>(p);

@@ -24,9 +24,11 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(hidden_size, device=device, dtype=dtype))
         self.register_parameter("bias", None)
 
-    def forward(self, x, residual=None, prenorm=False, residual_in_fp32=False):
+    def forward(self, x, residual=None, prenorm=False, residual_in_fp32=False, round_input=False):
+        """``round_input`` (not in the reference's signature) rounds ``x + residual`` to x's dtype before the
+        norm, which is what a block computes when it adds first and then calls the norm on the cast sum."""
         return ops.add_rmsnorm(x, self.weight, self.bias, residual=residual, eps=self.eps, prenorm=prenorm,
-                               residual_in_fp32=residual_in_fp32)
+                               residual_in_fp32=residual_in_fp32, round_input=round_input)
 
 
 class GatedMlp(nn.Module):

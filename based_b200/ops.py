@@ -329,10 +329,11 @@ def gated_conv_step(u: torch.Tensor, state: torch.Tensor, weight: torch.Tensor,
 
 def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 residual: Optional[torch.Tensor] = None, *, eps: float = 1e-6, prenorm: bool = False,
-                residual_in_fp32: bool = False):
+                residual_in_fp32: bool = False, round_input: bool = False):
     """``z = x + residual``; ``out = rmsnorm(z) * weight (+ bias)`` in one pass; with ``prenorm`` returns
     ``(out, z)`` like rms_norm_fn (layer_norm.py:926-953).  ``z`` is fp32 when ``residual_in_fp32`` or
-    when ``residual`` already is, else x's dtype.  x ``[..., D]``."""
+    when ``residual`` already is, else x's dtype.  ``round_input`` rounds ``z`` to x's dtype before the
+    norm (the unfused ``norm(residual.to(weight.dtype))`` of block.py:134-137).  x ``[..., D]``."""
     _need_cuda(x, weight, bias, residual)
     D = x.shape[-1]
     x2 = x.reshape(-1, D)
@@ -359,7 +360,7 @@ def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
                 bias.data_ptr() if bias is not None else None, out.data_ptr(),
                 res_out.data_ptr() if res_out is not None else None, M, D, x2.stride(0),
                 res2.stride(0) if res2 is not None else 0, out.stride(0), res_out.stride(0) if res_out is not None else 0,
-                float(eps), _dt(x.dtype), _dt(res_dtype), _dt(weight.dtype), _stream())
+                float(eps), _dt(x.dtype), _dt(res_dtype), _dt(weight.dtype), int(round_input), _stream())
         _capi.check(code, "based_add_rmsnorm")
     out = out.reshape(x.shape)
     return (out, res_out.reshape(x.shape)) if prenorm else out

@@ -260,7 +260,7 @@ def norm_act_bench(ops, peaks):
 
     def norm():
         _capi.check(lib.based_add_rmsnorm(x.data_ptr(), res.data_ptr(), w.data_ptr(), None, out.data_ptr(),
-                                          res_out.data_ptr(), M, D, D, D, D, D, 1e-5, 1, 0, 1, st().cuda_stream), "norm")
+                                          res_out.data_ptr(), M, D, D, D, D, D, 1e-5, 1, 0, 1, 0, st().cuda_stream), "norm")
 
     def act():
         _capi.check(lib.based_gated_act(y.data_ptr(), y.data_ptr() + 2 * Fh, h.data_ptr(), M, Fh, 2 * Fh, 2 * Fh, Fh,

@@ -277,15 +277,19 @@ int based_gated_conv_step(const void* u1, const void* u2, void* y, void* state,
  *                 *_row_stride in elements, inner stride 1
  *   weight, bias  [D] in w_dtype; bias may be NULL
  *   The norm is taken of z as residual_out stores it (rounded to bf16 when res_dtype is bf16 and
- *   residual_out is given).  D a multiple of 8, at most 8192; pointers 16-byte aligned, row
- *   strides multiples of 8.  fp32 arithmetic.
+ *   residual_out is given).  round_input != 0 additionally rounds z to io_dtype before the norm:
+ *   that is what the blocks compute when they run the unfused sequence
+ *   `residual = x + residual; hidden = norm(residual.to(weight.dtype))` (block.py:134-137) with
+ *   an fp32 residual stream and bf16 activations.
+ *   D a multiple of 8, at most 8192; pointers 16-byte aligned, row strides multiples of 8.
+ *   fp32 arithmetic.
  */
 int based_add_rmsnorm(const void* x, const void* residual, const void* weight, const void* bias,
                       void* out, void* residual_out,
                       int64_t M, int D,
                       int64_t x_row_stride, int64_t residual_row_stride,
                       int64_t out_row_stride, int64_t residual_out_row_stride,
-                      float eps, int io_dtype, int res_dtype, int w_dtype, void* stream);
+                      float eps, int io_dtype, int res_dtype, int w_dtype, int round_input, void* stream);
 
 /* activation selectors of based_gated_act */
 #define BASED_ACT_SILU 0    /* SwiGLU: y * silu(gate) */

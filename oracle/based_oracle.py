@@ -376,13 +376,15 @@ def baseconv_forward(params: dict, x: torch.Tensor, state: Optional[torch.Tensor
 # Residual add + RMSNorm, gated MLP activation; pinned by tests/golden/norm_mlp.npz
 def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 residual: Optional[torch.Tensor] = None, eps: float = 1e-6,
-                residual_dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                residual_dtype: Optional[torch.dtype] = None,
+                round_input: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """``z = x + residual``; ``out = z / sqrt(mean(z^2) + eps) * weight (+ bias)``; returns
     ``(out, z)`` (the prenorm pair).  Restates rms_norm_ref with ``prenorm=True``
     (based/ops/triton/layer_norm.py:74-125: the sum :110-113, rstd :114, scaling :115) as
     Block.forward uses it (based/models/block.py:134-163).  ``z`` is returned in
     ``residual_dtype`` (default: x's dtype) and the norm sees it as stored, which is what
-    ``residual_in_fp32`` selects in the reference.
+    ``residual_in_fp32`` selects in the reference.  ``round_input`` rounds z to x's dtype before
+    the norm: the unfused ``norm(residual.to(weight.dtype))`` of block.py:134-137.
     """
     rd = residual_dtype or x.dtype
     z = x.to(torch.float64) if x.dtype == torch.float64 else x.float()
@@ -390,6 +392,8 @@ def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
         z = z + residual.to(z.dtype)
     z_st = z.to(rd)
     zz = z_st.to(z.dtype)
+    if round_input:
+        zz = zz.to(x.dtype).to(z.dtype)
     rstd = 1.0 / torch.sqrt(zz.square().mean(dim=-1, keepdim=True) + eps)
     out = zz * rstd * weight.to(z.dtype)
     if bias is not None:
