@@ -410,3 +410,35 @@ def gated_act(y: torch.Tensor, activation: str = "silu") -> torch.Tensor:
     if activation == "sigmoid":
         return a * torch.sigmoid(g)
     raise ValueError(activation)
+
+
+# --------------------------------------------------------------------------
+# Whole model (conv / linear-attention blocks); pinned by tests/golden/full_model.npz
+def model_forward(sd: dict, input_ids: torch.Tensor, n_layer: int, n_head: int, linattn_layers,
+                  feature_dim: int = 16, eps: float = 1e-5) -> torch.Tensor:
+    """Logits of the prenorm block stack on a whole sequence, from a reference state dict.
+
+    Restates GPTModel.forward / GPTLMHeadModel.forward (based/models/gpt.py:639-733, :794-830)
+    with Block.forward's prenorm path (based/models/block.py:134-163): embedding; per block
+    ``residual += hidden`` -> RMSNorm -> mixer -> ``residual += hidden`` -> RMSNorm -> SwiGLU MLP;
+    final add + RMSNorm; tied lm_head.  Layers listed in ``linattn_layers`` are LinearAttention,
+    the others BaseConv (the sliding-window mixer has its own oracle functions above).
+    """
+    h = sd["transformer.embeddings.word_embeddings.weight"][input_ids]
+    residual = None
+    d = h.shape[-1]
+    for i in range(n_layer):
+        p = f"transformer.layers.{i}."
+        x, residual = add_rmsnorm(h, sd[p + "norm1.weight"], residual=residual, eps=eps)
+        if i in linattn_layers:
+            x, _, _ = linattn_mixer_forward(x, sd[p + "mixer.proj_q.weight"], sd[p + "mixer.proj_k.weight"],
+                                            sd[p + "mixer.proj_v.weight"], sd[p + "mixer.out_proj.weight"],
+                                            n_head, feature_dim, d // n_head)
+        else:
+            x = baseconv_forward({"in_w": sd[p + "mixer.in_proj.weight"], "in_b": sd[p + "mixer.in_proj.bias"],
+                                  "conv_w": sd[p + "mixer.conv.conv.weight"], "out_w": sd[p + "mixer.out_proj.weight"],
+                                  "out_b": sd[p + "mixer.out_proj.bias"]}, x)
+        x, residual = add_rmsnorm(x, sd[p + "norm2.weight"], residual=residual, eps=eps)
+        h = gated_act(x @ sd[p + "mlp.fc1.weight"].T, "silu") @ sd[p + "mlp.fc2.weight"].T
+    h, _ = add_rmsnorm(h, sd["transformer.ln_f.weight"], residual=residual, eps=eps)
+    return h @ sd["transformer.embeddings.word_embeddings.weight"].T

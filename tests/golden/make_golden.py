@@ -198,6 +198,85 @@ def norm_mlp_case(ref_root):
     np.savez(os.path.join(HERE, "norm_mlp.npz"), **out)
 
 
+def full_model_case(ref_root, InferenceParams):
+    """The reference's GPTLMHeadModel (based/models/gpt.py:737-830) on CPU in fp32: BaseConv, LinearAttention
+    and BaseConv blocks with RMSNorm and SwiGLU MLPs.  Logits of a full pass, of the prompt pass and of
+    three single-token steps, plus the weights.
+
+    Three more shims, none of which touches the arithmetic being pinned: a stand-in for
+    ``hydra.utils.instantiate`` (hydra is not installed; gpt.py:90-96 only needs _target_/_partial_
+    resolution), ``rms_norm_fn`` -> the reference's own ``rms_norm_ref`` (the Triton kernel needs a GPU;
+    layer_norm.py:74-125 is its stated semantics), and ``swiglu = None`` so that GatedMlp takes its torch
+    branch (mlp.py:151-153).  The sliding-window mixer cannot run without a GPU and is left out here.
+    """
+    import contextlib
+    import functools
+    import importlib
+    import io
+
+    def locate(path):
+        mod, _, attr = path.rpartition(".")
+        return getattr(importlib.import_module(mod), attr)
+
+    def instantiate(cfg, *args, _partial_=False, **kwargs):
+        cfg = dict(cfg)
+        partial = cfg.pop("_partial_", _partial_)
+        target = locate(cfg.pop("_target_"))
+        cfg.pop("_recursive_", None)
+        built = {k: (instantiate(v) if isinstance(v, dict) and "_target_" in v else v) for k, v in cfg.items()}
+        built.update(kwargs)
+        return functools.partial(target, *args, **built) if partial else target(*args, **built)
+
+    hydra = types.ModuleType("hydra")
+    hydra.utils = types.ModuleType("hydra.utils")
+    hydra.utils.instantiate = instantiate
+    sys.modules.setdefault("hydra", hydra)
+    sys.modules.setdefault("hydra.utils", hydra.utils)
+    with contextlib.redirect_stdout(io.StringIO()):
+        import based.models.mlp as mlp
+        import based.ops.triton.layer_norm as ln
+
+        def rms_norm_fn(x, weight, bias, residual=None, eps=1e-6, dropout_p=0.0, prenorm=False,
+                        residual_in_fp32=False, **kw):
+            return ln.rms_norm_ref(x, weight, bias, residual=residual, eps=eps, prenorm=prenorm, upcast=True)
+
+        ln.rms_norm_fn = rms_norm_fn
+        mlp.swiglu = None
+        from based.models.gpt import GPT2MixerConfig, GPTLMHeadModel
+    cfg = GPT2MixerConfig(
+        n_embd=32, n_layer=3, n_head=2, n_inner=64, vocab_size=97, n_positions=0, max_position_embeddings=0,
+        mixer={"_target_": "based.models.mixers.convolution.BaseConv", "l_max": 64, "use_bias": True,
+               "expand_proj": 4, "kernel_size": 3},
+        alt_mixer={"_target_": "based.models.mixers.linear_attention.LinearAttention", "l_max": 64,
+                   "feature_map": {"_target_": "based.models.mixers.linear_attention.TaylorExp", "input_dim": 16},
+                   "feature_dim": 16, "num_heads": 2, "parallel_implementation": "quadratic"},
+        alt_mixer_layers=[1], alt_mixer_2_layers=[],
+        rms_norm=True, fused_mlp=False, attn_pdrop=0, embd_pdrop=0, resid_pdrop=0, mlp_fc1_bias=False,
+        mlp_fc2_bias=False, fused_bias_fc=False, out_proj_bias=False, qkv_proj_bias=False, use_flash_attn=False,
+        residual_in_fp32=True, activation_function="swiglu", rotary_emb_fraction=1, fused_dropout_add_ln=False,
+        pad_vocab_size_multiple=8, special_initializer=True, fixed_decay=False)
+    torch.manual_seed(0)
+    with contextlib.redirect_stdout(io.StringIO()):
+        m = GPTLMHeadModel(cfg)
+    # the special initialiser leaves the outputs tiny; scale the weights up so that every layer matters
+    with torch.no_grad():
+        for name, prm in m.named_parameters():
+            if prm.dim() > 1 and "embeddings" not in name:
+                prm.mul_(3.0)
+    out = {"sd." + k: t2n(v) for k, v in m.state_dict().items() if k != "lm_head.weight"}
+    ids = torch.randint(0, 97, (2, 13))
+    out["input_ids"] = ids.numpy().copy()
+    out["logits_full"] = t2n(m(ids).logits)
+    ip = InferenceParams(max_seqlen=32, max_batch_size=2)
+    out["logits_prefill_last"] = t2n(m(ids, inference_params=ip, num_last_tokens=1).logits)
+    for i in range(3):
+        ip.seqlen_offset = 13 + i
+        nxt = torch.randint(0, 97, (2, 1))
+        out[f"step{i}_ids"] = nxt.numpy().copy()
+        out[f"step{i}_logits"] = t2n(m(nxt, inference_params=ip, num_last_tokens=1).logits)
+    np.savez(os.path.join(HERE, "full_model.npz"), **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("BASED_REFERENCE"))
@@ -213,6 +292,7 @@ def main():
         config1_samples(LA, TE, IP)
         baseconv_case(args.ref, IP)
         norm_mlp_case(args.ref)
+        full_model_case(args.ref, IP)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -80,3 +80,23 @@ def test_baseconv_mirror_keeps_the_reference_interface():
     assert m.conv.layer_idx == (4, "conv")
     with pytest.raises(RuntimeError):  # CPU tensors are refused, there is no fallback
         m(torch.randn(1, 5, 64))
+
+
+def test_model_assembly_keeps_the_reference_parameter_names():
+    """Module tree of based/models/gpt.py:737-830 / block.py:27-93 (checked against the reference's own
+    state dict in tests/golden/full_model.npz) and the per-layer cache layout."""
+    import torch
+    from conftest import load_golden
+    from based_b200.model import BasedConfig, BasedLMHeadModel
+    g = load_golden("full_model.npz")
+    ref = {k[3:]: tuple(v.shape) for k, v in g.items() if k.startswith("sd.")}
+    cfg = BasedConfig(n_embd=32, n_layer=3, n_head=2, n_inner=64, vocab_size=97, alt_mixer_layers=[1],
+                      alt_mixer_2_layers=[], l_max=64)
+    m = BasedLMHeadModel(cfg)
+    mine = {k: tuple(v.shape) for k, v in m.state_dict().items() if k != "lm_head.weight"}
+    assert mine == ref
+    assert m.lm_head.weight is m.transformer.embeddings.word_embeddings.weight
+    cache = m.allocate_inference_cache(2, 32, dtype=torch.float32)
+    assert set(cache) == {0, 1, 2} and set(cache[0]) == {"conv"} and len(cache[1]) == 2
+    full = BasedConfig.based_360m()
+    assert full.padded_vocab_size == 50280 and len(full.alt_mixer_layers) == 5

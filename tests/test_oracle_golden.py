@@ -157,3 +157,18 @@ def test_rmsnorm_and_gated_mlp_oracle_match_reference_golden():
     for act in ("silu", "sigmoid"):
         h = O.gated_act(g[f"mlp_{act}_x"] @ g[f"mlp_{act}_fc1"].T, act)
         assert rel_err(h @ g[f"mlp_{act}_fc2"].T, g[f"mlp_{act}_y"]) < 1e-12
+
+
+def test_full_model_oracle_matches_reference_golden():
+    """Block stack (BaseConv, LinearAttention, BaseConv + RMSNorm + SwiGLU) against the reference's GPTLMHeadModel."""
+    g = load_golden("full_model.npz")
+    sd = {k[3:]: torch.as_tensor(v) for k, v in g.items() if k.startswith("sd.")}
+    ids = torch.as_tensor(g["input_ids"])
+    logits = O.model_forward(sd, ids, n_layer=3, n_head=2, linattn_layers=[1])
+    assert rel_err(logits, torch.as_tensor(g["logits_full"])) < 1e-5
+    # the reference's own step-by-step logits equal a longer full pass (recurrent == parallel)
+    seq = torch.cat([ids] + [torch.as_tensor(g[f"step{i}_ids"]) for i in range(3)], dim=1)
+    longer = O.model_forward(sd, seq, n_layer=3, n_head=2, linattn_layers=[1])
+    assert rel_err(longer[:, 12:13], torch.as_tensor(g["logits_prefill_last"])) < 1e-5
+    for i in range(3):
+        assert rel_err(longer[:, 13 + i:14 + i], torch.as_tensor(g[f"step{i}_logits"])) < 1e-5
