@@ -72,7 +72,39 @@ swa_prefill_simt_kernel(const IO* __restrict__ q, const IO* __restrict__ k, cons
   }
 }
 
-// One warp per (batch, head).
+// dot product of a cached key row with the query held in shared memory (fp32); 16-byte loads
+__device__ __forceinline__ float dot_row(const __nv_bfloat16* kc, const float* sq, int hd) {
+  float dot = 0.f;
+  for (int c = 0; c < hd; c += 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(kc + c);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      dot = fmaf(sq[c + 2 * i], __uint_as_float(w[i] << 16), dot);
+      dot = fmaf(sq[c + 2 * i + 1], __uint_as_float(w[i] & 0xFFFF0000u), dot);
+    }
+  }
+  return dot;
+}
+__device__ __forceinline__ float dot_row(const float* kc, const float* sq, int hd) {
+  float dot = 0.f;
+  for (int c = 0; c < hd; c += 4) {
+    const float4 v = *reinterpret_cast<const float4*>(kc + c);
+    dot = fmaf(sq[c], v.x, dot);
+    dot = fmaf(sq[c + 1], v.y, dot);
+    dot = fmaf(sq[c + 2], v.z, dot);
+    dot = fmaf(sq[c + 3], v.w, dot);
+  }
+  return dot;
+}
+// two adjacent value columns of a cached row
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) {
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+
+// One warp per (batch, head).  hd is a multiple of 8 and the cache 16-byte aligned (checked by the launcher).
 template <typename IO>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 swa_decode_kernel(const IO* __restrict__ q, const IO* __restrict__ k_new, const IO* __restrict__ v_new,
@@ -146,9 +178,7 @@ swa_decode_kernel(const IO* __restrict__ q, const IO* __restrict__ k_new, const 
     sc[n] = -INFINITY;
     if (jj < nk) {
       const IO* kc = cache_b + (size_t)(lo + jj) * row + (size_t)h * hd;
-      float dot = 0.f;
-      for (int c = 0; c < hd; ++c) dot = fmaf(s_q[warp][c], to_float(kc[c]), dot);
-      sc[n] = dot * scale;
+      sc[n] = dot_row(kc, s_q[warp], hd) * scale;
       m = fmaxf(m, sc[n]);
     }
   }
@@ -166,13 +196,29 @@ swa_decode_kernel(const IO* __restrict__ q, const IO* __restrict__ k_new, const 
   sum = warp_sum(sum);
   __syncwarp();
   const float inv = 1.f / sum;
-  for (int c = lane; c < hd; c += 32) {
-    float acc = 0.f;
-    for (int jj = 0; jj < nk; ++jj) {
-      const IO* vc = cache_b + (size_t)(lo + jj) * row + (size_t)(H + h) * hd;
-      acc = fmaf(s_p[warp][jj], to_float(vc[c]), acc);
+  // a lane owns two adjacent value columns; four rows per round so that their loads overlap
+  for (int c = 2 * lane; c < hd; c += 64) {
+    const IO* vc = cache_b + (size_t)lo * row + (size_t)(H + h) * hd + c;
+    float a0 = 0.f, a1 = 0.f;
+    int jj = 0;
+    for (; jj + 4 <= nk; jj += 4) {
+      float2 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) x[u] = load2(vc + (size_t)(jj + u) * row);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a0 = fmaf(s_p[warp][jj + u], x[u].x, a0);
+        a1 = fmaf(s_p[warp][jj + u], x[u].y, a1);
+      }
     }
-    o[b * so.b + h * so.h + c] = from_float<IO>(acc * inv);
+    for (; jj < nk; ++jj) {
+      const float2 x = load2(vc + (size_t)jj * row);
+      a0 = fmaf(s_p[warp][jj], x.x, a0);
+      a1 = fmaf(s_p[warp][jj], x.y, a1);
+    }
+    IO* op = o + b * so.b + h * so.h + c;
+    op[0] = from_float<IO>(a0 * inv);
+    op[1] = from_float<IO>(a1 * inv);
   }
 }
 
@@ -196,14 +242,68 @@ __global__ void rotary_kernel(IO* __restrict__ x, int L, int H, Strides3 sx, con
   px[c + half] = from_float<IO>(x0 * sn + x1 * cs);
 }
 
+// The same with 16-byte accesses: one thread per group of 8 (bf16) / 4 (fp32) rotated pairs.
+template <typename IO>
+__global__ void rotary_vec_kernel(IO* __restrict__ x, int L, int H, Strides3 sx, const IO* __restrict__ rcos,
+                                  const IO* __restrict__ rsin, int half, const int32_t* __restrict__ offsets,
+                                  int offset_scalar, long long total) {
+  constexpr int N = 16 / sizeof(IO);
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int groups = half / N;
+  const int c = (int)(idx % groups) * N;
+  long long r = idx / groups;
+  const int h = (int)(r % H); r /= H;
+  const int l = (int)(r % L);
+  const int b = (int)(r / L);
+  const int pos = l + (offsets ? offsets[b] : offset_scalar);
+  IO* px = x + b * sx.b + (int64_t)l * sx.l + h * sx.h + c;
+  union V { uint4 u; IO e[N]; } x0, x1, cs, sn;
+  x0.u = *reinterpret_cast<const uint4*>(px);
+  x1.u = *reinterpret_cast<const uint4*>(px + half);
+  cs.u = __ldg(reinterpret_cast<const uint4*>(rcos + (size_t)pos * half + c));
+  sn.u = __ldg(reinterpret_cast<const uint4*>(rsin + (size_t)pos * half + c));
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    const float a = to_float(x0.e[i]), bb = to_float(x1.e[i]), cc = to_float(cs.e[i]), ss = to_float(sn.e[i]);
+    x0.e[i] = from_float<IO>(a * cc - bb * ss);
+    x1.e[i] = from_float<IO>(a * ss + bb * cc);
+  }
+  *reinterpret_cast<uint4*>(px) = x0.u;
+  *reinterpret_cast<uint4*>(px + half) = x1.u;
+}
+
 }  // namespace
 
 int launch_rotary(void* x, int B, int L, int H, Strides3 sx, const void* rcos, const void* rsin, int rotary_dim,
                   const int32_t* offsets, int offset_scalar, int io_dtype, cudaStream_t stream) {
   const int half = rotary_dim / 2;
+  const int threads = 256;
+  if (io_dtype != BASED_BF16 && io_dtype != BASED_F32) return BASED_ERR_DTYPE;
+  {
+    // 16-byte path when every access it makes is aligned
+    const int N = io_dtype == BASED_BF16 ? 8 : 4;
+    if (half % N == 0 && sx.b % N == 0 && sx.l % N == 0 && sx.h % N == 0 && aligned16(x) && aligned16(rcos) &&
+        aligned16(rsin)) {
+      const long long total = (long long)B * L * H * (half / N);
+      if (total == 0) return 0;
+      const long long blocks = (total + threads - 1) / threads;
+      if (blocks > 2147483647LL) return BASED_ERR_TOO_LARGE;
+      if (io_dtype == BASED_BF16) {
+        using T = __nv_bfloat16;
+        rotary_vec_kernel<T><<<(unsigned)blocks, threads, 0, stream>>>(
+            static_cast<T*>(x), L, H, sx, static_cast<const T*>(rcos), static_cast<const T*>(rsin), half, offsets,
+            offset_scalar, total);
+      } else {
+        rotary_vec_kernel<float><<<(unsigned)blocks, threads, 0, stream>>>(
+            static_cast<float*>(x), L, H, sx, static_cast<const float*>(rcos), static_cast<const float*>(rsin), half,
+            offsets, offset_scalar, total);
+      }
+      return (int)cudaGetLastError();
+    }
+  }
   const long long total = (long long)B * L * H * half;
   if (total == 0) return 0;
-  const int threads = 256;
   const long long blocks = (total + threads - 1) / threads;
   if (blocks > 2147483647LL) return BASED_ERR_TOO_LARGE;
   if (io_dtype == BASED_BF16) {
@@ -247,6 +347,7 @@ int launch_swa_decode(const void* q, const void* k_new, const void* v_new, void*
                       Strides2 sk, Strides2 sv, Strides2 so, int window_left, float scale, int io_dtype,
                       cudaStream_t stream) {
   if (window_left + 1 > kMaxKeysPerLane * 32) return BASED_ERR_TOO_LARGE;
+  if (!aligned16(kv_cache) || hd % 8 != 0) return BASED_ERR_ALIGN;  // 16-byte reads of cached rows
   const int BH = B * H;
   const int grid = (BH + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if (io_dtype == BASED_BF16) {

@@ -42,8 +42,14 @@ class RotaryEmbedding(nn.Module):
         L = qkv.shape[1]
         need = max_seqlen if max_seqlen is not None else L + (0 if torch.is_tensor(seqlen_offset) else seqlen_offset)
         self._update_cos_sin_cache(max(need, L), device=qkv.device, dtype=qkv.dtype)
-        ops.rotary_apply_(qkv[:, :, 0], self._cos_cached, self._sin_cached, seqlen_offset)
-        ops.rotary_apply_(qkv[:, :, 1], self._cos_cached, self._sin_cached, seqlen_offset)
+        B, _, three, H, hd = qkv.shape
+        if qkv.stride(2) == H * hd and qkv.stride(3) == hd:
+            # q and k are adjacent in the packed tensor: one launch over 2H heads
+            qk = torch.as_strided(qkv, (B, L, 2 * H, hd), (qkv.stride(0), qkv.stride(1), hd, 1), qkv.storage_offset())
+            ops.rotary_apply_(qk, self._cos_cached, self._sin_cached, seqlen_offset)
+        else:
+            ops.rotary_apply_(qkv[:, :, 0], self._cos_cached, self._sin_cached, seqlen_offset)
+            ops.rotary_apply_(qkv[:, :, 1], self._cos_cached, self._sin_cached, seqlen_offset)
         return qkv
 
 

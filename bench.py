@@ -273,6 +273,35 @@ def norm_act_bench(ops, peaks):
             "gated_act": {"ms": ta, "bytes": ba, "hbm_frac": ba / (ta * 1e-3) / (peaks["hbm_gbs"] * 1e9)}}
 
 
+def generation_bench(B=16, L=2048, new_tokens=512):
+    """The 360M-parameter Based model (27 blocks: 17 BaseConv, 5 LinearAttention, 5 SlidingAttention; bf16,
+    random-init weights, synthetic token ids): one prompt pass over [B, L], then greedy single-token steps
+    replayed from a CUDA graph.  Device times by CUDA events inside generate()."""
+    from based_b200.model import BasedConfig, BasedLMHeadModel
+    torch.manual_seed(0)
+    cfg = BasedConfig.based_360m()
+    cfg.l_max = L + new_tokens
+    model = BasedLMHeadModel(cfg, device="cuda", dtype=torch.bfloat16).eval()
+    with torch.no_grad():
+        for prm in model.parameters():
+            if prm.dim() > 1:
+                prm.normal_(0, 0.02)
+    nparam = sum(p.numel() for p in model.parameters())
+    ids = torch.randint(0, cfg.vocab_size, (B, L), device="cuda")
+    model.generate(ids[:, :256], max_new_tokens=8, cg=True)   # warm-up: cuBLAS heuristics, rotary tables
+    t = {}
+    out = model.generate(ids, max_new_tokens=new_tokens, cg=True, timings=t)
+    assert out.shape == (B, L + new_tokens)
+    steps = new_tokens - 1  # the first new token comes from the prompt pass
+    res = {"model": "based-360m (random init)", "params": nparam, "B": B, "prompt": L, "new_tokens": new_tokens,
+           "prefill_ms": t["prefill_ms"], "prefill_tok_per_s": B * L / (t["prefill_ms"] * 1e-3),
+           "decode_ms_per_step": t["decode_ms"] / steps, "decode_tok_per_s": B * steps / (t["decode_ms"] * 1e-3),
+           "decode": "CUDA graph replay of one step (27 blocks + lm_head + argmax)"}
+    del model
+    torch.cuda.empty_cache()
+    return res
+
+
 def small_batch_prefill(ops, L):
     """One sequence (B=1, H=16, dv=64): one CTA per head against the sequence split the library picks."""
     g = torch.Generator(device="cuda").manual_seed(L + 1)
@@ -433,6 +462,8 @@ def main():
             line["prefill_small_batch"] = small_batch_prefill(ops, max(lengths))
             line["gated_conv"] = gated_conv_bench(ops, peaks)
             line["norm_act"] = norm_act_bench(ops, peaks)
+            if not args.quick:
+                line["generation_360m"] = generation_bench()
         if world == 1 and not args.no_cpu:
             use_all_host_threads()
             tput, dt = cpu_decode_baseline(B_DEC, 20, 2)
