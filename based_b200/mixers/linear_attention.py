@@ -11,6 +11,7 @@ import math
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from .. import ops
 from ..sharding import all_reduce_sum_, head_slice
@@ -61,6 +62,7 @@ class LinearAttention(nn.Module):
         parallel_implementation: str = "quadratic",
         state_dtype: torch.dtype = None,
         process_group=None,
+        fuse_qkv: bool = False,
         device=None,
         dtype=None,
         **kwargs,
@@ -97,6 +99,9 @@ class LinearAttention(nn.Module):
         # extension: dtype of freshly created prefill states; None = the activations' dtype,
         # which is what the reference's einsum produces (linear_attention.py:221-222)
         self.state_dtype = state_dtype
+        # extension: in eval mode run proj_q, proj_k, proj_v as ONE GEMM over their concatenated weights
+        # (the parameters stay separate, so reference checkpoints still load)
+        self.fuse_qkv = fuse_qkv
         fk = {"device": device, "dtype": dtype}
         self.proj_q = nn.Linear(self.d_model, self.feature_dim * self.num_heads, bias=False, **fk)
         self.proj_k = nn.Linear(self.d_model, self.feature_dim * self.num_heads, bias=False, **fk)
@@ -108,7 +113,14 @@ class LinearAttention(nn.Module):
         Extra keyword arguments the model passes to every mixer (``position_ids``, ``decay``,
         ``stream``, ``seqlen``) are accepted and ignored, as in the reference."""
         b, l, _ = hidden_states.size()
-        q, k, v = self.proj_q(hidden_states), self.proj_k(hidden_states), self.proj_v(hidden_states)
+        if self.fuse_qkv and not self.training:
+            # one GEMM for the three projections; q, k, v are column slices of its output (the kernels take
+            # strided views), so nothing is copied
+            nq = self.feature_dim * self.num_heads
+            qkv = F.linear(hidden_states, self._fused_qkv_weight())
+            q, k, v = qkv[..., :nq], qkv[..., nq:2 * nq], qkv[..., 2 * nq:]
+        else:
+            q, k, v = self.proj_q(hidden_states), self.proj_k(hidden_states), self.proj_v(hidden_states)
         q = q.view(b, l, self.num_heads, self.feature_dim).transpose(1, 2)
         k = k.view(b, l, self.num_heads, self.feature_dim).transpose(1, 2)
         v = v.view(b, l, self.num_heads, self.head_dim).transpose(1, 2)
@@ -131,6 +143,16 @@ class LinearAttention(nn.Module):
         else:
             inference_params.key_value_memory_dict[self.layer_idx] = (kv_state, k_state)
         return y
+
+    def _fused_qkv_weight(self):
+        """``cat(proj_q.weight, proj_k.weight, proj_v.weight)``, rebuilt when a projection changes
+        (in-place update, new storage, dtype or device)."""
+        ws = (self.proj_q.weight, self.proj_k.weight, self.proj_v.weight)
+        key = tuple((w._version, w.data_ptr(), w.dtype, w.device) for w in ws)
+        if getattr(self, "_wqkv_key", None) != key:
+            self._wqkv = torch.cat([w.detach() for w in ws], dim=0).contiguous()
+            self._wqkv_key = key
+        return self._wqkv
 
     def parallel_forward(self, x, q, k, v, kv_state=None, k_state=None):
         """Whole-sequence path (linear_attention.py:152-227): q, k ``[B, H, L, 16]`` raw,

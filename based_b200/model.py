@@ -70,7 +70,8 @@ class Block(nn.Module):
         self.residual_in_fp32 = config.residual_in_fp32
         if layer_idx in config.alt_mixer_layers:
             self.mixer = LinearAttention(d, feature_map=TaylorExp(input_dim=config.feature_dim), l_max=config.l_max,
-                                         feature_dim=config.feature_dim, num_heads=config.n_head, layer_idx=layer_idx, **fk)
+                                         feature_dim=config.feature_dim, num_heads=config.n_head, layer_idx=layer_idx,
+                                         fuse_qkv=True, **fk)
         elif layer_idx in config.alt_mixer_2_layers:
             head_dim = d // config.n_head
             self.mixer = SlidingAttention(d, num_heads=config.n_head, window_size=config.window_size, causal=True,

@@ -117,3 +117,27 @@ def test_sliding_attention_mixer_prefill_and_decode(rotary):
             ip.seqlen_offset = L + s
             y = m(x[:, L + s:L + s + 1].cuda(), inference_params=ip)
             assert rel_err(y.float().cpu(), ref_full[:, L + s:L + s + 1]) < 3e-2, s
+
+
+def test_linear_attention_fused_qkv_projection_is_the_same_mixer():
+    """One GEMM over the concatenated projection weights: same outputs and states, prompt pass and steps;
+    a later change of a projection weight is picked up."""
+    import copy
+    from based_b200.generation import InferenceParams
+    from based_b200.mixers import LinearAttention, TaylorExp
+    torch.manual_seed(3)
+    a = LinearAttention(256, feature_map=TaylorExp(input_dim=16), num_heads=4, layer_idx=0).to("cuda", torch.bfloat16).eval()
+    b = copy.deepcopy(a)
+    b.fuse_qkv = True
+    x = torch.randn(2, 200, 256, device="cuda", dtype=torch.bfloat16)
+    with torch.inference_mode():
+        ia, ib = InferenceParams(max_seqlen=256, max_batch_size=2), InferenceParams(max_seqlen=256, max_batch_size=2)
+        ya, yb = a(x, inference_params=ia), b(x, inference_params=ib)
+        assert torch.equal(ya, yb)
+        assert torch.equal(ia.key_value_memory_dict[0][0], ib.key_value_memory_dict[0][0])
+        ia.seqlen_offset = ib.seqlen_offset = 200
+        xt = torch.randn(2, 1, 256, device="cuda", dtype=torch.bfloat16)
+        assert torch.allclose(a(xt, inference_params=ia).float(), b(xt, inference_params=ib).float(), atol=2e-2, rtol=2e-2)
+        b.proj_v.weight.mul_(2.0)
+        a.proj_v.weight.mul_(2.0)
+        assert torch.equal(a(x), b(x))
