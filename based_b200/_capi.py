@@ -39,6 +39,8 @@ SIGNATURES = {
     "based_gated_conv_step": (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "based_add_rmsnorm": (c_int, [c_void_p] * 6 + [c_int64, c_int] + [c_int64] * 4 + [c_float, c_int, c_int, c_int, c_int, c_void_p]),
     "based_gated_act": (c_int, [c_void_p] * 3 + [c_int64, c_int] + [c_int64] * 3 + [c_int, c_int, c_void_p]),
+    "based_decode_linear": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_int64] * 2 + [c_int, c_int]
+                            + [c_void_p] * 3 + [c_int, c_int, c_void_p]),
 }
 
 _lib = None

@@ -265,4 +265,20 @@ int based_gated_act(const void* y, const void* gate, void* out, int64_t M, int F
                           static_cast<cudaStream_t>(stream));
 }
 
+int based_decode_linear(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                        int64_t x_row_stride, int64_t out_row_stride, int epilogue, int act, void* conv_state,
+                        const void* conv_weight, const void* conv_bias, int conv_k, int conv_w_dtype, void* stream) {
+  if (!x || !w || !out) return BASED_ERR_NULL;
+  if (M < 0 || N <= 0 || K <= 0 || M > 65535 * 16) return BASED_ERR_SHAPE;
+  if (epilogue == BASED_EPI_GATED && act != BASED_ACT_SILU && act != BASED_ACT_SIGMOID) return BASED_ERR_SHAPE;
+  if (epilogue == BASED_EPI_CONV) {
+    if (!conv_state || !conv_weight) return BASED_ERR_NULL;
+    if (conv_k < 1 || conv_k > 8) return BASED_ERR_SHAPE;
+    if (!dtype_ok(conv_w_dtype)) return BASED_ERR_DTYPE;
+  }
+  if (M == 0) return BASED_OK;
+  return launch_decode_linear(x, w, bias, out, M, N, K, x_row_stride, out_row_stride, epilogue, act, conv_state,
+                              conv_weight, conv_bias, conv_k, conv_w_dtype, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -120,9 +120,18 @@ class BaseConv(nn.Module):
     def forward(self, u, position_ids=None, inference_params=None, *args, **kwargs):
         """u ``[B, L, d_model]`` -> ``[B, L, d_model]``; with ``inference_params`` the prompt pass
         fills the convolution state and later single-token calls step it."""
-        u = self.in_proj(u)
+        if inference_params is not None and inference_params.seqlen_offset > 0:
+            state = self.conv._get_state(inference_params)
+            if (ops.DECODE_LINEAR_USE["conv"] and ops._decode_rows(u, self.in_proj.weight)
+                    and state.dtype == torch.bfloat16 and state.is_contiguous()
+                    and state.shape[0] == u.shape[0] and u.shape[1] == 1 and self.d_inner % 8 == 0):
+                # decode step: in_proj, the convolution step on the state, silu and the gate in one launch
+                v = ops.decode_linear(u, self.in_proj.weight, self.in_proj.bias, epilogue="conv", conv_state=state,
+                                      conv_weight=self.conv.conv.weight, conv_bias=self.conv.conv.bias)
+                return ops.linear(v, self.out_proj.weight, self.out_proj.bias)
+        u = ops.linear(u, self.in_proj.weight, self.in_proj.bias)
         v = self.conv.gated(u, inference_params=inference_params)
-        return self.out_proj(v)
+        return ops.linear(v, self.out_proj.weight, self.out_proj.bias)
 
     def allocate_inference_cache(self, batch_size: int, max_seqlen: int, dtype=None, **kwargs):
         return {"conv": self.conv.allocate_inference_cache(batch_size, max_seqlen, dtype=dtype, **kwargs)}

@@ -117,7 +117,7 @@ class LinearAttention(nn.Module):
             # one GEMM for the three projections; q, k, v are column slices of its output (the kernels take
             # strided views), so nothing is copied
             nq = self.feature_dim * self.num_heads
-            qkv = F.linear(hidden_states, self._fused_qkv_weight())
+            qkv = ops.linear(hidden_states, self._fused_qkv_weight())
             q, k, v = qkv[..., :nq], qkv[..., nq:2 * nq], qkv[..., 2 * nq:]
         else:
             q, k, v = self.proj_q(hidden_states), self.proj_k(hidden_states), self.proj_v(hidden_states)
@@ -177,7 +177,7 @@ class LinearAttention(nn.Module):
         assert l == 1, f"q.shape is {q.shape} but should be ({b}, {h}, 1, {d})"
         eps = 1e-6 if "fla" in self.parallel_implementation else 1e-12
         y = ops.linattn_decode(q, k, v, kv_state, k_state, eps=eps)
-        return all_reduce_sum_(self.out_proj(y), self.process_group)
+        return all_reduce_sum_(ops.linear(y, self.out_proj.weight, self.out_proj.bias), self.process_group)
 
     def expanded_size(self):
         return self.feature_dim ** 2 + self.feature_dim + 1

@@ -142,7 +142,7 @@ class SlidingAttention(nn.Module):
         if self.training and self.dropout_p > 0:
             raise NotImplementedError("attention dropout is not implemented (inference kernels)")
         batch, seqlen = x.shape[:2]
-        qkv = self.Wqkv(x)
+        qkv = ops.linear(x, self.Wqkv.weight, self.Wqkv.bias)
         in_dtype = qkv.dtype
         if in_dtype == torch.float16:
             raise TypeError("float16 is not supported by the B200 kernels; use bfloat16")
@@ -174,5 +174,5 @@ class SlidingAttention(nn.Module):
             context = ops.swa_decode(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], cache, lens, w, self.softmax_scale,
                                      rotary_cos=cos, rotary_sin=sin)
         context = context.to(in_dtype).reshape(batch, seqlen, self.num_heads * self.head_dim)
-        out = all_reduce_sum_(self.out_proj(context), self.process_group)
+        out = all_reduce_sum_(ops.linear(context, self.out_proj.weight, self.out_proj.bias), self.process_group)
         return out if not self.return_residual else (out, x)

@@ -17,6 +17,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import ops
 from .generation import InferenceParams
 from .mixers import BaseConv, LinearAttention, SlidingAttention, TaylorExp
 from .modules import GatedMlp, RMSNorm
@@ -146,7 +147,7 @@ class BasedLMHeadModel(nn.Module):
         hidden_states = self.transformer(input_ids, inference_params=inference_params)
         if num_last_tokens > 0:
             hidden_states = hidden_states[:, -num_last_tokens:]
-        return self.lm_head(hidden_states)
+        return ops.linear(hidden_states, self.lm_head.weight, self.lm_head.bias)
 
     @torch.inference_mode()
     def generate(self, input_ids, max_new_tokens: int, cg: bool = False, timings: Optional[dict] = None):

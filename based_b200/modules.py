@@ -50,12 +50,16 @@ class GatedMlp(nn.Module):
         self.fc2 = nn.Linear(hidden_features, out_features, bias=bias2, **fk)
 
     def forward(self, x):
-        y = self.fc1(x)
         if self.activation in (F.sigmoid, torch.sigmoid):
-            y = ops.gated_act(y, "sigmoid")
+            act = "sigmoid"
         elif self.activation is F.silu:
-            y = ops.gated_act(y, "silu")
+            act = "silu"
         else:
             raise NotImplementedError("GatedMlp: activation must be F.silu (SwiGLU) or F.sigmoid (GLU)")
-        y = self.fc2(y)
+        if ops.DECODE_LINEAR_USE["gated"] and ops._decode_rows(x, self.fc1.weight) and self.fc1.weight.shape[0] % 16 == 0:
+            # decode step: fc1 and the gated activation in one launch, fc2 in another
+            y = ops.decode_linear(x, self.fc1.weight, self.fc1.bias, epilogue="gated", activation=act)
+        else:
+            y = ops.gated_act(self.fc1(x), act)
+        y = ops.linear(y, self.fc2.weight, self.fc2.bias)
         return y if not self.return_residual else (y, x)

@@ -385,3 +385,65 @@ def gated_act(y: torch.Tensor, activation: str = "silu") -> torch.Tensor:
                                                g.stride(0), out.stride(0), _ACTS[activation], _dt(y.dtype), _stream())
         _capi.check(code, "based_gated_act")
     return out.reshape(*y.shape[:-1], F)
+
+
+DECODE_LINEAR_MAX_ROWS = 64  # beyond this the library GEMM is the better tool
+# Which decode-step products the mixers and the MLP hand to decode_linear instead of cuBLAS (+ a separate
+# elementwise launch).  Measured on the 360M model at batch 16 with the weights streaming from HBM
+# (ms per decode step): none 1.146, gated 1.089, gated + conv 1.145, all three 1.329 -- only fc1 + SwiGLU pays.
+DECODE_LINEAR_USE = {"plain": False, "gated": True, "conv": False}
+
+
+def decode_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
+                  epilogue: str = "plain", activation: str = "silu", conv_state: Optional[torch.Tensor] = None,
+                  conv_weight: Optional[torch.Tensor] = None, conv_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x W^T (+ bias)`` for the few rows of a decode step (bf16), with a fused epilogue:
+    ``"plain"``; ``"gated"`` -> ``first_half * act(second_half)`` (mlp.py:146-154); ``"conv"`` -> the BaseConv
+    decode step on the first half (``conv_state [M, N/2, k]`` updated in place), silu, gate by the second half
+    (convolution.py:88-109, :205-211).  x ``[..., K]``; returns ``[..., N]`` or ``[..., N/2]``."""
+    _need_cuda(x, weight, bias, conv_state, conv_weight, conv_bias)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise TypeError("decode_linear takes bfloat16 activations and weights")
+    K = x.shape[-1]
+    x2 = x.reshape(-1, K)
+    _inner_contig(x2, "x")
+    M, N = x2.shape[0], weight.shape[0]
+    if weight.shape[1] != K or not weight.is_contiguous():
+        raise ValueError("weight must be a contiguous [N, K] tensor")
+    epi = {"plain": 0, "gated": 1, "conv": 2}[epilogue]
+    n_out = N if epi == 0 else N // 2
+    out = torch.empty(M, n_out, dtype=torch.bfloat16, device=x.device)
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    ck, cw_dt = 0, BASED_BF16
+    if epi == 2:
+        conv_weight = conv_weight.reshape(conv_weight.shape[0], -1).contiguous()
+        ck, cw_dt = conv_weight.shape[1], _dt(conv_weight.dtype)
+        if conv_bias is not None:
+            conv_bias = conv_bias.to(conv_weight.dtype).contiguous()
+        if conv_state.shape != (M, n_out, ck) or conv_state.dtype != torch.bfloat16 or not conv_state.is_contiguous():
+            raise ValueError("conv_state must be a contiguous bfloat16 [M, N/2, k] tensor")
+    if M > 0:
+        with torch.cuda.device(x.device):
+            code = _capi.lib().based_decode_linear(
+                x2.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                M, N, K, x2.stride(0), out.stride(0), epi, _ACTS[activation],
+                conv_state.data_ptr() if epi == 2 else None, conv_weight.data_ptr() if epi == 2 else None,
+                conv_bias.data_ptr() if (epi == 2 and conv_bias is not None) else None, ck, cw_dt, _stream())
+        _capi.check(code, "based_decode_linear")
+    return out.reshape(*x.shape[:-1], n_out)
+
+
+def _decode_rows(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """True when ``x W^T`` is a decode-step product the library's own kernel should run."""
+    rows = x.numel() // x.shape[-1] if x.numel() else 0
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < rows <= DECODE_LINEAR_MAX_ROWS
+            and x.shape[-1] % 32 == 0 and weight.shape[0] % 8 == 0 and weight.is_contiguous() and x.stride(-1) == 1
+            and not torch.is_grad_enabled())
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``nn.functional.linear`` for the mixers: the decode-step kernel for a few bf16 rows, cuBLAS otherwise."""
+    if DECODE_LINEAR_USE["plain"] and _decode_rows(x, weight):
+        return decode_linear(x, weight, bias)
+    return torch.nn.functional.linear(x, weight, bias)

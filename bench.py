@@ -288,7 +288,7 @@ def generation_bench(B=16, L=2048, new_tokens=512):
                 prm.normal_(0, 0.02)
     nparam = sum(p.numel() for p in model.parameters())
     ids = torch.randint(0, cfg.vocab_size, (B, L), device="cuda")
-    model.generate(ids[:, :256], max_new_tokens=8, cg=True)   # warm-up: cuBLAS heuristics, rotary tables
+    model.generate(ids, max_new_tokens=8, cg=True)   # warm-up at full size: allocator, cuBLAS heuristics, rotary tables
     t = {}
     out = model.generate(ids, max_new_tokens=new_tokens, cg=True, timings=t)
     assert out.shape == (B, L + new_tokens)

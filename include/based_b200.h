@@ -308,6 +308,35 @@ int based_gated_act(const void* y, const void* gate, void* out,
                     int64_t y_row_stride, int64_t gate_row_stride, int64_t out_row_stride,
                     int act, int io_dtype, void* stream);
 
+/* epilogue selectors of based_decode_linear */
+#define BASED_EPI_PLAIN 0  /* out[M, N]   = x W^T + bias */
+#define BASED_EPI_GATED 1  /* out[M, N/2] = (x W1^T + b1) * act(x W2^T + b2), W = [W1; W2], act as in based_gated_act */
+#define BASED_EPI_CONV 2   /* out[M, N/2] = silu(conv_step(u1)) * u2 with [u1 | u2] = x W^T + bias */
+
+/*
+ * A linear layer on the few rows of a decode step (one token per sequence), bf16, with the
+ * elementwise step that follows it in the Based blocks fused into the epilogue.
+ *
+ * Replaces, for single-token steps, nn.Linear calls of the mixers and the MLP
+ * (based/models/mixers/linear_attention.py:126-128, :251; slide_attention.py:544, :599;
+ * convolution.py:205, :212; based/models/mlp.py:142, :155) together with
+ *   GATED: `y, gate = y.chunk(2, dim=-1); y = y * act(gate)` (mlp.py:146-154)
+ *   CONV:  ShortConvolution.step + silu + gate (convolution.py:88-109, :205-211); `conv_state`
+ *          [M, N/2, conv_k] (bf16) is updated in place, taps conv_weight [N/2, conv_k] and
+ *          conv_bias [N/2] (or NULL) are in conv_w_dtype
+ * which the reference runs as separate cuBLAS and elementwise launches.
+ *
+ *   x [M, K], W [N, K] (nn.Linear layout, contiguous), bias [N] or NULL, out as above; all bf16;
+ *   row strides in elements.  K a multiple of 32; the number of outputs a multiple of 8;
+ *   x and W 16-byte aligned, x_row_stride a multiple of 8.  Built for M <= 16 (weights are read
+ *   once per 16 rows); larger M works and re-reads W from L2 per 16 rows.
+ */
+int based_decode_linear(const void* x, const void* w, const void* bias, void* out,
+                        int M, int N, int K, int64_t x_row_stride, int64_t out_row_stride,
+                        int epilogue, int act,
+                        void* conv_state, const void* conv_weight, const void* conv_bias,
+                        int conv_k, int conv_w_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
