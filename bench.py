@@ -273,13 +273,14 @@ def norm_act_bench(ops, peaks):
             "gated_act": {"ms": ta, "bytes": ba, "hbm_frac": ba / (ta * 1e-3) / (peaks["hbm_gbs"] * 1e9)}}
 
 
-def generation_bench(B=16, L=2048, new_tokens=512):
-    """The 360M-parameter Based model (27 blocks: 17 BaseConv, 5 LinearAttention, 5 SlidingAttention; bf16,
-    random-init weights, synthetic token ids): one prompt pass over [B, L], then greedy single-token steps
-    replayed from a CUDA graph.  Device times by CUDA events inside generate()."""
+def generation_bench(B=16, L=2048, new_tokens=512, size="360m"):
+    """The 360M-parameter Based model (27 blocks: 17 BaseConv, 5 LinearAttention, 5 SlidingAttention) or the
+    1.4B one (36 blocks: 22 / 7 / 7, d_model 1792, head_dim 112); bf16, random-init weights, synthetic token
+    ids: one prompt pass over [B, L], then greedy single-token steps replayed from a CUDA graph.  Device times
+    by CUDA events inside generate()."""
     from based_b200.model import BasedConfig, BasedLMHeadModel
     torch.manual_seed(0)
-    cfg = BasedConfig.based_360m()
+    cfg = BasedConfig.based_360m() if size == "360m" else BasedConfig.based_1b()
     cfg.l_max = L + new_tokens
     model = BasedLMHeadModel(cfg, device="cuda", dtype=torch.bfloat16).eval()
     with torch.no_grad():
@@ -293,10 +294,10 @@ def generation_bench(B=16, L=2048, new_tokens=512):
     out = model.generate(ids, max_new_tokens=new_tokens, cg=True, timings=t)
     assert out.shape == (B, L + new_tokens)
     steps = new_tokens - 1  # the first new token comes from the prompt pass
-    res = {"model": "based-360m (random init)", "params": nparam, "B": B, "prompt": L, "new_tokens": new_tokens,
+    res = {"model": f"based-{size} (random init)", "params": nparam, "B": B, "prompt": L, "new_tokens": new_tokens,
            "prefill_ms": t["prefill_ms"], "prefill_tok_per_s": B * L / (t["prefill_ms"] * 1e-3),
            "decode_ms_per_step": t["decode_ms"] / steps, "decode_tok_per_s": B * steps / (t["decode_ms"] * 1e-3),
-           "decode": "CUDA graph replay of one step (27 blocks + lm_head + argmax)"}
+           "decode": f"CUDA graph replay of one step ({cfg.n_layer} blocks + lm_head + argmax)"}
     del model
     torch.cuda.empty_cache()
     return res
@@ -451,9 +452,9 @@ def main():
             "gpu_launches": K,
             "clocks": clocks,
         }
-        traffic_file = os.path.join(ROOT, "profiles", "decode_traffic_bytes.json")
-        if os.path.exists(traffic_file):
-            line["roofline"]["traffic"] = json.load(open(traffic_file)).get("dram_bytes_per_launch")
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu
+        # capture summarised in profiles/linattn_decode_B256_H16.md (291.5 MB + 233.0 MB)
+        line["roofline"]["traffic"] = 524.5e6
         if world == 1 and not args.no_sweep:
             lengths = args.sweep_L if args.sweep_L else ([2048] if args.quick else [2048, 8192, 32768])
             lin, swa = prefill_sweep(ops, peaks, lengths)
@@ -464,6 +465,8 @@ def main():
             line["norm_act"] = norm_act_bench(ops, peaks)
             if not args.quick:
                 line["generation_360m"] = generation_bench()
+                # the per-GPU share of the 8-GPU generation config: 8 of 64 sequences, prompt 4096, 1024 new tokens
+                line["generation_1b"] = generation_bench(B=8, L=4096, new_tokens=1024, size="1b")
         if world == 1 and not args.no_cpu:
             use_all_host_threads()
             tput, dt = cpu_decode_baseline(B_DEC, 20, 2)
