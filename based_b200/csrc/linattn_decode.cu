@@ -10,9 +10,23 @@
 // One row of 273 elements is not 16-byte aligned, but RPG = 16/sizeof(state) consecutive rows
 // are exactly 273 sixteen-byte vectors.  A warp owns such a row group: 128-bit coalesced
 // loads, FMA, 128-bit stores, and a per-row dot product with phi(q) reduced by shuffles.
+//
+// Two kernels.  The staged one (linattn_decode_staged_kernel) is persistent: one CTA per SM
+// walks over (batch, head) blocks; the whole [dv, 273] state block of an item (70 KB at dv = 64,
+// fp32) is brought into shared memory by ONE bulk async copy (cp.async.bulk, completion on an
+// mbarrier), updated in place there, and written back by ONE bulk store, with three blocks in
+// rotation per CTA (one being loaded, one computed on, one being stored).  The copies are issued
+// by a single thread and need no registers, so ~140 KB per SM are in flight all the time and no
+// warp ever waits on a global load.  The direct kernel (linattn_decode_kernel) streams the state
+// through registers, one CTA per item; it serves shapes whose blocks do not fit in shared memory
+// three (or two) times.
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace based {
+
+__device__ unsigned int g_decode_status = 0;  // ORed with a code when a bounded wait expires
+
 namespace {
 
 constexpr int kThreads = 256;
@@ -176,9 +190,242 @@ linattn_decode_kernel(const IO* __restrict__ q, const IO* __restrict__ k, const 
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Staged persistent kernel.  Shared memory: NSTAGE state blocks | tables | small vectors | barriers.
+struct StagedParams {
+  const void *q, *k, *v;
+  void *y, *kv_state, *k_state;
+  int H, dv, items, nstage;
+  uint32_t block_bytes;
+  Strides2 sq, sk, sv, sy;
+  float eps;
+  unsigned int* status;
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst_saddr, const void* gsrc, uint32_t bytes, uint32_t mbar_saddr) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst_saddr),
+               "l"(gsrc), "r"(bytes), "r"(mbar_saddr)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar_saddr, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(mbar_saddr),
+               "r"(bytes)
+               : "memory");
+}
+// at most one committed bulk store still reads its shared-memory source
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory"); }
+
+constexpr int kStagedThreads = 512;  // one CTA per SM: sixteen warps share the in-place update of a block
+constexpr int kStagedWarps = kStagedThreads / 32;
+
+template <typename IO, typename ST>
+__global__ void __launch_bounds__(kStagedThreads, 1) linattn_decode_staged_kernel(const StagedParams p) {
+  using VO = VecOps<ST>;
+  constexpr int VEC = VO::kVec;
+  constexpr int RPG = VEC;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int dv = p.dv, NS = p.nstage;
+  const uint32_t blk = p.block_bytes;
+  // layout
+  uint8_t* tabs = smem + (size_t)NS * blk;
+  float (*s_tq)[kTab] = reinterpret_cast<float (*)[kTab]>(tabs);
+  float (*s_tk)[kTab] = reinterpret_cast<float (*)[kTab]>(tabs + 4 * kTab * sizeof(float));
+  float* s_x = reinterpret_cast<float*>(tabs + 8 * kTab * sizeof(float));  // [2][16]
+  float* s_v = s_x + 2 * kFeatureDim;                                      // [128]
+  float* s_num = s_v + 128;                                                // [128]
+  float* s_den = s_num + 128;                                              // [1] (+3 pad)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_den + 4);                 // [NS] full barriers
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 4);
+  const uint32_t sb = tc::smem_u32(smem), bar0 = tc::smem_u32(bars);
+
+  const IO* q = static_cast<const IO*>(p.q);
+  const IO* k = static_cast<const IO*>(p.k);
+  const IO* v = static_cast<const IO*>(p.v);
+  IO* y = static_cast<IO*>(p.y);
+  ST* kv_state = static_cast<ST*>(p.kv_state);
+  ST* k_state = static_cast<ST*>(p.k_state);
+
+  if (tid == 0) {
+    for (int i = 0; i < NS; ++i) tc::mbar_init(bar0 + 8 * i, 1);
+    *abort_flag = 0;
+    tc::fence_mbar_init();
+  }
+  __syncthreads();
+  // items of this CTA: blockIdx.x, + gridDim.x, ...; item j of the CTA uses stage j % NS, phase (j / NS) & 1
+  const int first = blockIdx.x, step = gridDim.x;
+  const int nmine = first < p.items ? (p.items - first + step - 1) / step : 0;
+  auto issue_load = [&](int j) {  // thread 0 only
+    const int item = first + j * step;
+    const uint32_t bar = bar0 + 8 * (j % NS);
+    mbar_expect_tx(bar, blk);
+    bulk_load(sb + (j % NS) * blk, reinterpret_cast<const uint8_t*>(kv_state) + (size_t)item * blk, blk, bar);
+  };
+  if (tid == 0)
+    for (int j = 0; j < NS - 1 && j < nmine; ++j) issue_load(j);
+
+  for (int j = 0; j < nmine; ++j) {
+    const int bh = first + j * step;
+    const int b = bh / p.H, h = bh - b * p.H;
+    // ---- this item's q, k, v and the shifted feature tables (while its state block is in flight)
+    if (tid < kFeatureDim) {
+      s_x[tid] = to_float(q[b * p.sq.b + h * p.sq.h + tid]);
+    } else if (tid < 2 * kFeatureDim) {
+      s_x[tid] = to_float(k[b * p.sk.b + h * p.sk.h + tid - kFeatureDim]);
+    } else if (tid - 2 * kFeatureDim < dv) {
+      s_v[tid - 2 * kFeatureDim] = to_float(v[b * p.sv.b + h * p.sv.h + tid - 2 * kFeatureDim]);
+    }
+    // the k_state row of this item: the last warp fetches it now and uses it after the tables are built
+    float ksr[kIters];
+    if (warp == kStagedWarps - 1) {
+      const ST* ks = k_state + (size_t)bh * kExpandedDim;
+#pragma unroll
+      for (int n = 0; n < kIters; ++n) {
+        const int f = lane + 32 * n;
+        ksr[n] = f < kExpandedDim ? to_float(ks[f]) : 0.f;
+      }
+    }
+    __syncthreads();
+#ifndef BASED_DEC_SKIP_TABLES
+    for (int idx = tid; idx < 2 * 4 * kTab; idx += kStagedThreads) {
+      const int which = idx / (4 * kTab);
+      const int rem = idx - which * 4 * kTab;
+      const int s = rem / kTab, i = rem - s * kTab;
+      int f = i + s;
+      if (f >= kExpandedDim) f -= kExpandedDim;
+      const float val = taylor_feature(s_x + which * kFeatureDim, f);
+      if (which == 0) s_tq[s][i] = val; else s_tk[s][i] = val;
+    }
+#endif
+    __syncthreads();
+    // ---- k_state (1 KB): last warp, straight from / to global
+    if (warp == kStagedWarps - 1) {
+      ST* ks = k_state + (size_t)bh * kExpandedDim;
+      float den = 0.f;
+#pragma unroll
+      for (int n = 0; n < kIters; ++n) {
+        const int f = lane + 32 * n;
+        if (f < kExpandedDim) {
+          const float nw = VO::round(ksr[n] + s_tk[0][f]);
+          ks[f] = from_float<ST>(nw);
+          den += s_tq[0][f] * nw;
+        }
+      }
+      den = warp_sum(den);
+      if (lane == 0) *s_den = den;
+    }
+    // ---- the state block has landed?
+    tc::mbar_wait_bounded(bar0 + 8 * (j % NS), (uint32_t)((j / NS) & 1), abort_flag, p.status, 0x10000u);
+    uint8_t* blkp = smem + (size_t)(j % NS) * blk;
+    const int ngroups = dv / RPG;
+#ifdef BASED_DEC_SKIP_COMPUTE
+    for (int g = warp; g < 0; g += kStagedWarps) {
+#else
+    for (int g = warp; g < ngroups; g += kStagedWarps) {
+#endif
+      uint4* base = reinterpret_cast<uint4*>(blkp + (size_t)g * RPG * kExpandedDim * sizeof(ST));
+      float acc[RPG];
+#pragma unroll
+      for (int rr = 0; rr < RPG; ++rr) acc[rr] = 0.f;
+#pragma unroll
+      for (int n = 0; n < kIters; ++n) {
+        const int idx = lane + 32 * n;
+        if (idx < kVecPerGroup) {
+          const int e0 = idx * VEC;
+          const int row0 = e0 / kExpandedDim;
+          const int f0 = e0 - row0 * kExpandedDim;
+          const int s = f0 & 3, i = f0 - s;
+          float pk[VEC], pq[VEC], e[VEC];
+#pragma unroll
+          for (int c4 = 0; c4 < VEC / 4; ++c4) {
+            const float4 a = *reinterpret_cast<const float4*>(&s_tk[s][i + 4 * c4]);
+            const float4 bq = *reinterpret_cast<const float4*>(&s_tq[s][i + 4 * c4]);
+            pk[4 * c4] = a.x; pk[4 * c4 + 1] = a.y; pk[4 * c4 + 2] = a.z; pk[4 * c4 + 3] = a.w;
+            pq[4 * c4] = bq.x; pq[4 * c4 + 1] = bq.y; pq[4 * c4 + 2] = bq.z; pq[4 * c4 + 3] = bq.w;
+          }
+          VO::unpack(base[idx], e);
+          const int rbase = g * RPG + row0;
+          const float v0 = s_v[rbase];
+          const float v1 = s_v[min(rbase + 1, dv - 1)];
+          const int cwrap = kExpandedDim - f0;  // elements c >= cwrap belong to row0 + 1
+          float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+          for (int c = 0; c < VEC; ++c) {
+            const bool hi = c >= cwrap;
+            const float nw = VO::round(fmaf(pk[c], hi ? v1 : v0, e[c]));
+            e[c] = nw;
+            const float contrib = pq[c] * nw;
+            a0 += hi ? 0.f : contrib;
+            a1 += hi ? contrib : 0.f;
+          }
+          base[idx] = VO::pack(e);
+#pragma unroll
+          for (int rr = 0; rr < RPG; ++rr) {
+            acc[rr] += (row0 == rr) ? a0 : 0.f;
+            acc[rr] += (row0 + 1 == rr) ? a1 : 0.f;
+          }
+        }
+      }
+#pragma unroll
+      for (int rr = 0; rr < RPG; ++rr) {
+        const float t = warp_sum(acc[rr]);
+        if (lane == 0) s_num[g * RPG + rr] = t;
+      }
+    }
+    tc::fence_proxy_async();  // this thread's shared-memory writes, before the bulk store reads them
+    __syncthreads();
+    if (tid == 0) {
+      tc::bulk_store(reinterpret_cast<uint8_t*>(kv_state) + (size_t)bh * blk, sb + (j % NS) * blk, blk);
+      tc::bulk_commit();
+      // the stage that item j + NS - 1 will use is the one item j - 1 was stored from
+      if (j + NS - 1 < nmine) {
+        bulk_wait_read_1();
+        issue_load(j + NS - 1);
+      }
+    }
+    if (tid < dv) y[b * p.sy.b + h * p.sy.h + tid] = from_float<IO>(s_num[tid] / (*s_den + p.eps));
+    // the next iteration's first __syncthreads orders these reads of s_num / s_den before their next writes
+  }
+  if (tid == 0) tc::bulk_wait_all();
+}
+
+template <typename IO, typename ST>
+int launch_staged(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state, int B, int H,
+                  int dv, Strides2 sq, Strides2 sk, Strides2 sv, Strides2 sy, float eps, cudaStream_t stream) {
+  const size_t blk = (size_t)dv * kExpandedDim * sizeof(ST);
+  const size_t extra = 8 * kTab * sizeof(float) + (2 * kFeatureDim + 128 + 128 + 4) * sizeof(float) + 4 * 8 + 16;
+  int dev = 0, smem_max = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return BASED_ERR_IMPL;
+  int nstage = 3;
+  while (nstage >= 2 && nstage * blk + extra > (size_t)smem_max) --nstage;
+  if (nstage < 2 || blk % 16 != 0 || blk >= (1u << 20) || !aligned16(kv_state)) return BASED_ERR_IMPL;
+  StagedParams p{q, k, v, y, kv_state, k_state, H, dv, B * H, nstage, (uint32_t)blk, sq, sk, sv, sy, eps, nullptr};
+  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_decode_status);
+  if (e != cudaSuccess) return (int)e;
+  const int smem = (int)(nstage * blk + extra);
+  e = cudaFuncSetAttribute(linattn_decode_staged_kernel<IO, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return (int)e;
+  const int grid = B * H < sms ? B * H : sms;
+  linattn_decode_staged_kernel<IO, ST><<<grid, kStagedThreads, smem, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 template <typename IO, typename ST>
 int launch_typed(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state, int B, int H,
                  int dv, Strides2 sq, Strides2 sk, Strides2 sv, Strides2 sy, float eps, cudaStream_t stream) {
+  // the staged kernel when the state block fits in shared memory at least twice, and there is more than one
+  // block per SM to rotate through; else the direct one
+  {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && B * H >= 2 * sms) {
+      const int rc = launch_staged<IO, ST>(q, k, v, y, kv_state, k_state, B, H, dv, sq, sk, sv, sy, eps, stream);
+      if (rc != BASED_ERR_IMPL) return rc;
+    }
+  }
   linattn_decode_kernel<IO, ST><<<B * H, kThreads, 0, stream>>>(
       static_cast<const IO*>(q), static_cast<const IO*>(k), static_cast<const IO*>(v), static_cast<IO*>(y),
       static_cast<ST*>(kv_state), static_cast<ST*>(k_state), H, dv, sq, sk, sv, sy, eps);
@@ -186,6 +433,18 @@ int launch_typed(const void* q, const void* k, const void* v, void* y, void* kv_
 }
 
 }  // namespace
+
+int read_decode_status(unsigned int* out, int reset) {
+  unsigned int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(v));
+  if (e != cudaSuccess) return (int)e;
+  if (out) *out = v;
+  if (reset && v != 0) {
+    v = 0;
+    e = cudaMemcpyToSymbol(g_decode_status, &v, sizeof(v));
+  }
+  return (int)e;
+}
 
 int launch_linattn_decode(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
                           int B, int H, int dv, Strides2 sq, Strides2 sk, Strides2 sv, Strides2 sy,

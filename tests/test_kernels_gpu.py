@@ -168,6 +168,34 @@ def test_linattn_decode_vs_oracle(ops, io, st, dv):
             kv_ref, ks_ref = kv.cpu().double(), ks.cpu().double()
 
 
+@pytest.mark.parametrize("io,st,B,H,dv", [(torch.bfloat16, torch.float32, 19, 16, 64), (torch.float32, torch.float32, 37, 8, 32),
+                                          (torch.bfloat16, torch.bfloat16, 40, 8, 16), (torch.bfloat16, torch.float32, 20, 16, 112),
+                                          (torch.bfloat16, torch.float32, 75, 4, 64)])
+def test_linattn_decode_many_heads_vs_oracle(ops, io, st, B, H, dv):
+    """Enough (batch, head) blocks for the persistent bulk-copy kernel (at least two per SM): three steps, with
+    the blocks of one CTA reusing its three shared-memory stages; dv = 112 does not fit and takes the direct kernel."""
+    from based_b200 import _capi
+    g = torch.Generator().manual_seed(B + dv)
+    kv0 = (0.02 * torch.randn(B, H, 1, dv, 273, generator=g)).to(st)
+    ks0 = (1.0 + 0.02 * torch.randn(B, H, 1, 1, 273, generator=g)).to(st)
+    kv_ref, ks_ref = kv0.double(), ks0.double()
+    kv, ks = kv0.cuda(), ks0.cuda()
+    tol = 2e-2 if (io == torch.bfloat16 or st == torch.bfloat16) else 1e-4
+    for s in range(3):
+        q = (torch.randn(B, H, 1, 16, generator=g) / 2).to(io)
+        k = (torch.randn(B, H, 1, 16, generator=g) / 2).to(io)
+        v = torch.randn(B, H, 1, dv, generator=g).to(io)
+        y_ref = O.linattn_recurrent_step(kv_ref, ks_ref, q.double(), k.double(), v.double())
+        y = ops.linattn_decode(q.cuda(), k.cuda(), v.cuda(), kv, ks)
+        y_ref = y_ref.transpose(1, 2).reshape(B, 1, H * dv)
+        assert rel_err(y.cpu(), y_ref) < tol, f"step {s}"
+        assert rel_err(kv.cpu(), kv_ref) < tol and rel_err(ks.cpu(), ks_ref) < tol
+        if st == torch.bfloat16:
+            kv_ref, ks_ref = kv.cpu().double(), ks.cpu().double()
+    torch.cuda.synchronize()
+    assert _capi.read_status() == 0
+
+
 def test_linattn_decode_golden(ops):
     """Decode steps the reference itself ran (recurrent_forward), from its prefill state."""
     g = load_golden("linattn_qkv_f32_dv112.npz")
