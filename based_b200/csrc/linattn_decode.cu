@@ -215,6 +215,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t mbar_saddr, uint32_t byt
 // at most one committed bulk store still reads its shared-memory source
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory"); }
 
+// Measured at B=256, H=16, dv=64, fp32 state: staged 0.132 ms against 0.109 ms for the direct kernel, so the
+// direct kernel stays the default until the staged pipeline is faster.
+constexpr bool kPreferStaged = false;
 constexpr int kStagedThreads = 512;  // one CTA per SM: sixteen warps share the in-place update of a block
 constexpr int kStagedWarps = kStagedThreads / 32;
 
@@ -421,7 +424,8 @@ int launch_typed(const void* q, const void* k, const void* v, void* y, void* kv_
   {
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && B * H >= 2 * sms) {
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && B * H >= 2 * sms &&
+        kPreferStaged) {
       const int rc = launch_staged<IO, ST>(q, k, v, y, kv_state, k_state, B, H, dv, sq, sk, sv, sy, eps, stream);
       if (rc != BASED_ERR_IMPL) return rc;
     }
