@@ -35,11 +35,10 @@ const char* based_error_string(int code) {
 }
 
 int based_read_status(unsigned int* out, int reset) {
-  unsigned int a = 0, b = 0, c = 0;
+  unsigned int a = 0, b = 0;
   int rc = read_tc_status(&a, reset);
   if (rc == 0) rc = read_tc_status_swa(&b, reset);
-  if (rc == 0) rc = read_decode_status(&c, reset);
-  if (out) *out = a | b | c;
+  if (out) *out = a | b;
   return rc;
 }
 

@@ -90,7 +90,6 @@ int launch_decode_linear(const void* x, const void* w, const void* bias, void* o
 
 int read_tc_status(unsigned int* out, int reset);      // linear-attention prefill kernel
 int read_tc_status_swa(unsigned int* out, int reset);  // sliding-window prefill kernel
-int read_decode_status(unsigned int* out, int reset);  // staged linear-attention decode kernel
 
 int launch_swa_prefill_simt(const void* q, const void* k, const void* v, void* o, int B, int L, int H, int hd,
                             Strides3 sq, Strides3 sk, Strides3 sv, Strides3 so, int window_left, float scale,

@@ -172,8 +172,7 @@ def test_linattn_decode_vs_oracle(ops, io, st, dv):
                                           (torch.bfloat16, torch.bfloat16, 40, 8, 16), (torch.bfloat16, torch.float32, 20, 16, 112),
                                           (torch.bfloat16, torch.float32, 75, 4, 64)])
 def test_linattn_decode_many_heads_vs_oracle(ops, io, st, B, H, dv):
-    """Enough (batch, head) blocks for the persistent bulk-copy kernel (at least two per SM): three steps, with
-    the blocks of one CTA reusing its three shared-memory stages; dv = 112 does not fit and takes the direct kernel."""
+    """More (batch, head) blocks than SMs x resident CTAs, several head counts and widths, three steps each."""
     from based_b200 import _capi
     g = torch.Generator().manual_seed(B + dv)
     kv0 = (0.02 * torch.randn(B, H, 1, dv, 273, generator=g)).to(st)
