@@ -111,7 +111,7 @@ def mixer_level_case(LinearAttention, TaylorExp, InferenceParams):
 
 
 def config1_samples(LinearAttention, TaylorExp, InferenceParams):
-    """BASELINE config 1 (d_model 1024, 16 heads, feature_dim 16, head_dim 64, B=2, L=1024, fp32, seed 0):
+    """Parity configuration (d_model 1024, 16 heads, feature_dim 16, head_dim 64, B=2, L=1024, fp32, seed 0):
     the inputs are regenerated from the seed by the test; only strided samples of the outputs are stored."""
     torch.manual_seed(0)
     m = LinearAttention(d_model=1024, feature_map=TaylorExp(input_dim=16), feature_dim=16,

@@ -294,7 +294,7 @@ def test_swa_decode_equals_prefill(ops):
 
 # ------------------------------------------------------------------ full-size, size-independent properties
 def test_prefill_full_size_properties(ops):
-    """BASELINE config-3 shape (B=8, H=16, L=8192, dv=64, bf16), too large for the quadratic oracle
+    """Prefill-sweep shape (B=8, H=16, L=8192, dv=64, bf16), too large for the quadratic oracle
     as a whole: (1) sampled (batch, head) slices against the chunked fp64 oracle, (2) linearity in v
     (the normaliser does not depend on v), (3) recurrent == parallel for the last positions,
     (4) tensor-core and CUDA-core kernels agree."""
@@ -332,7 +332,7 @@ def test_prefill_full_size_properties(ops):
 
 
 def test_decode_full_size_properties(ops):
-    """BASELINE config-2 shape (B=256, H=16, fp32 state): sampled units against the oracle after
+    """Decode-microbenchmark shape (B=256, H=16, fp32 state): sampled units against the oracle after
     several in-place steps, and determinism (two runs from the same state are bit-identical)."""
     B, H, dv = 256, 16, 64
     g = torch.Generator(device="cuda").manual_seed(1)

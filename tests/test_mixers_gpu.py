@@ -61,7 +61,7 @@ def test_linear_attention_preallocated_cache_is_filled_in_place():
 
 
 def test_linear_attention_config1_against_reference_samples():
-    """BASELINE config 1 at full size (d_model 1024, 16 heads, B=2, L=1024, fp32, seed 0)."""
+    """The parity configuration at full size (d_model 1024, 16 heads, B=2, L=1024, fp32, seed 0)."""
     from based_b200.generation import InferenceParams
     from based_b200.mixers import LinearAttention, TaylorExp
     g = load_golden("linattn_config1_samples.npz")

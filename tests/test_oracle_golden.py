@@ -81,7 +81,7 @@ def test_linattn_mixer_forward():
 
 
 def test_linattn_config1_samples():
-    """BASELINE config 1 at full size: inputs regenerated from seed 0, outputs compared
+    """The parity configuration at full size: inputs regenerated from seed 0, outputs compared
     with strided samples the reference produced."""
     g = load_golden("linattn_config1_samples.npz")
     torch.manual_seed(0)
