@@ -41,6 +41,7 @@ SIGNATURES = {
     "based_gated_act": (c_int, [c_void_p] * 3 + [c_int64, c_int] + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "based_decode_linear": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_int64] * 2 + [c_int, c_int]
                             + [c_void_p] * 3 + [c_int, c_int, c_void_p]),
+    "based_rotary_qkv_cache": (c_int, [c_void_p] + [c_int] * 4 + [_I64P, c_void_p, c_void_p, c_void_p, _I64P, c_void_p]),
 }
 
 _lib = None

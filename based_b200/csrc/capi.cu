@@ -281,4 +281,14 @@ int based_decode_linear(const void* x, const void* w, const void* bias, void* ou
                               conv_weight, conv_bias, conv_k, conv_w_dtype, static_cast<cudaStream_t>(stream));
 }
 
+int based_rotary_qkv_cache(void* qkv, int B, int L, int H, int hd, const int64_t qkv_strides[4],
+                           const void* rotary_cos, const void* rotary_sin, void* kv_cache,
+                           const int64_t cache_strides[2], void* stream) {
+  if (!qkv || !qkv_strides || !rotary_cos || !rotary_sin || !kv_cache || !cache_strides) return BASED_ERR_NULL;
+  if (B < 0 || L < 0 || H < 0 || hd < 16 || hd > 256) return BASED_ERR_SHAPE;
+  return launch_rotary_qkv_cache(qkv, B, L, H, hd, qkv_strides[0], qkv_strides[1], qkv_strides[2], qkv_strides[3],
+                                 rotary_cos, rotary_sin, kv_cache, cache_strides[0], cache_strides[1],
+                                 static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

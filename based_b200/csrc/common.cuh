@@ -84,6 +84,9 @@ int launch_add_rmsnorm(const void* x, const void* residual, const void* weight, 
 int launch_gated_act(const void* y, const void* gate, void* out, int64_t M, int F, int64_t sy, int64_t sg, int64_t so,
                      int act, int io_dtype, cudaStream_t stream);
 
+int launch_rotary_qkv_cache(void* qkv, int B, int L, int H, int hd, int64_t sb, int64_t sl, int64_t s3, int64_t sh,
+                            const void* rcos, const void* rsin, void* cache, int64_t cb, int64_t cl,
+                            cudaStream_t stream);
 int launch_decode_linear(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, int64_t sx,
                          int64_t so, int epilogue, int act, void* conv_state, const void* conv_weight,
                          const void* conv_bias, int conv_k, int conv_w_dtype, cudaStream_t stream);

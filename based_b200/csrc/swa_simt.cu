@@ -273,7 +273,70 @@ __global__ void rotary_vec_kernel(IO* __restrict__ x, int L, int H, Strides3 sx,
   *reinterpret_cast<uint4*>(px + half) = x1.u;
 }
 
+// Prompt pass of the sliding-window mixer on the packed projection qkv [B, L, 3, H, hd] (bf16): q and k rotated in
+// place (whole head, non-interleaved), and the rotated k and v written to the layer's cache [*, max_seqlen, 2, H, hd]
+// in the same pass.  One thread per 16-byte piece: q and k pieces carry a rotated pair of 8-element groups, v pieces
+// a plain copy.  Pieces per head: hd/16 (q) + hd/16 (k) + hd/8 (v) = hd/4.
+__global__ void __launch_bounds__(256)
+rotary_qkv_cache_kernel(__nv_bfloat16* __restrict__ qkv, int L, int H, int hd, int64_t sb, int64_t sl, int64_t s3,
+                        int64_t sh, const __nv_bfloat16* __restrict__ rcos, const __nv_bfloat16* __restrict__ rsin,
+                        __nv_bfloat16* __restrict__ cache, int64_t cb, int64_t cl, long long total) {
+  using IO = __nv_bfloat16;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int half = hd / 2, gq = half / 8, per_head = 2 * gq + hd / 8;
+  const int piece = (int)(idx % per_head);
+  long long r = idx / per_head;
+  const int h = (int)(r % H); r /= H;
+  const int l = (int)(r % L);
+  const int b = (int)(r / L);
+  IO* base = qkv + b * sb + (int64_t)l * sl + h * sh;
+  IO* crow = cache + b * cb + (int64_t)l * cl + (int64_t)h * hd;  // k part; the v part is H * hd further
+  if (piece >= 2 * gq) {  // v: copy
+    const int c = (piece - 2 * gq) * 8;
+    *reinterpret_cast<uint4*>(crow + (int64_t)H * hd + c) = *reinterpret_cast<const uint4*>(base + 2 * s3 + c);
+    return;
+  }
+  const int part = piece / gq, c = (piece - part * gq) * 8;  // part 0 = q, 1 = k
+  IO* px = base + part * s3 + c;
+  union V { uint4 u; IO e[8]; } x0, x1, cs, sn;
+  x0.u = *reinterpret_cast<const uint4*>(px);
+  x1.u = *reinterpret_cast<const uint4*>(px + half);
+  cs.u = __ldg(reinterpret_cast<const uint4*>(rcos + (size_t)l * half + c));
+  sn.u = __ldg(reinterpret_cast<const uint4*>(rsin + (size_t)l * half + c));
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float a = to_float(x0.e[i]), bb = to_float(x1.e[i]), cc = to_float(cs.e[i]), ss = to_float(sn.e[i]);
+    x0.e[i] = from_float<IO>(a * cc - bb * ss);
+    x1.e[i] = from_float<IO>(a * ss + bb * cc);
+  }
+  *reinterpret_cast<uint4*>(px) = x0.u;
+  *reinterpret_cast<uint4*>(px + half) = x1.u;
+  if (part == 1) {
+    *reinterpret_cast<uint4*>(crow + c) = x0.u;
+    *reinterpret_cast<uint4*>(crow + c + half) = x1.u;
+  }
+}
+
 }  // namespace
+
+int launch_rotary_qkv_cache(void* qkv, int B, int L, int H, int hd, int64_t sb, int64_t sl, int64_t s3, int64_t sh,
+                            const void* rcos, const void* rsin, void* cache, int64_t cb, int64_t cl,
+                            cudaStream_t stream) {
+  if (hd % 16 != 0) return BASED_ERR_SHAPE;
+  const int64_t strides[] = {sb, sl, s3, sh, cb, cl};
+  for (int64_t s : strides)
+    if (s % 8 != 0) return BASED_ERR_ALIGN;
+  if (!aligned16(qkv) || !aligned16(rcos) || !aligned16(rsin) || !aligned16(cache)) return BASED_ERR_ALIGN;
+  const long long total = (long long)B * L * H * (hd / 4);
+  if (total == 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  if (blocks > 2147483647LL) return BASED_ERR_TOO_LARGE;
+  rotary_qkv_cache_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+      static_cast<__nv_bfloat16*>(qkv), L, H, hd, sb, sl, s3, sh, static_cast<const __nv_bfloat16*>(rcos),
+      static_cast<const __nv_bfloat16*>(rsin), static_cast<__nv_bfloat16*>(cache), cb, cl, total);
+  return (int)cudaGetLastError();
+}
 
 int launch_rotary(void* x, int B, int L, int H, Strides3 sx, const void* rcos, const void* rsin, int rotary_dim,
                   const int32_t* offsets, int offset_scalar, int io_dtype, cudaStream_t stream) {

@@ -152,14 +152,24 @@ class SlidingAttention(nn.Module):
         w = self.window[0]
 
         if inference_params is None or inference_params.seqlen_offset == 0:
-            if self.rotary_emb_dim > 0:
-                rmax = inference_params.max_seqlen if inference_params is not None else None
-                qkv = self.rotary_emb(qkv, seqlen_offset=0, max_seqlen=rmax)
+            cache = None
             if inference_params is not None:
                 cache = self._kv_cache(inference_params, qkv)
                 b0 = inference_params.batch_size_offset
                 assert b0 + batch <= cache.shape[0] and seqlen <= cache.shape[1]
-                cache[b0:b0 + batch, :seqlen] = qkv[:, :, 1:].to(cache.dtype)
+            if (cache is not None and self.rotary_emb_dim == self.head_dim and cache.dtype == torch.bfloat16
+                    and self.head_dim % 16 == 0):
+                # rotary on q, k and the cache fill in one pass over the packed projection
+                self.rotary_emb._update_cos_sin_cache(max(inference_params.max_seqlen, seqlen), device=qkv.device,
+                                                      dtype=qkv.dtype)
+                ops.rotary_qkv_cache_(qkv, self.rotary_emb._cos_cached, self.rotary_emb._sin_cached,
+                                      cache[b0:b0 + batch])
+            else:
+                if self.rotary_emb_dim > 0:
+                    rmax = inference_params.max_seqlen if inference_params is not None else None
+                    qkv = self.rotary_emb(qkv, seqlen_offset=0, max_seqlen=rmax)
+                if cache is not None:
+                    cache[b0:b0 + batch, :seqlen] = qkv[:, :, 1:].to(cache.dtype)
             context = ops.swa_prefill(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], w, self.softmax_scale)
         else:
             cache = self._kv_cache(inference_params, qkv)[:batch]

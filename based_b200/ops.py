@@ -447,3 +447,30 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if DECODE_LINEAR_USE["plain"] and _decode_rows(x, weight):
         return decode_linear(x, weight, bias)
     return torch.nn.functional.linear(x, weight, bias)
+
+
+def rotary_qkv_cache_(qkv: torch.Tensor, rotary_cos: torch.Tensor, rotary_sin: torch.Tensor,
+                      kv_cache: torch.Tensor) -> torch.Tensor:
+    """Prompt pass of the sliding-window mixer: whole-head RoPE on q and k of packed ``qkv [B, L, 3, H, hd]`` in
+    place, and rotated k plus v written to ``kv_cache[:B, :L]`` (``[*, max_seqlen, 2, H, hd]``) in the same launch
+    (slide_attention.py:553-556 and :255-281).  bf16 only; returns ``qkv``."""
+    _need_cuda(qkv, rotary_cos, rotary_sin, kv_cache)
+    B, L, three, H, hd = qkv.shape
+    if three != 3 or qkv.dtype != torch.bfloat16 or kv_cache.dtype != torch.bfloat16:
+        raise TypeError("rotary_qkv_cache_ takes a bfloat16 [B, L, 3, H, hd] tensor and a bfloat16 cache")
+    _inner_contig(qkv, "qkv")
+    if rotary_cos.shape[-1] * 2 != hd or rotary_cos.shape[0] < L or rotary_cos.dtype != torch.bfloat16:
+        raise ValueError("rotary tables must be bfloat16 [>= L, hd/2]")
+    if not (rotary_cos.is_contiguous() and rotary_sin.is_contiguous()):
+        raise ValueError("rotary tables must be contiguous")
+    if (kv_cache.shape[0] < B or kv_cache.shape[1] < L or tuple(kv_cache.shape[2:]) != (2, H, hd)
+            or kv_cache.stride()[2:] != (H * hd, hd, 1)):
+        raise ValueError("kv_cache must be [>= B, >= L, 2, H, hd] with the last three dims contiguous")
+    if qkv.numel() == 0:
+        return qkv
+    with torch.cuda.device(qkv.device):
+        code = _capi.lib().based_rotary_qkv_cache(
+            qkv.data_ptr(), B, L, H, hd, _capi.strides(*qkv.stride()[:4]), rotary_cos.data_ptr(), rotary_sin.data_ptr(),
+            kv_cache.data_ptr(), _capi.strides(*kv_cache.stride()[:2]), _stream())
+    _capi.check(code, "based_rotary_qkv_cache")
+    return qkv

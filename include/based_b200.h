@@ -308,6 +308,24 @@ int based_gated_act(const void* y, const void* gate, void* out,
                     int64_t y_row_stride, int64_t gate_row_stride, int64_t out_row_stride,
                     int act, int io_dtype, void* stream);
 
+/*
+ * Prompt pass of the sliding-window mixer, before attention: rotary embedding (non-interleaved, whole
+ * head, positions 0 .. L-1) applied in place to q and k of the packed projection qkv [B, L, 3, H, hd],
+ * and the rotated k and the v written into the layer's KV cache in the same pass.
+ *
+ * Replaces `self.rotary_emb(qkv, ...)` followed by the cache fill `_update_kv_cache(kv, ...)`
+ * (based/models/mixers/slide_attention.py:553-556, :255-281), two passes over k and v in the reference.
+ *
+ *   qkv_strides   (batch, seq, part, head) element strides of qkv, hd contiguous; bf16
+ *   rotary_cos/sin [>= L, hd/2] bf16, contiguous
+ *   kv_cache      points at the first cache row to fill; layout [.., max_seqlen, 2, H, hd] with
+ *                 cache_strides = (batch, seq) element strides and (2, H, hd) contiguous; bf16
+ *   hd a multiple of 16; all strides multiples of 8; pointers 16-byte aligned.
+ */
+int based_rotary_qkv_cache(void* qkv, int B, int L, int H, int hd, const int64_t qkv_strides[4],
+                           const void* rotary_cos, const void* rotary_sin,
+                           void* kv_cache, const int64_t cache_strides[2], void* stream);
+
 /* epilogue selectors of based_decode_linear */
 #define BASED_EPI_PLAIN 0  /* out[M, N]   = x W^T + bias */
 #define BASED_EPI_GATED 1  /* out[M, N/2] = (x W1^T + b1) * act(x W2^T + b2), W = [W1; W2], act as in based_gated_act */

@@ -403,3 +403,22 @@ def test_decode_step_is_cuda_graph_capturable(ops):
     for _ in range(3):
         y_eager = ops.linattn_decode(q, k, v, kv_ref, ks_ref)
     assert torch.equal(y, y_eager) and torch.equal(kv, kv_ref) and torch.equal(ks, ks_ref)
+
+
+@pytest.mark.parametrize("B,L,H,hd", [(2, 37, 4, 64), (1, 130, 2, 112), (3, 1, 2, 16)])
+def test_rotary_qkv_cache_equals_rotary_then_copy(ops, B, L, H, hd):
+    """The fused prompt-pass kernel (RoPE on q, k in place + cache fill) against the separate rotary launches and
+    a copy, bit for bit; the oracle pins the rotary itself."""
+    g = torch.Generator().manual_seed(hd + L)
+    qkv = torch.randn(B, L, 3, H, hd, generator=g).bfloat16()
+    cos, sin = O.rotary_cos_sin(L + 9, hd, dtype=torch.bfloat16)
+    a, b = qkv.clone().cuda(), qkv.clone().cuda()
+    cache = torch.full((B + 1, L + 5, 2, H, hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.rotary_qkv_cache_(a, cos.cuda(), sin.cuda(), cache[1:])
+    ops.rotary_apply_(b[:, :, 0], cos.cuda(), sin.cuda(), 0)
+    ops.rotary_apply_(b[:, :, 1], cos.cuda(), sin.cuda(), 0)
+    assert torch.equal(a, b)
+    assert torch.equal(cache[1:, :L], b[:, :, 1:])
+    assert (cache[0] == 7).all() and (cache[1:, L:] == 7).all()          # nothing else is touched
+    ref_q = O.apply_rotary(qkv[:, :, 0], cos, sin, 0)
+    assert rel_err(a[:, :, 0].cpu().float(), ref_q.float()) < 1e-2
