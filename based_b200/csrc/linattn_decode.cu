@@ -15,7 +15,7 @@
 namespace based {
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 192;  // 6 warps, three CTAs per SM (96 registers): measured 0.1055 ms against 0.1091 ms with 256 x 2
 constexpr int kWarps = kThreads / 32;
 constexpr int kTab = 288;     // table length: 273 + wrap-around + padding, multiple of 4
 constexpr int kVecPerGroup = kExpandedDim;  // 273 vectors of 16 B per row group
@@ -56,7 +56,7 @@ template <> struct VecOps<__nv_bfloat16> {
 };
 
 template <typename IO, typename ST>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 linattn_decode_kernel(const IO* __restrict__ q, const IO* __restrict__ k, const IO* __restrict__ v,
                       IO* __restrict__ y, ST* __restrict__ kv_state, ST* __restrict__ k_state,
                       int H, int dv, Strides2 sq, Strides2 sk, Strides2 sv, Strides2 sy, float eps) {
