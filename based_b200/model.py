@@ -23,6 +23,30 @@ from .mixers import BaseConv, LinearAttention, SlidingAttention, TaylorExp
 from .modules import GatedMlp, RMSNorm
 
 
+def sample_token(logits: torch.Tensor, top_k: int = 1, top_p: float = 0.0, temperature: float = 1.0) -> torch.Tensor:
+    """Next token per row of ``logits [B, V]``: greedy for ``top_k == 1``; otherwise restrict to the ``top_k`` largest
+    logits (all of them for ``top_k <= 0``), divide by ``temperature``, drop the low-probability tail whose
+    cumulative probability is at most ``1 - top_p`` (nucleus sampling; no-op for ``top_p`` outside (0, 1)), and draw
+    from the softmax of what is left.  Same policy as ``sample`` in based/generation.py:38-92."""
+    if top_k == 1:
+        return logits.argmax(dim=-1)
+    if not 0.0 <= top_p <= 1.0:
+        raise ValueError("top_p must be in [0, 1]")
+    if top_k > 0:
+        vals, idx = torch.topk(logits, min(top_k, logits.size(-1)), dim=-1)       # descending
+    else:
+        vals, idx = torch.sort(logits, dim=-1, descending=True)
+    vals = vals.float()
+    if temperature != 1.0:
+        vals = vals / temperature
+    if 0.0 < top_p < 1.0:
+        probs = vals.softmax(dim=-1)
+        tail = probs.flip(-1).cumsum(dim=-1).flip(-1)     # mass of this candidate and everything less likely
+        vals = vals.masked_fill(tail <= 1.0 - top_p, float("-inf"))
+    choice = torch.multinomial(vals.softmax(dim=-1), num_samples=1)
+    return idx.gather(-1, choice).squeeze(-1)
+
+
 @dataclass
 class BasedConfig:
     """The fields of the reference's experiment configs that shape the model
@@ -150,9 +174,11 @@ class BasedLMHeadModel(nn.Module):
         return ops.linear(hidden_states, self.lm_head.weight, self.lm_head.bias)
 
     @torch.inference_mode()
-    def generate(self, input_ids, max_new_tokens: int, cg: bool = False, timings: Optional[dict] = None):
-        """Greedy decoding: one prompt pass, then one token per step (generation.py:93-204).  With ``cg`` the
-        decode step is captured once in a CUDA graph and replayed (:689-739).  Returns ``[B, L + max_new_tokens]``.
+    def generate(self, input_ids, max_new_tokens: int, cg: bool = False, timings: Optional[dict] = None,
+                 top_k: int = 1, top_p: float = 0.0, temperature: float = 1.0):
+        """Decoding: one prompt pass, then one token per step (generation.py:93-204); greedy by default, top-k /
+        nucleus / temperature sampling as :func:`sample_token` otherwise.  With ``cg`` the decode step is
+        captured once in a CUDA graph and replayed (:689-739).  Returns ``[B, L + max_new_tokens]``.
         ``timings``, when given, receives device times in ms: ``prefill_ms``, ``decode_ms`` (all steps)."""
         B, L = input_ids.shape
         dtype = self.lm_head.weight.dtype
@@ -164,7 +190,7 @@ class BasedLMHeadModel(nn.Module):
         out[:, :L] = input_ids
         ev[0].record()
         logits = self.forward(input_ids, inference_params=ip, num_last_tokens=1)
-        token = logits[:, -1, : self.config.vocab_size].argmax(dim=-1, keepdim=True)
+        token = sample_token(logits[:, -1, : self.config.vocab_size], top_k, top_p, temperature).unsqueeze(-1)
         ev[1].record()
         ip.seqlen_offset = L
         if max_new_tokens > 0:
@@ -173,7 +199,7 @@ class BasedLMHeadModel(nn.Module):
 
         def step():
             lg = self.forward(cur, inference_params=ip, num_last_tokens=1)
-            cur.copy_(lg[:, -1, : self.config.vocab_size].argmax(dim=-1, keepdim=True))
+            cur.copy_(sample_token(lg[:, -1, : self.config.vocab_size], top_k, top_p, temperature).unsqueeze(-1))
             ip.lengths_per_sample.add_(1)
 
         graph = None

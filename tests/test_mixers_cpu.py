@@ -100,3 +100,22 @@ def test_model_assembly_keeps_the_reference_parameter_names():
     assert set(cache) == {0, 1, 2} and set(cache[0]) == {"conv"} and len(cache[1]) == 2
     full = BasedConfig.based_360m()
     assert full.padded_vocab_size == 50280 and len(full.alt_mixer_layers) == 5
+
+
+def test_sample_token_policy():
+    """Greedy, top-k support, nucleus support and temperature of the sampling policy (host logic, CPU tensors)."""
+    import torch
+    from based_b200.model import sample_token
+    torch.manual_seed(0)
+    logits = torch.tensor([[2.0, 1.0, 0.5, -1.0, -3.0], [0.0, 3.0, 2.9, -2.0, 1.0]])
+    assert sample_token(logits).tolist() == [0, 1]
+    many = logits.repeat_interleave(400, dim=0)
+    topk = sample_token(many, top_k=2)
+    assert set(topk[:400].tolist()) == {0, 1} and set(topk[400:].tolist()) == {1, 2}
+    # nucleus: row 0 probabilities ~ [0.61, 0.22, 0.14, 0.03, 0.004]; top_p = 0.8 keeps the smallest head whose
+    # mass reaches 0.8 -> tokens 0 and 1; row 1 ~ [0.024, 0.48, 0.43, 0.003, 0.065] -> tokens 1 and 2
+    nuc = sample_token(many, top_k=0, top_p=0.8)
+    assert set(nuc[:400].tolist()) == {0, 1} and set(nuc[400:].tolist()) == {1, 2}
+    # a very low temperature makes sampling greedy; top_p outside (0, 1) filters nothing
+    assert sample_token(many, top_k=5, temperature=1e-3).tolist() == [0] * 400 + [1] * 400
+    assert len(set(sample_token(many, top_k=0, top_p=0.0, temperature=3.0)[:400].tolist())) >= 4

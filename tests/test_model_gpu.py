@@ -86,3 +86,19 @@ def test_generate_cuda_graph_equals_eager():
     with torch.inference_mode():
         first = m(ids)[:, -1, :211].argmax(-1)
     assert torch.equal(eager[:, 40], first)
+
+
+def test_generate_with_sampling():
+    """Sampling decode: reproducible under a seed, tokens inside the vocabulary, and equal to greedy when the
+    temperature is tiny; the CUDA-graph path accepts it too."""
+    m = _small_model(seed=3)
+    ids = torch.randint(0, 211, (3, 20), device="cuda")
+    greedy = m.generate(ids, max_new_tokens=8)
+    torch.manual_seed(5)
+    a = m.generate(ids, max_new_tokens=8, top_k=20, top_p=0.9, temperature=0.8)
+    torch.manual_seed(5)
+    b = m.generate(ids, max_new_tokens=8, top_k=20, top_p=0.9, temperature=0.8)
+    assert torch.equal(a, b) and int(a.max()) < 211 and int(a.min()) >= 0
+    assert torch.equal(m.generate(ids, max_new_tokens=8, top_k=20, temperature=1e-4), greedy)
+    g = m.generate(ids, max_new_tokens=8, cg=True, top_k=20, top_p=0.9, temperature=0.8)
+    assert g.shape == (3, 28) and int(g.max()) < 211 and torch.equal(g[:, :20], ids)
