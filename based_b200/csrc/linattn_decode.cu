@@ -15,8 +15,9 @@
 namespace based {
 namespace {
 
-constexpr int kThreads = 192;  // 6 warps, three CTAs per SM (96 registers): measured 0.1055 ms against 0.1091 ms with 256 x 2
-constexpr int kWarps = kThreads / 32;
+// CTA size: 192 threads (three CTAs per SM, 96 registers) when there are many (batch, head) blocks -- measured
+// 0.1052 ms against 0.1091 ms at B=256, H=16, fp32 state -- and 256 threads (two per SM) when there are few, where
+// one block's latency is what counts (B=16, H=16, bf16 state: 10.6 us against 17.3 us).
 constexpr int kTab = 288;     // table length: 273 + wrap-around + padding, multiple of 4
 constexpr int kVecPerGroup = kExpandedDim;  // 273 vectors of 16 B per row group
 constexpr int kIters = (kVecPerGroup + 31) / 32;  // 9
@@ -55,14 +56,15 @@ template <> struct VecOps<__nv_bfloat16> {
   static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 };
 
-template <typename IO, typename ST>
-__global__ void __launch_bounds__(kThreads, 3)
+template <typename IO, typename ST, int kThreads>
+__global__ void __launch_bounds__(kThreads, kThreads <= 192 ? 3 : 2)
 linattn_decode_kernel(const IO* __restrict__ q, const IO* __restrict__ k, const IO* __restrict__ v,
                       IO* __restrict__ y, ST* __restrict__ kv_state, ST* __restrict__ k_state,
                       int H, int dv, Strides2 sq, Strides2 sk, Strides2 sv, Strides2 sy, float eps) {
   using VO = VecOps<ST>;
   constexpr int VEC = VO::kVec;
   constexpr int RPG = VEC;  // rows per 16-byte-aligned group
+  constexpr int kWarps = kThreads / 32;
 
   // s_t*[s][i] = phi[(i + s) % 273]: four shifted copies so that phi[f0 .. f0+VEC) can be
   // fetched with aligned 128-bit shared loads whatever f0 mod 4 is.
@@ -179,9 +181,17 @@ linattn_decode_kernel(const IO* __restrict__ q, const IO* __restrict__ k, const 
 template <typename IO, typename ST>
 int launch_typed(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state, int B, int H,
                  int dv, Strides2 sq, Strides2 sk, Strides2 sv, Strides2 sy, float eps, cudaStream_t stream) {
-  linattn_decode_kernel<IO, ST><<<B * H, kThreads, 0, stream>>>(
-      static_cast<const IO*>(q), static_cast<const IO*>(k), static_cast<const IO*>(v), static_cast<IO*>(y),
-      static_cast<ST*>(kv_state), static_cast<ST*>(k_state), H, dv, sq, sk, sv, sy, eps);
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if ((long long)B * H >= 6LL * sms) {  // at least two waves of three CTAs per SM
+    linattn_decode_kernel<IO, ST, 192><<<B * H, 192, 0, stream>>>(
+        static_cast<const IO*>(q), static_cast<const IO*>(k), static_cast<const IO*>(v), static_cast<IO*>(y),
+        static_cast<ST*>(kv_state), static_cast<ST*>(k_state), H, dv, sq, sk, sv, sy, eps);
+  } else {
+    linattn_decode_kernel<IO, ST, 256><<<B * H, 256, 0, stream>>>(
+        static_cast<const IO*>(q), static_cast<const IO*>(k), static_cast<const IO*>(v), static_cast<IO*>(y),
+        static_cast<ST*>(kv_state), static_cast<ST*>(k_state), H, dv, sq, sk, sv, sy, eps);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -196,11 +196,21 @@ swa_decode_kernel(const IO* __restrict__ q, const IO* __restrict__ k_new, const 
   sum = warp_sum(sum);
   __syncwarp();
   const float inv = 1.f / sum;
-  // a lane owns two adjacent value columns; four rows per round so that their loads overlap
+  // a lane owns two adjacent value columns; sixteen (then four) rows per round so that their loads overlap
   for (int c = 2 * lane; c < hd; c += 64) {
     const IO* vc = cache_b + (size_t)lo * row + (size_t)(H + h) * hd + c;
     float a0 = 0.f, a1 = 0.f;
     int jj = 0;
+    for (; jj + 16 <= nk; jj += 16) {  // sixteen rows in flight: the loop is latency-bound
+      float2 x[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) x[u] = load2(vc + (size_t)(jj + u) * row);
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        a0 = fmaf(s_p[warp][jj + u], x[u].x, a0);
+        a1 = fmaf(s_p[warp][jj + u], x[u].y, a1);
+      }
+    }
     for (; jj + 4 <= nk; jj += 4) {
       float2 x[4];
 #pragma unroll
