@@ -323,6 +323,8 @@ def main():
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--strong", action="store_true",
+                    help="strong scaling: split the one B=256 batch across the GPUs instead of one batch per GPU")
     ap.add_argument("--no-sweep", action="store_true", help="skip the prefill / SWA sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--quick", action="store_true", help="prefill sweep at L=2048 only")
@@ -347,11 +349,14 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
     K, W, pool = args.steps, args.warmup, 16
+    # weak scaling (default, what the N-GPU launches measure): every rank runs the whole B=256 batch of its own;
+    # --strong: the one B=256 batch is split across the ranks (B / N sequences each)
+    Bd = B_DEC // world if args.strong else B_DEC
 
-    qh, kh, vh, kv0, ks0 = decode_inputs(B_DEC, pool, "cpu", seed=rank)
+    qh, kh, vh, kv0, ks0 = decode_inputs(Bd, pool, "cpu", seed=rank)
     q, k, v = qh.to(dev), kh.to(dev), vh.to(dev)
     kv, ks = kv0.to(dev), ks0.to(dev)
-    y = torch.empty(B_DEC, 1, H * DV, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(Bd, 1, H * DV, dtype=torch.bfloat16, device=dev)
 
     def barrier():
         if world > 1:
@@ -380,11 +385,11 @@ def main():
     # the public op.  The copies run on their own streams, double-buffered, so that step i+1's inputs
     # travel while step i computes (what a serving loop does); the state stays on the device.
     qp, kp, vp = qh.pin_memory(), kh.pin_memory(), vh.pin_memory()
-    yh = [torch.empty(B_DEC, 1, H * DV, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    yh = [torch.empty(Bd, 1, H * DV, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     qd = [torch.empty_like(q[0]) for _ in range(2)]
     kd = [torch.empty_like(k[0]) for _ in range(2)]
     vd = [torch.empty_like(v[0]) for _ in range(2)]
-    yd = [torch.empty(B_DEC, 1, H * DV, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    yd = [torch.empty(Bd, 1, H * DV, dtype=torch.bfloat16, device=dev) for _ in range(2)]
     Ke = min(K, 400)
     main = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
@@ -434,19 +439,20 @@ def main():
 
     if rank == 0:
         launch_ms = ms / K
-        achieved = DEC_BYTES_PER_UNIT * B_DEC * H / (launch_ms * 1e-3) / 1e9
+        achieved = DEC_BYTES_PER_UNIT * Bd * H / (launch_ms * 1e-3) / 1e9
         line = {
-            "metric": "decode_tok_per_s", "value": world * B_DEC * K / (ms * 1e-3), "unit": "tok/s",
+            "metric": "decode_tok_per_s", "value": world * Bd * K / (ms * 1e-3), "unit": "tok/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": launch_ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": "strong" if args.strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "decode microbench: B=256,H=16,d=16,dv=64, fp32 state [B,H,1,64,273], bf16 q/k/v, "
-                                   "1 token/step; per-GPU shard fixed (batch x heads), no collective",
+                                   "1 token/step; " + ("one batch split across the GPUs" if args.strong else "per-GPU shard fixed")
+                                   + " (batch x heads), no collective",
                        "l2": "state (286 MB) larger than L2 (126 MB): no flush needed"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
                          "kernel": "linattn_decode_kernel<bf16,float>",
-                         "algorithmic_bytes_per_launch": DEC_BYTES_PER_UNIT * B_DEC * H},
-            "e2e": {"value": world * B_DEC * Ke / (ms_e2e * 1e-3), "unit": "tok/s",
+                         "algorithmic_bytes_per_launch": DEC_BYTES_PER_UNIT * Bd * H},
+            "e2e": {"value": world * Bd * Ke / (ms_e2e * 1e-3), "unit": "tok/s",
                     "h2d_bytes_per_step": (qp[0].numel() + kp[0].numel() + vp[0].numel()) * 2,
                     "d2h_bytes_per_step": yh[0].numel() * 2, "steps": Ke},
             "gpu_launches": K,
