@@ -55,9 +55,11 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
   const uint32_t sb = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int hd = p.hd, W = p.W, NK = TQ + W;
+  // head index fastest: CTAs that run at the same time then read the SAME token rows of the packed projection
+  // (H x 128 contiguous bytes per row and part) instead of one 128-byte piece out of every row's 6 KB
   int tile = blockIdx.x;
-  const int ti = tile % p.tiles_per_seq; tile /= p.tiles_per_seq;
-  const int h = tile % p.H, b = tile / p.H;
+  const int h = tile % p.H; tile /= p.H;
+  const int ti = tile % p.tiles_per_seq, b = tile / p.tiles_per_seq;
   const int t0 = ti * TQ;          // first query of the tile
   const int k0 = t0 - W;           // position of key column 0 (may be negative)
 
