@@ -1,0 +1,130 @@
+"""The drop-in claim, checked with the reference's own host code: its ``GPTLMHeadModel`` (based/models/gpt.py:737-830)
+is built through its own ``create_mixer_cls`` (gpt.py:64-96) with the ``_target_`` paths pointing at ``based_b200``'s
+mixers, and its own ``GenerationMixin.generate`` / ``decode`` / ``update_graph_cache`` / ``capture_graph``
+(based/generation.py:94-204, :558-578, :614-739) drive the B200 kernels — eager and from a captured CUDA graph.
+
+Three models share one set of weights:
+  ref/ref    reference model, reference mixers (torch LinearAttention + BaseConv, flash-attn SlidingAttention)
+  ref/b200   reference model, based_b200 mixers
+  b200/b200  based_b200.model.BasedLMHeadModel
+Logits are compared with the tolerance of the other model tests (relative error 5e-2 in bf16, the reference's own
+bf16 tolerance being atol 5e-2 / rtol 1e-2, based/tests/test_generation.py:106-115).  The reference modules come from
+``oracle/_ref`` (staged by ``oracle/make_ref.py``); without it the tests skip."""
+import pytest
+import torch
+
+from conftest import rel_err
+from oracle import ref_shims
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not ref_shims.available(), reason="no staged reference under oracle/_ref")]
+
+KW = dict(n_embd=128, n_layer=4, n_head=2, n_inner=256, vocab_size=211, alt_mixer_layers=[1], alt_mixer_2_layers=[2],
+          l_max=256, window_size=64)
+TOL = 5e-2
+
+
+@pytest.fixture(scope="module")
+def models():
+    from based_b200.model import BasedConfig, BasedLMHeadModel
+    ns = ref_shims.reference()
+    torch.manual_seed(0)
+    ref_ref = ns.GPTLMHeadModel(ref_shims.based_config(ns, **KW, targets="reference"))
+    # the special initialiser leaves the outputs tiny; scale the weights up so that every layer matters
+    with torch.no_grad():
+        for name, prm in ref_ref.named_parameters():
+            if prm.dim() > 1 and "embeddings" not in name:
+                prm.mul_(3.0)
+    sd = ref_ref.state_dict()
+    ref_b200 = ns.GPTLMHeadModel(ref_shims.based_config(ns, **KW, targets="b200"))
+    assert ref_b200.load_state_dict(sd, strict=True) is not None
+    cfg = BasedConfig(n_embd=KW["n_embd"], n_layer=KW["n_layer"], n_head=KW["n_head"], n_inner=KW["n_inner"],
+                      vocab_size=KW["vocab_size"], alt_mixer_layers=KW["alt_mixer_layers"],
+                      alt_mixer_2_layers=KW["alt_mixer_2_layers"], window_size=KW["window_size"], l_max=KW["l_max"])
+    own = BasedLMHeadModel(cfg)
+    missing, unexpected = own.load_state_dict(sd, strict=False)
+    assert unexpected == [] and set(missing) <= {"lm_head.weight"}
+    own.tie_weights()
+    out = {}
+    for name, m in (("ref_ref", ref_ref), ("ref_b200", ref_b200), ("own", own)):
+        m = m.to(device="cuda", dtype=torch.bfloat16).eval()
+        if name != "own":
+            m.tie_weights()
+        out[name] = m
+    out["ns"] = ns
+    return out
+
+
+def test_reference_model_instantiates_b200_mixers_through_create_mixer_cls(models):
+    """gpt.py:87 gates ``sliding_window_additions`` on the substring ``slide`` in the ``_target_`` path: with the
+    module path of the class it is applied, so the mixer gets rotary over the whole head and no biases."""
+    from based_b200 import mixers
+    layers = models["ref_b200"].transformer.layers
+    assert isinstance(layers[0].mixer, mixers.BaseConv) and isinstance(layers[3].mixer, mixers.BaseConv)
+    assert isinstance(layers[1].mixer, mixers.LinearAttention)
+    slide = layers[2].mixer
+    assert isinstance(slide, mixers.SlidingAttention)
+    assert slide.rotary_emb_dim == slide.head_dim == 64 and slide.window == (32, 0)
+    assert slide.Wqkv.bias is None and slide.out_proj.bias is None and slide.softmax_scale == 64 ** -0.5
+    ref_keys = list(models["ref_ref"].state_dict().keys())
+    assert list(models["ref_b200"].state_dict().keys()) == ref_keys
+
+
+def test_full_pass_logits_agree(models):
+    ids = torch.randint(0, KW["vocab_size"], (3, 100), device="cuda", generator=torch.Generator("cuda").manual_seed(1))
+    with torch.inference_mode():
+        a = models["ref_ref"](ids).logits.float()
+        b = models["ref_b200"](ids).logits.float()
+        c = models["own"](ids).float()
+    assert rel_err(b, a) < TOL          # B200 mixers inside the reference model == the reference's mixers
+    assert rel_err(c, b) < TOL          # the compact model == the reference model around the same kernels
+
+
+def _teacher_forced(model, ids, teacher, cg):
+    out = model.generate(ids, max_length=teacher.shape[1], top_k=1, cg=cg, teacher_outputs=teacher,
+                         return_dict_in_generate=True, output_scores=True)
+    assert torch.equal(out.sequences, teacher)
+    return torch.stack(out.scores, 1).float()   # [B, steps, vocab]
+
+
+@pytest.mark.parametrize("cg", [False, True])
+def test_reference_generate_drives_b200_mixers(models, cg):
+    """Prompt pass + single-token steps through the reference's decode loop, teacher-forced so that the three models see
+    the same tokens: per-step logits of ref/b200 match ref/ref; with ``cg`` the steps are graph replays."""
+    g = torch.Generator("cuda").manual_seed(2)
+    B, L, N = 3, 70, 24
+    teacher = torch.randint(0, KW["vocab_size"], (B, L + N), device="cuda", generator=g)
+    ids = teacher[:, :L].contiguous()
+    s_ref = _teacher_forced(models["ref_ref"], ids, teacher, cg=False)
+    s_new = _teacher_forced(models["ref_b200"], ids, teacher, cg=cg)
+    assert s_new.shape == s_ref.shape == (B, N, s_ref.shape[-1])
+    for t in range(N):
+        assert rel_err(s_new[:, t], s_ref[:, t]) < TOL, f"step {t}"
+    from based_b200 import _capi
+    assert _capi.read_status() == 0
+
+
+def test_reference_generate_graph_replay_equals_eager(models):
+    """Free-running greedy generation through the reference loop: the captured-graph run reproduces the eager run
+    token for token, and the compact model's own loop produces the same tokens up to the first near-tie."""
+    g = torch.Generator("cuda").manual_seed(3)
+    B, L, N = 2, 50, 20
+    ids = torch.randint(0, KW["vocab_size"], (B, L), device="cuda", generator=g)
+    m = models["ref_b200"]
+    eager = m.generate(ids, max_length=L + N, top_k=1, cg=False, return_dict_in_generate=True, output_scores=True)
+    graphed = m.generate(ids, max_length=L + N, top_k=1, cg=True, return_dict_in_generate=True, output_scores=True)
+    assert eager.sequences.shape == (B, L + N)
+    assert torch.equal(eager.sequences, graphed.sequences)
+    for a, b in zip(eager.scores, graphed.scores):
+        assert rel_err(b.float(), a.float()) < 1e-6 or torch.equal(a, b)
+    own = models["own"].generate(ids, max_new_tokens=N, cg=True)
+    scores = torch.stack(eager.scores, 1).float()[..., :KW["vocab_size"]]
+    for bi in range(B):
+        diff = (own[bi] != eager.sequences[bi]).nonzero()
+        if diff.numel() == 0:
+            continue
+        t = int(diff[0]) - L                      # first differing generated position
+        top2 = scores[bi, t].topk(2).values
+        # the two hosts differ only in the norm / activation kernels around the mixers: a different token is
+        # acceptable only where the reference logits themselves are tied within the tolerance
+        assert (top2[0] - top2[1]) < TOL * scores[bi, t].abs().max(), f"sequence {bi} diverges at step {t}"
