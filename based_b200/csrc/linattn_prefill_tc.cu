@@ -33,11 +33,6 @@ __device__ unsigned int g_tc_status = 0;  // ORed with a code when a bounded wai
 // written earlier in the same call, so nothing here has to start at zero.
 static __device__ __align__(256) unsigned char g_static_scratch[BASED_STATIC_SCRATCH_BYTES];
 
-#ifdef BASED_TC_TRACE
-// Debug build only: per-role cycle counters of CTA 0 (cycles spent in each barrier wait, total
-// cycles), read back with based_tc_trace_read().
-__device__ unsigned long long g_tc_trace[5][32];
-#endif
 
 namespace {
 
@@ -97,34 +92,9 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   auto bar = [&](int i) { return sb + lay.bar + 8 * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + lay.bar + 8 * B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + lay.bar + 8 * B_COUNT + 4);
-#ifdef BASED_TC_TRACE
-  // phase slots are only ever indexed by compile-time constants, so they stay in registers;
-  // the time spent in barrier waits is a single sum (slot 0)
-  unsigned long long tr_wait[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) tr_wait[i] = 0;
-  unsigned long long tr_wsum = 0;
-  long long tr_t = 0;
-  long long tr_t2 = 0;
-#define TR_BEGIN() tr_t = clock64()
-#define TR_END(slot) tr_wait[slot] += clock64() - tr_t
-#define TR2_BEGIN() tr_t2 = clock64()
-#define TR2_END(slot) tr_wait[slot] += clock64() - tr_t2
-  const long long tr_start = clock64();
-  auto wait = [&](int i, uint32_t parity, unsigned int code) {
-    const long long t0 = clock64();
-    mbar_wait_bounded(bar(i), parity & 1u, abort_flag, p.status, code);
-    tr_wsum += clock64() - t0;
-  };
-#else
-#define TR_BEGIN()
-#define TR_END(slot)
-#define TR2_BEGIN()
-#define TR2_END(slot)
   auto wait = [&](int i, uint32_t parity, unsigned int code) {
     mbar_wait_bounded(bar(i), parity & 1u, abort_flag, p.status, code);
   };
-#endif
 
   // ------------------------------------------------------------------ set-up
   if (tid == 0) {
@@ -205,27 +175,9 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   } else if (warp == W_MMA) {
     // ================================================================ MMA issue: one thread runs the whole loop
     if (lane == 0) {
-#ifdef BASED_TC_TRACE
-      auto mwait = [&](int i, uint32_t parity, unsigned int code) {
-        const long long t0 = clock64();
-        mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
-        const unsigned long long dt = clock64() - t0;
-        tr_wsum += dt;
-        switch (code & 15u) {  // constant slot numbers keep the counters in registers
-          case 1: tr_wait[1] += dt; break;   // P_READY
-          case 2: tr_wait[2] += dt; break;   // O_FREE
-          case 3: tr_wait[3] += dt; break;   // FULL (next chunk)
-          case 4: tr_wait[4] += dt; break;   // PQ_READY
-          case 5: tr_wait[5] += dt; break;   // STB_READY
-          case 6: tr_wait[6] += dt; break;   // PK_READY
-          default: break;
-        }
-      };
-#else
       auto mwait = [&](int i, uint32_t parity, unsigned int code) {
         mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
       };
-#endif
       const int NS = lay.nstage, NPK = lay.npk;
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_o_pv = make_idesc_bf16(128, NV, 0, 1);   // A = P (TMEM), B = V' MN-major
@@ -270,20 +222,16 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         mwait(B_P_READY, c, 0x201u);
         if (c > 0) mwait(B_O_FREE, c - 1, 0x202u);
         fence_after_sync();
-        TR_BEGIN();
 #pragma unroll
         for (int j = 0; j < C / 16; ++j)
           mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
-        TR_END(26);
         // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
         if (c + 1 < nchunks) {
           mwait(B_FULL + st1, st1_par, 0x203u);
           fence_after_sync();
-          TR_BEGIN();
           const uint32_t so = st1 * stage_units;
           mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
           mma_commit(bar(B_S_DONE));
-          TR_END(27);
         }
         // O(c) += phi'(Q_c) State(c-1) and State^T += V'(c)^T phi'(K_c), issued alternately: the two
         // accumulation chains are independent, so one fills the other's latency gaps.  The drain that
@@ -293,7 +241,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         else if (has_init) mwait(B_INIT, 0, 0x207u);  // state^T and its bf16 copy were preloaded
         mwait(B_PK_READY, c, 0x206u);
         fence_after_sync();
-        TR_BEGIN();
         {
           const uint64_t d_pk_c = d_pk + pkb * (40960 >> 4);
 #pragma unroll
@@ -308,20 +255,11 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         mma_commit(bar(B_ST_DONE));
         mma_commit(bar(B_EMPTY + st));
         mma_commit(bar(B_PK_FREE + pkb));
-        TR_END(28);
         st = st1;
         if (++st1 == NS) { st1 = 0; st1_par ^= 1u; }
         if (++pkb == NPK) pkb = 0;
       }
       }
-#ifdef BASED_TC_TRACE
-      if (bh == 0) {
-        tr_wait[0] = tr_wsum;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) g_tc_trace[2][i] = tr_wait[i];
-        g_tc_trace[2][31] = clock64() - tr_start;
-      }
-#endif
     }
   } else if (warp < 4) {
     // ================================================================ expansion warps: phi'(Q) -> TMEM, phi'(K) -> smem
@@ -337,7 +275,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       if (mode != MODE_SEG_STATE) {
       if (c > 0) wait(B_O_DONE, c - 1, 0x301u);  // the previous phi'(Q) has been consumed
       fence_after_sync();
-      TR_BEGIN();
       {
         uint32_t hold[4];
         expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
@@ -350,12 +287,9 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
           }
         });
       }
-      TR_END(17);
-      TR_BEGIN();
       tmem_st_wait();
       fence_before_sync();
       __syncwarp();
-      TR_END(18);
       if (lane == 0) mbar_arrive(bar(B_PQ_READY));
       }
       {
@@ -371,17 +305,13 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       const int pkb = c % lay.npk;
       if (c >= lay.npk) wait(B_PK_FREE + pkb, c / lay.npk - 1, 0x302u);
       uint8_t* dst = smem + lay.phik + pkb * 40960 + t * 16;
-      TR_BEGIN();
       expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
         constexpr int g = decltype(G)::value;
         if constexpr (g == 0) w0 &= one;
         *reinterpret_cast<uint4*>(dst + g * 2048) = make_uint4(w0, w1, w2, w3);
       });
-      TR_END(19);
-      TR_BEGIN();
       fence_proxy_async();
       __syncwarp();
-      TR_END(20);
       if (lane == 0) mbar_arrive(bar(B_PK_READY));
     }
   } else if (warp >= W_OUT && warp < W_MMA) {
@@ -401,7 +331,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       // ---- epilogue: y = O[:, :dv] / (O[:, dv] + eps), 32 columns per round trip ----
       wait(B_O_DONE, c, 0x401u);
       fence_after_sync();
-      TR_BEGIN();
       {
         uint32_t dreg;
         tmem_ld1(tlane + TM_O + dv, dreg);
@@ -415,11 +344,9 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
 #pragma unroll 1
         for (int i0 = 0; i0 < n16; i0 += 2) {
           uint32_t r0[16], r1[16];
-          TR2_BEGIN();
           tmem_ld16(tlane + TM_O + 16 * i0, r0);
           if (i0 + 1 < n16) tmem_ld16(tlane + TM_O + 16 * (i0 + 1), r1);
           tmem_ld_wait();
-          TR2_END(24);
           if (i0 == 0) inv = 1.0f / (__uint_as_float(dreg) + p.eps);
           uint4 lo, hi;
           cvt16(r0, inv, lo, hi);
@@ -461,7 +388,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         }
         __syncwarp();  // the tile is rewritten by other lanes in the next chunk
       }
-      TR_END(22);
     }
   } else {
     // ================================================================ polynomial / state-drain warps
@@ -471,7 +397,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
     auto make_p = [&](int c) {
       wait(B_S_DONE, c, 0x400u);
       fence_after_sync();
-      TR_BEGIN();
       constexpr uint32_t k1 = 0x3F803F80u, kq = 0x3E803E80u, k32 = 0x3D003D00u;  // (1,1) (1/4,1/4) (1/32,1/32)
 #pragma unroll 1
       for (int piece = 0; piece <= qd; ++piece) {
@@ -498,7 +423,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       tmem_st_wait();
       fence_before_sync();
       __syncwarp();
-      TR_END(21);
       if (lane == 0) mbar_arrive(bar(B_P_READY));
     };
     auto cvt16 = [&](const uint32_t (&r)[16], float sc, uint4& lo, uint4& hi) {
@@ -568,15 +492,12 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       wait(B_ST_DONE, c, 0x402u);
       fence_after_sync();
       if (!last) {
-        TR_BEGIN();
 #pragma unroll 1
         for (int i = 0; i < (qd * 32 < NV ? 5 : 0); ++i) {  // 32 feature columns per round trip; warp-uniform skip of a quadrant without state rows
           uint32_t r0[16], r1[16];
-          TR2_BEGIN();
           tmem_ld16(tlane + TM_ST + 32 * i, r0);
           tmem_ld16(tlane + TM_ST + 32 * i + 16, r1);
           tmem_ld_wait();
-          TR2_END(25);
           uint4 a0, a1, b0, b1;
           cvt16(r0, 1.0f, a0, a1);
           cvt16(r1, 1.0f, b0, b1);
@@ -591,7 +512,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
         fence_proxy_async();
         fence_before_sync();
         __syncwarp();
-        TR_END(23);
         if (lane == 0) mbar_arrive(bar(B_STB_READY));
       } else if (write_state) {
         stage_state();
@@ -600,15 +520,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
     }
   }
 
-#ifdef BASED_TC_TRACE
-  if (bh == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == W_LOAD || warp == W_OUT)) {
-    const int role = warp == 0 ? 0 : warp == 4 ? 1 : warp == W_OUT ? 4 : 3;
-    tr_wait[0] = tr_wsum;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) g_tc_trace[role][i] = tr_wait[i];
-    g_tc_trace[role][31] = clock64() - tr_start;
-  }
-#endif
   // ------------------------------------------------------------------ final state, reference layout
   fence_before_sync();
   __syncthreads();
@@ -662,11 +573,6 @@ __global__ void __launch_bounds__(256) segment_scan_kernel(float* __restrict__ x
 
 }  // namespace
 
-#ifdef BASED_TC_TRACE
-extern "C" int based_tc_trace_read(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 5 * 32);
-}
-#endif
 
 int read_tc_status(unsigned int* out, int reset) {
   unsigned int v = 0;

@@ -26,13 +26,6 @@ namespace based {
 
 __device__ unsigned int g_tc_status_swa = 0;
 
-#ifdef BASED_TC_TRACE
-// Debug build only: cycles per phase summed over all CTAs (thread 0), and the CTA count.
-__device__ unsigned long long g_swa_trace[16];
-#define SWA_TR(slot) do { if (tid == 0) { const long long now_ = clock64(); atomicAdd(&g_swa_trace[slot], (unsigned long long)(now_ - tr_t)); tr_t = now_; } } while (0)
-#else
-#define SWA_TR(slot)
-#endif
 
 namespace {
 
@@ -72,9 +65,6 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM_BAR + 36);
 
-#ifdef BASED_TC_TRACE
-  long long tr_t = clock64();
-#endif
   if (tid == 0) {
     mbar_init(bar_qk, 1);
     mbar_init(bar_v, 1);
@@ -93,12 +83,10 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
     }
     for (int a = 0; a < natom; ++a) tma::load_4d(sb + SM_V + a * kv_atom, &p.mv, bar_v, 64 * a, k0, h, b);
   }
-  SWA_TR(0);  // set-up + load issue
   // TMEM is allocated only now: when more CTAs are resident than TMEM can serve, the extra
   // CTA blocks here with its loads already in flight.
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
-  SWA_TR(10);  // TMEM allocation
   fence_before_sync();
   __syncthreads();  // barriers initialised, TMEM base published
   fence_after_sync();
@@ -110,7 +98,6 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
   if (tid == 0) {
     mbar_wait_bounded<false>(bar_qk, 0, abort_flag, p.status, 64u);
     fence_after_sync();
-    SWA_TR(1);  // load wait
     const uint32_t idesc = make_idesc_bf16(128, NK, 0, 0);
     int first = 1;
     for (int a = 0; a < natom; ++a) {
@@ -136,7 +123,6 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
   const int first_col = -k0 - c_lo;  // columns below this (relative) are before the sequence start
   mbar_wait_bounded(bar_s, 0, abort_flag, p.status, 16u);
   fence_after_sync();
-  SWA_TR(2);  // S MMA
   // Visibility of the 32 columns of piece pc for this row as a bit mask (bit i = column i),
   // so the inner loops are branch-free selects.
   auto piece_mask = [&](int pc) -> uint32_t {
@@ -149,15 +135,12 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
   float m = -INFINITY;
   for (int pc = 0; pc < npieces; ++pc) {
     uint32_t r[32];
-    SWA_TR(3);
     tmem_ld32(tlane + TM_S + c_lo + 32 * pc, r);
     tmem_ld_wait();
-    SWA_TR(9);  // TMEM load round trips of the max pass
     const uint32_t mask = piece_mask(pc);
 #pragma unroll
     for (int i = 0; i < 32; ++i) m = fmaxf(m, (mask & (1u << i)) ? __uint_as_float(r[i]) : -INFINITY);
   }
-  SWA_TR(3);  // max pass
   const float msc = m * p.scale_log2e;
   float sum = 0.f;
   for (int pc = 0; pc < npieces; ++pc) {
@@ -182,7 +165,6 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
     }
     tmem_st16(tlane + TM_S + ((c_lo + 32 * pc) >> 1), pk);
   }
-  SWA_TR(4);  // exp pass
   // zero the P columns of keys this warp's rows cannot see
   {
     uint32_t z[16];
@@ -195,7 +177,6 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
   tmem_st_wait();
   fence_before_sync();
   __syncthreads();
-  SWA_TR(5);  // zero fill + barrier
 
   // ---- O = P V ----
   if (tid == 0) {
@@ -213,7 +194,6 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
   // ---- epilogue ----
   mbar_wait_bounded(bar_o, 0, abort_flag, p.status, 32u);
   fence_after_sync();
-  SWA_TR(6);  // PV MMA
   {
     // Each thread writes its normalised row into the output tile (Q's space, free since S was
     // computed) in the 128-byte-swizzled layout; one thread then hands the tile to the TMA unit,
@@ -238,7 +218,6 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
       *reinterpret_cast<uint4*>(atom + tma::sw128_offset(t, 2 * (i & 3) + 1)) = hi;
     }
     fence_proxy_async();  // generic-proxy writes -> visible to the TMA unit
-    SWA_TR(7);  // O -> staging
     __syncthreads();
     if (tid == 0) {
       for (int a = 0; a < natom; ++a) tma::store_4d(&p.mo, sb + SM_Q + a * q_atom, 64 * a, t0, h, b);
@@ -246,12 +225,8 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
       bulk_wait_read_all();  // shared memory must stay intact until the TMA unit has read it
     }
   }
-  SWA_TR(8);  // copy-out
   fence_before_sync();
   __syncthreads();
-#ifdef BASED_TC_TRACE
-  if (tid == 0) atomicAdd(&g_swa_trace[15], 1ull);
-#endif
   if (warp == 0) {
     fence_after_sync();
     tmem_dealloc(tmem, p.tmem_cols);
@@ -260,16 +235,6 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
 
 }  // namespace
 
-#ifdef BASED_TC_TRACE
-extern "C" int based_swa_trace_read(unsigned long long* out, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, g_swa_trace, sizeof(unsigned long long) * 16);
-  if (e == cudaSuccess && reset) {
-    unsigned long long z[16] = {0};
-    e = cudaMemcpyToSymbol(g_swa_trace, z, sizeof(z));
-  }
-  return (int)e;
-}
-#endif
 
 int read_tc_status_swa(unsigned int* out, int reset) {
   unsigned int v = 0;

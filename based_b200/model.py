@@ -228,6 +228,7 @@ class BasedLMHeadModel(nn.Module):
         ev[2].record()
         if timings is not None:
             torch.cuda.synchronize()
+            ops.check_status()   # the device is idle here: a tensor-core kernel that gave up on a wait shows now
             timings["prefill_ms"] = ev[0].elapsed_time(ev[1])
             timings["decode_ms"] = ev[1].elapsed_time(ev[2])
         return out

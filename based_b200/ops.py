@@ -24,9 +24,29 @@ def _dt(t: torch.dtype) -> int:
 
 
 def _need_cuda(*ts):
+    """Every op starts here: CUDA tensors only, and no autograd.  The kernels write into fresh buffers through
+    raw pointers and register no backward, so under grad mode the result would silently be cut off from the
+    graph (the projections before a mixer would get no gradient and nothing would say so)."""
     for t in ts:
         if t is not None and not t.is_cuda:
             raise RuntimeError("based_b200 ops run on CUDA tensors only (there is no CPU path)")
+    if torch.is_grad_enabled():
+        for t in ts:
+            if t is not None and t.requires_grad:
+                raise RuntimeError(
+                    "based_b200 kernels are inference-only (no backward): call them under torch.no_grad() or "
+                    "torch.inference_mode(), or detach the inputs")
+
+
+def check_status(reset: bool = True) -> int:
+    """Read the tensor-core kernels' status word and raise if a bounded in-kernel wait ever expired (the results
+    of that launch are then meaningless).  It synchronises the device, so call it where the caller synchronises
+    anyway: after a generation loop, at the end of a timed region."""
+    code = _capi.read_status(reset)
+    if code != 0:
+        raise _capi.BasedLibraryError(f"a bounded wait expired inside a tensor-core kernel (status 0x{code:x}); "
+                                      "the outputs of that launch are not valid")
+    return code
 
 
 def _inner_contig(t, name):

@@ -4,7 +4,7 @@ golden vectors the reference produced.  Tolerances: relative error (max |a-b| / 
 import pytest
 import torch
 
-from conftest import load_golden, rel_err
+from conftest import load_golden, rel_err, state_block_errs, worst_window_err
 from oracle import based_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -51,6 +51,10 @@ def test_linattn_prefill_vs_oracle(ops, impl, dtype, L, dv):
     assert rel_err(y.cpu(), y_ref) < tol
     assert rel_err(kv.cpu(), kv_ref) < tol
     assert rel_err(ks.cpu(), ks_ref) < tol
+    # late rows and the small second-order blocks of the state, each against its own scale
+    assert worst_window_err(y.cpu(), y_ref, 2, length=32) < tol
+    for name, e in {**state_block_errs(kv.cpu(), kv_ref), **{"k_" + n: e for n, e in state_block_errs(ks.cpu(), ks_ref).items()}}.items():
+        assert e < tol, (name, e)
 
 
 @pytest.mark.parametrize("B,H,L,dv,nseg", [(1, 2, 1024, 64, 2), (1, 2, 1024 + 77, 64, 3), (2, 1, 4096, 64, 8),
@@ -70,6 +74,9 @@ def test_linattn_prefill_sequence_split_vs_oracle(ops, B, H, L, dv, nseg):
     assert rel_err(y.cpu(), y_ref) < tol
     assert rel_err(kv.cpu(), kv_ref) < tol
     assert rel_err(ks.cpu(), ks_ref) < tol
+    assert worst_window_err(y.cpu(), y_ref, 2) < tol
+    for name, e in state_block_errs(kv.cpu(), kv_ref).items():
+        assert e < tol, (name, e)
     # the split only changes the order of fp32 additions in the state
     assert rel_err(y.float(), y1.float()) < 1e-2
     assert rel_err(kv, kv1) < 1e-5
@@ -315,6 +322,9 @@ def test_prefill_full_size_properties(ops):
         yr, kvr, ksr = O.linattn_chunked(q[b:b + 1, h:h + 1].cpu().double(), k[b:b + 1, h:h + 1].cpu().double(),
                                          v1[b:b + 1, h:h + 1].cpu().double(), chunk=512)
         assert rel_err(y1[b:b + 1, h:h + 1].cpu(), yr) < 2e-2
+        assert worst_window_err(y1[b:b + 1, h:h + 1].cpu(), yr, 2) < 2e-2
+        for name, e in state_block_errs(kv1[b:b + 1, h:h + 1].cpu(), kvr).items():
+            assert e < 2e-2, (b, h, name, e)
         assert rel_err(kv1[b:b + 1, h:h + 1].cpu(), kvr) < 2e-2
         assert rel_err(ks1[b:b + 1, h:h + 1].cpu(), ksr) < 2e-2
     # (2) linearity in v (bf16 rounding of the inputs/outputs bounds the slack)

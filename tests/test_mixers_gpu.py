@@ -141,3 +141,32 @@ def test_linear_attention_fused_qkv_projection_is_the_same_mixer():
         b.proj_v.weight.mul_(2.0)
         a.proj_v.weight.mul_(2.0)
         assert torch.equal(a(x), b(x))
+
+
+def test_mixers_refuse_autograd_instead_of_dropping_gradients():
+    """The kernels have no backward.  Under grad mode a call must raise — not return an output cut off from the graph,
+    which would leave the projections in front of the kernel without gradients and say nothing."""
+    from based_b200 import ops
+    from based_b200.mixers import BaseConv, LinearAttention, SlidingAttention, TaylorExp
+    from based_b200.modules import GatedMlp, RMSNorm
+    torch.manual_seed(0)
+    x = torch.randn(2, 24, 64, device="cuda", dtype=torch.bfloat16)
+    mods = [LinearAttention(64, feature_map=TaylorExp(16), num_heads=2, head_dim=32),
+            SlidingAttention(64, 2, qkv_proj_bias=False, out_proj_bias=False, window_size=64),
+            BaseConv(64, l_max=64, kernel_size=3), RMSNorm(64), GatedMlp(64, activation=torch.nn.functional.silu)]
+    for m in mods:
+        m = m.to("cuda", torch.bfloat16)
+        with pytest.raises(RuntimeError, match="inference-only"):
+            m(x.clone().requires_grad_())
+        with pytest.raises(RuntimeError, match="inference-only"):
+            m(x)                                    # the parameters require grad
+        with torch.inference_mode():
+            assert m(x).shape == x.shape
+        with torch.no_grad():
+            assert m(x).shape == x.shape
+    q = torch.randn(1, 2, 8, 16, device="cuda").requires_grad_()
+    v = torch.randn(1, 2, 8, 32, device="cuda")
+    with pytest.raises(RuntimeError, match="inference-only"):
+        ops.linattn_prefill(q, q, v)
+    y, _, _ = ops.linattn_prefill(q.detach(), q.detach(), v)
+    assert y.shape == (1, 2, 8, 32)
