@@ -5,15 +5,20 @@ the decode microbench workload — bf16 q/k/v, fp32 state [B=256, H=16, 1, 64, 2
 per sequence per step.  One "step" is one pass of the decode kernel over the whole batch.
 Per-GPU work is fixed as GPUs are added (batch x heads shards, no collective): weak scaling.
 
-The same line carries: ``roofline`` (HBM fraction of the decode kernel), ``e2e`` (the same
-step through the public API with host buffers: H2D of q/k/v and D2H of y inside the timed
-region), ``cpu_baseline`` (the CPU oracle's restatement of the reference's recurrent_forward
-on the host cores), ``prefill`` / ``swa`` (the prefill sweep: tok/s and roofline fractions),
-``clocks`` sampled during the timed region.
+The same line carries: ``roofline`` (HBM fraction of the decode kernel), ``repeats`` (the timed region
+run again many times: median / min / max and, with several GPUs, per-rank times), ``e2e`` (the same
+step through the public API with host buffers: H2D of q/k/v and D2H of y inside the timed region),
+``prefill`` / ``swa`` (the prefill sweep: tok/s and roofline fractions, each rank its own copy),
+``cpu_baseline`` plus ``prefill_cpu`` / ``swa_cpu`` (the reference's own PyTorch code on the host cores,
+one GPU only), ``generation_*`` (whole-model prompt pass and CUDA-graph decode), with several GPUs
+``strong`` (the one batch split across the ranks) and ``tp`` (head-sharded mixers with the all-reduce after
+the output projection), ``clocks`` sampled during the timed region and ``status`` (the kernels' bounded-wait
+status word, 0 = no wait ever expired).
 
-``--impl reference`` times the CPU restatement of the reference's PyTorch code for the same
-step on the host cores (the reference is pure Python/PyTorch for this path and cannot travel
-to the GPU box; the oracle is pinned against it by golden vectors).
+``--impl reference`` times the reference's own ``recurrent_forward`` (its unmodified Python module staged under
+``oracle/_ref``; the CPU restatement of it when nothing is staged) on the host cores at the same B=256 workload,
+and, when a GPU is visible, adds ``torch_on_gpu``: the same reference PyTorch code run on the GPU, so that a
+GPU-against-GPU figure stands next to the CPU one.
 """
 import argparse
 import json
@@ -36,6 +41,18 @@ PREFILL_FLOP_PER_TOKEN_HEAD = 4 * D_EXP * (DV + 1)
 PREFILL_BYTES_PER_TOKEN_HEAD = 2 * (16 + 16 + DV + DV)
 SWA_BYTES_PER_TOKEN_HEAD = 4 * 64 * 2
 SWA_FLOP_PER_TOKEN_HEAD = 4 * 65 * 64
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the decode kernel at B=256, H=16 from an ncu capture
+# (291.5 MB read + 233.0 MB written; the tail of the writes is still in L2 when the kernel ends)
+DECODE_DRAM_TRAFFIC_PER_LAUNCH = 524.5e6
+WORKLOAD = ("decode microbench: B=256,H=16,d=16,dv=64, fp32 state [B,H,1,64,273], bf16 q/k/v, "
+            "1 token/step")
+
+
+def workload_config(strong):
+    """The `config` object of the JSON line; the same for both arms (they run the same workload)."""
+    return {"workload": WORKLOAD,
+            "sharding": ("one batch split across the GPUs" if strong else "per-GPU shard fixed") + " (batch x heads), no collective",
+            "l2": "state (286 MB) larger than L2 (126 MB): no flush needed"}
 
 
 def load_peaks():
@@ -102,18 +119,115 @@ def decode_inputs(B, pool, device, seed):
     return q, k, v, kv, ks
 
 
-def cpu_decode_baseline(B, steps, warmup, seed=0):
-    """The oracle's recurrent step (restating linear_attention.py:139, :230-251) on the host cores."""
-    from oracle import based_oracle as O
+def _reference_modules():
+    """The reference's own LinearAttention / TaylorExp (staged copy), or None when nothing is staged."""
+    try:
+        from oracle import ref_shims
+        if ref_shims.available():
+            return ref_shims.reference(model=False)
+    except Exception as exc:  # an import problem on this machine: fall back to the restatement, and say so
+        print(f"[bench] staged reference not importable: {exc!r}", file=sys.stderr)
+    return None
+
+
+def _reference_mixer(ns, device="cpu"):
+    m = ns.LinearAttention(d_model=H * DV, feature_map=ns.TaylorExp(input_dim=D_FEAT), feature_dim=D_FEAT,
+                           num_heads=H, head_dim=DV)
+    m.out_proj = torch.nn.Identity()
+    return m.to(device)
+
+
+def reference_decode(B, steps, warmup, device="cpu", seed=0):
+    """tok/s of the reference's decode step (TaylorExp on q and k, then recurrent_forward,
+    linear_attention.py:139, :230-251; out_proj = identity) at batch B on `device`.  Uses the staged reference
+    module when present (kind "reference"), else the CPU restatement (kind "port")."""
     q, k, v, kv, ks = decode_inputs(B, 4, "cpu", seed)
-    q, k, v = q.unsqueeze(3), k.unsqueeze(3), v.unsqueeze(3)   # [pool, B, H, 1, .]
-    for i in range(warmup):
-        O.linattn_recurrent_step(kv, ks, q[i % 4], k[i % 4], v[i % 4])
-    t0 = time.perf_counter()
-    for i in range(steps):
-        O.linattn_recurrent_step(kv, ks, q[i % 4], k[i % 4], v[i % 4])
-    dt = time.perf_counter() - t0
-    return B * steps / dt, dt
+    q, k, v = q.unsqueeze(3).to(device), k.unsqueeze(3).to(device), v.unsqueeze(3).to(device)   # [pool, B, H, 1, .]
+    kv, ks = kv.to(device), ks.to(device)
+    ns = _reference_modules()
+    if ns is not None:
+        m = _reference_mixer(ns, device)
+        x = torch.zeros(B, 1, H * DV, device=device)
+
+        def step(i):
+            return m.recurrent_forward(x, kv, ks, m.feature_map(q[i % 4]), m.feature_map(k[i % 4]), v[i % 4])
+        kind = "reference"
+    else:
+        from oracle import based_oracle as O
+
+        def step(i):
+            return O.linattn_recurrent_step(kv, ks, q[i % 4], k[i % 4], v[i % 4])
+        kind = "port"
+    sync = torch.cuda.synchronize if str(device).startswith("cuda") else (lambda: None)
+    with torch.no_grad():
+        for i in range(warmup):
+            step(i)
+        sync()
+        t0 = time.perf_counter()
+        for i in range(steps):
+            step(i)
+        sync()
+        dt = time.perf_counter() - t0
+    return B * steps / dt, dt, kind
+
+
+def reference_prefill_cpu():
+    """The reference's quadratic parallel_forward (linear_attention.py:171-183, :220-222) on the host cores:
+    the parity configuration in full through LinearAttention.forward (d_model 1024, 16 heads, B=2, L=1024, fp32), and
+    the prefill sweep's shapes on ONE (batch, head) slice each (the quadratic form needs B*H*L*L elements: 34 GB at
+    L=8192 for the whole batch), scaled by B*H = 128 and labelled extrapolated."""
+    ns = _reference_modules()
+    if ns is None:
+        return None
+    out = {"kind": "reference", "cores": torch.get_num_threads()}
+    with torch.no_grad():
+        torch.manual_seed(0)
+        m = ns.LinearAttention(d_model=1024, feature_map=ns.TaylorExp(input_dim=16), feature_dim=16, num_heads=16,
+                               head_dim=64)
+        x = torch.randn(2, 1024, 1024)
+        m(x)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            m(x)
+        dt = (time.perf_counter() - t0) / 3
+        out["parity_config"] = {"shape": "B=2,L=1024,d_model=1024,H=16,fp32, whole mixer with projections",
+                                "ms": dt * 1e3, "tok_per_s": 2 * 1024 / dt}
+        mq = _reference_mixer(ns)
+        mq.is_inference = True
+        sweep = []
+        for L in (2048, 8192):
+            g = torch.Generator().manual_seed(L)
+            q = torch.randn(1, 1, L, 16, generator=g) / 4
+            k = torch.randn(1, 1, L, 16, generator=g) / 4
+            v = torch.randn(1, 1, L, DV, generator=g) / 4
+            xx = torch.zeros(1, L, DV)
+            mq.num_heads = 1
+            t0 = time.perf_counter()
+            mq.parallel_forward(xx, q, k, v)
+            dt = time.perf_counter() - t0
+            sweep.append({"L": L, "slice_ms": dt * 1e3, "sample": "one (batch, head) slice of 128, fp32",
+                          "tok_per_s_extrapolated": 8 * L / (dt * 8 * H)})
+        out["sweep"] = sweep
+        out["note"] = ("L=32768 is not run: one slice of the quadratic form needs 2 x 4.3 GB for A_qk alone; by the "
+                       "measured L^2 growth it would be 16 x the L=8192 slice time")
+    return out
+
+
+def swa_restatement_cpu():
+    """The reference has no CPU sliding-window attention (slide_attention.py:317-319: flash-attn only), so this
+    times the CPU RESTATEMENT of its semantics on one (batch, head) slice of the sweep's shapes, scaled by B*H."""
+    from oracle import based_oracle as O
+    out = {"kind": "port", "cores": torch.get_num_threads(), "note": "CPU restatement of the reference's flash-attn "
+           "call semantics, not reference code", "sweep": []}
+    for L in (2048, 8192):
+        g = torch.Generator().manual_seed(L)
+        qkv = torch.randn(1, L, 3, 1, 64, generator=g) / 4
+        t0 = time.perf_counter()
+        O.swa_prefill(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], 64)
+        dt = time.perf_counter() - t0
+        out["sweep"].append({"L": L, "slice_ms": dt * 1e3, "sample": "one (batch, head) slice of 128, fp32",
+                             "tok_per_s_extrapolated": 8 * L / (dt * 8 * H)})
+    return out
 
 
 def use_all_host_threads():
@@ -123,25 +237,66 @@ def use_all_host_threads():
     return n
 
 
+def reference_on_gpu(steps):
+    """The reference's own PyTorch code run on the GPU (what a user of the reference gets on this machine without
+    this library): decode step at B=256 and the quadratic prefill at the sweep's shapes that fit."""
+    ns = _reference_modules()
+    if ns is None or not torch.cuda.is_available():
+        return None
+    out = {}
+    tput, dt, kind = reference_decode(B_DEC, max(steps, 10), 3, device="cuda")
+    out["decode"] = {"tok_per_s": tput, "ms_per_step": 1e3 * dt / max(steps, 10), "kind": kind,
+                     "what": "TaylorExp x2 + recurrent_forward as torch ops on cuda, B=256, fp32 state, bf16 q/k/v"}
+    m = _reference_mixer(ns, "cuda").bfloat16()
+    m.is_inference = True
+    pre = []
+    with torch.no_grad():
+        for L in (2048, 8192):
+            g = torch.Generator(device="cuda").manual_seed(L)
+            q = (torch.randn(8, H, L, 16, device="cuda", generator=g) / 4).bfloat16()
+            k = (torch.randn(8, H, L, 16, device="cuda", generator=g) / 4).bfloat16()
+            v = (torch.randn(8, H, L, DV, device="cuda", generator=g) / 4).bfloat16()
+            xx = torch.zeros(8, L, H * DV, device="cuda", dtype=torch.bfloat16)
+            try:
+                m.parallel_forward(xx, q, k, v)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for _ in range(3):
+                    m.parallel_forward(xx, q, k, v)
+                torch.cuda.synchronize()
+                dt = (time.perf_counter() - t0) / 3
+                pre.append({"L": L, "ms": dt * 1e3, "tok_per_s": 8 * L / dt})
+            except torch.cuda.OutOfMemoryError:
+                pre.append({"L": L, "ms": None, "note": "out of memory (quadratic form)"})
+            torch.cuda.empty_cache()
+    pre.append({"L": 32768, "ms": None, "note": "not run: A_qk alone is 275 GB in bf16"})
+    out["prefill_quadratic"] = pre
+    return out
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
     use_all_host_threads()
-    Bs = 32
-    tput, dt = cpu_decode_baseline(Bs, args.steps, args.warmup)
+    tput, dt, kind = reference_decode(B_DEC, args.steps, args.warmup)
     cores = torch.get_num_threads()
-    sample = (f"each step = one recurrent step on B={Bs} of the 256 sequences (H=16, fp32 state, bf16 q/k/v), "
-              f"{args.steps} steps, CPU restatement of recurrent_forward")
+    what = ("the reference's own LinearAttention.recurrent_forward + TaylorExp (unmodified module, staged copy)"
+            if kind == "reference" else "CPU restatement of recurrent_forward (no staged reference on this machine)")
+    sample = (f"each step = one full recurrent step of the workload (B=256, H=16, fp32 state, bf16 q/k/v), "
+              f"{args.steps} steps after {args.warmup} warm-up steps; {what}")
     line = {
         "impl": "reference", "metric": "decode_tok_per_s", "value": tput, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "decode microbench: B=256,H=16,d=16,dv=64, fp32 state [B,H,1,64,273], bf16 q/k/v, "
-                               "1 token/step"},
-        "cpu_baseline": {"value": tput, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": workload_config(False),
+        "cpu_baseline": {"value": tput, "unit": "tok/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": tput, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "host_cpus": os.cpu_count(),
     }
+    try:
+        line["torch_on_gpu"] = reference_on_gpu(args.steps)
+    except Exception as exc:  # the CPU figure above is the arm's result; this is an extra
+        line["torch_on_gpu"] = {"error": repr(exc)}
     print(json.dumps(line), flush=True)
 
 
@@ -183,41 +338,54 @@ def time_graph(fn, iters, replays=3):
     return e0.elapsed_time(e1) / (iters * replays)  # ms
 
 
-def prefill_sweep(ops, peaks, lengths):
-    """Prefill sweep: B=8, H=16, d=16, dv=64, bf16, q/k/v ~ N(0,1)/4; linear attention and window-64 SWA."""
+def time_flushed(fn, flush, iters, warmup=3):
+    """Device time per call of `fn` with L2 flushed before every call: the events sit between the flush and the
+    kernel (flush -> event -> kernel -> event), and the per-call times are summed, so the flush itself is never in
+    the measured interval.  The flush is long enough (256 MB of writes) that the host has queued the kernel and
+    both events well before the first event is reached."""
+    for _ in range(warmup):
+        flush.zero_()
+        fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for e0, e1 in ev:
+        flush.zero_()
+        e0.record()
+        fn()
+        e1.record()
+    torch.cuda.synchronize()
+    ts = sorted(e0.elapsed_time(e1) for e0, e1 in ev)
+    return sum(ts) / len(ts), ts[0], ts[-1]  # ms: mean, min, max
+
+
+def prefill_sweep(ops, peaks, lengths, dev):
+    """Prefill sweep: B=8, H=16, d=16, dv=64, bf16, q/k/v ~ N(0,1)/4; linear attention and window-64 SWA.  With
+    several GPUs every rank runs the whole sweep on its own copy (weak scaling); times are the max over ranks."""
+    from based_b200.sharding import max_over_ranks
     out_lin, out_swa = [], []
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     for L in lengths:
-        g = torch.Generator(device="cuda").manual_seed(L)
-        q = (torch.randn(8, H, L, 16, device="cuda", generator=g) / 4).bfloat16()
-        k = (torch.randn(8, H, L, 16, device="cuda", generator=g) / 4).bfloat16()
-        v = (torch.randn(8, H, L, DV, device="cuda", generator=g) / 4).bfloat16()
-        y = torch.empty(8, L, H, DV, dtype=torch.bfloat16, device="cuda").permute(0, 2, 1, 3)
-        kv = torch.empty(8, H, 1, DV, D_EXP, device="cuda")
-        ks = torch.empty(8, H, 1, 1, D_EXP, device="cuda")
-
-        def lin():
-            flush.zero_()
-            ops.linattn_prefill(q, k, v, out=y, kv_state=kv, k_state=ks)
-
-        def fl():
-            flush.zero_()
-
-        iters = 5 if L >= 32768 else 10
-        t = time_kernel(lin, iters) - time_kernel(fl, iters)
+        g = torch.Generator(device=dev).manual_seed(L)
+        q = (torch.randn(8, H, L, 16, device=dev, generator=g) / 4).bfloat16()
+        k = (torch.randn(8, H, L, 16, device=dev, generator=g) / 4).bfloat16()
+        v = (torch.randn(8, H, L, DV, device=dev, generator=g) / 4).bfloat16()
+        y = torch.empty(8, L, H, DV, dtype=torch.bfloat16, device=dev).permute(0, 2, 1, 3)
+        kv = torch.empty(8, H, 1, DV, D_EXP, device=dev)
+        ks = torch.empty(8, H, 1, 1, D_EXP, device=dev)
+        iters = 10 if L >= 32768 else 20
+        t, tmin, tmax = time_flushed(lambda: ops.linattn_prefill(q, k, v, out=y, kv_state=kv, k_state=ks), flush, iters)
+        t, tmin, tmax = max_over_ranks([t, tmin, tmax], dev)
         units = 8 * H * L
-        out_lin.append({"L": L, "ms": t, "tok_per_s": 8 * L / (t * 1e-3),
+        out_lin.append({"L": L, "ms": t, "ms_min": tmin, "ms_max": tmax, "tok_per_s": world * 8 * L / (t * 1e-3),
                         "tensor_frac": units * PREFILL_FLOP_PER_TOKEN_HEAD / (t * 1e-3) / (peaks["bf16_tflops"] * 1e12),
                         "hbm_frac": units * PREFILL_BYTES_PER_TOKEN_HEAD / (t * 1e-3) / (peaks["hbm_gbs"] * 1e9)})
-        qkv = (torch.randn(8, L, 3, H, 64, device="cuda", generator=g) / 4).bfloat16()
-        o = torch.empty(8, L, H, 64, dtype=torch.bfloat16, device="cuda")
-
-        def swa():
-            flush.zero_()
-            ops.swa_prefill(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], 64, out=o)
-
-        t = time_kernel(swa, iters) - time_kernel(fl, iters)
-        out_swa.append({"L": L, "ms": t, "tok_per_s": 8 * L / (t * 1e-3),
+        qkv = (torch.randn(8, L, 3, H, 64, device=dev, generator=g) / 4).bfloat16()
+        o = torch.empty(8, L, H, 64, dtype=torch.bfloat16, device=dev)
+        t, tmin, tmax = time_flushed(lambda: ops.swa_prefill(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], 64, out=o), flush,
+                                     iters)
+        t, tmin, tmax = max_over_ranks([t, tmin, tmax], dev)
+        out_swa.append({"L": L, "ms": t, "ms_min": tmin, "ms_max": tmax, "tok_per_s": world * 8 * L / (t * 1e-3),
                         "hbm_frac": units * SWA_BYTES_PER_TOKEN_HEAD / (t * 1e-3) / (peaks["hbm_gbs"] * 1e9),
                         "tensor_frac": units * SWA_FLOP_PER_TOKEN_HEAD / (t * 1e-3) / (peaks["bf16_tflops"] * 1e12)})
         del q, k, v, y, qkv, o
@@ -294,9 +462,13 @@ def generation_bench(B=16, L=2048, new_tokens=512, size="360m"):
     out = model.generate(ids, max_new_tokens=new_tokens, cg=True, timings=t)
     assert out.shape == (B, L + new_tokens)
     steps = new_tokens - 1  # the first new token comes from the prompt pass
-    res = {"model": f"based-{size} (random init)", "params": nparam, "B": B, "prompt": L, "new_tokens": new_tokens,
-           "prefill_ms": t["prefill_ms"], "prefill_tok_per_s": B * L / (t["prefill_ms"] * 1e-3),
-           "decode_ms_per_step": t["decode_ms"] / steps, "decode_tok_per_s": B * steps / (t["decode_ms"] * 1e-3),
+    from based_b200.sharding import max_over_ranks
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    pre_ms, dec_ms = max_over_ranks([t["prefill_ms"], t["decode_ms"]], ids.device)   # slowest rank
+    res = {"model": f"based-{size} (random init)", "params": nparam, "B_per_gpu": B, "B_total": world * B, "prompt": L,
+           "new_tokens": new_tokens, "sharding": "batch-sharded replicas, no communication",
+           "prefill_ms": pre_ms, "prefill_tok_per_s": world * B * L / (pre_ms * 1e-3),
+           "decode_ms_per_step": dec_ms / steps, "decode_tok_per_s": world * B * steps / (dec_ms * 1e-3),
            "decode": f"CUDA graph replay of one step ({cfg.n_layer} blocks + lm_head + argmax)"}
     del model
     torch.cuda.empty_cache()
@@ -317,6 +489,75 @@ def small_batch_prefill(ops, L):
             "tok_per_s": L / (ts * 1e-3), "l2": "inputs (3 MB) stay in L2 between iterations"}
 
 
+def tp_bench(dev, world):
+    """The tensor-parallel variant of the 8-GPU generation configuration: the 1.4B model's LinearAttention and
+    SlidingAttention mixers (d_model 1792, 16 heads, head_dim 112) head-sharded over the ranks — q/k/v projections
+    column-parallel, state / KV cache local, out_proj row-parallel, ONE all-reduce of [B, L, d_model] at the end
+    (modelled on RowParallelLinear.forward, based/ops/fused_dense.py:239-246).  Activations are replicated, so every
+    rank sees the whole batch of 64.  Times are CUDA-event device times, max over ranks; `allreduce_ms` is the same
+    collective on a tensor of the output's size timed on its own, `allreduce_share` its part of the mixer's time."""
+    import torch.distributed as dist
+    from based_b200.generation import InferenceParams
+    from based_b200.mixers import LinearAttention, SlidingAttention, TaylorExp
+    from based_b200.sharding import max_over_ranks
+    Dm, Hh, B, L = 1792, 16, 64, 4096
+    if Hh % world != 0:
+        return None
+    torch.manual_seed(0)
+    kw = {"device": dev, "dtype": torch.bfloat16, "process_group": dist.group.WORLD}
+    mixers = {
+        "linear_attention": LinearAttention(Dm, feature_map=TaylorExp(16), num_heads=Hh, layer_idx=0, fuse_qkv=True, **kw),
+        "sliding_attention": SlidingAttention(Dm, Hh, qkv_proj_bias=False, out_proj_bias=False, rotary_emb_dim=Dm // Hh,
+                                              window_size=128, layer_idx=1, **kw),
+    }
+    x = torch.randn(B, L, Dm, device=dev, dtype=torch.bfloat16)
+    x1 = torch.randn(B, 1, Dm, device=dev, dtype=torch.bfloat16)
+
+    def timed(fn, iters):
+        for _ in range(2):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return max_over_ranks([e0.elapsed_time(e1) / iters], dev)[0]
+
+    out = {"config": f"d_model={Dm}, heads={Hh} ({Hh // world} per rank), head_dim={Dm // Hh}, B={B}, prompt={L}, bf16, "
+                     "NCCL all-reduce after out_proj"}
+    buf_p = torch.empty(B, L, Dm, device=dev, dtype=torch.bfloat16)
+    buf_d = torch.empty(B, 1, Dm, device=dev, dtype=torch.bfloat16)
+    ar_p = timed(lambda: dist.all_reduce(buf_p), 5)
+    ar_d = timed(lambda: dist.all_reduce(buf_d), 50)
+    out["allreduce_prompt_ms"], out["allreduce_prompt_bytes"] = ar_p, buf_p.numel() * 2
+    out["allreduce_decode_ms"], out["allreduce_decode_bytes"] = ar_d, buf_d.numel() * 2
+    with torch.inference_mode():
+        for name, m in mixers.items():
+            m.eval()
+            ip = InferenceParams(max_seqlen=L + 64, max_batch_size=B)
+            ip.key_value_memory_dict[m.layer_idx] = m.allocate_inference_cache(B, L + 64, dtype=torch.bfloat16)
+            ip.lengths_per_sample = torch.full((B,), L, dtype=torch.int32, device=dev)
+
+            def prompt():
+                ip.seqlen_offset = 0
+                m(x, inference_params=ip)
+
+            def step():
+                ip.seqlen_offset = L
+                m(x1, inference_params=ip)
+
+            tp_ms = timed(prompt, 5)
+            td_ms = timed(step, 50)
+            out[name] = {"prompt_ms": tp_ms, "prompt_tok_per_s": B * L / (tp_ms * 1e-3),
+                         "prompt_allreduce_share": ar_p / tp_ms,
+                         "decode_step_ms": td_ms, "decode_tok_per_s": B / (td_ms * 1e-3),
+                         "decode_allreduce_share": ar_d / td_ms, "decode_timing": "eager launches, device time"}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -325,10 +566,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--strong", action="store_true",
                     help="strong scaling: split the one B=256 batch across the GPUs instead of one batch per GPU")
-    ap.add_argument("--no-sweep", action="store_true", help="skip the prefill / SWA sweep")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--quick", action="store_true", help="prefill sweep at L=2048 only")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the prefill / SWA sweep and the model runs")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
+    ap.add_argument("--quick", action="store_true", help="prefill sweep at L=2048 only, no model runs")
     ap.add_argument("--sweep-L", type=int, nargs="*", default=None, help="sequence lengths of the prefill sweep")
+    ap.add_argument("--regions", type=int, default=25, help="how many times the K-step region is repeated for the "
+                    "median / min / max record (the first one is the headline)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -341,6 +584,7 @@ def main():
 
     import torch.distributed as dist
     from based_b200 import build_library, ops
+    from based_b200.sharding import max_over_ranks
     build_library()
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -349,36 +593,55 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
     K, W, pool = args.steps, args.warmup, 16
-    # weak scaling (default, what the N-GPU launches measure): every rank runs the whole B=256 batch of its own;
-    # --strong: the one B=256 batch is split across the ranks (B / N sequences each)
-    Bd = B_DEC // world if args.strong else B_DEC
-
-    qh, kh, vh, kv0, ks0 = decode_inputs(Bd, pool, "cpu", seed=rank)
-    q, k, v = qh.to(dev), kh.to(dev), vh.to(dev)
-    kv, ks = kv0.to(dev), ks0.to(dev)
-    y = torch.empty(Bd, 1, H * DV, dtype=torch.bfloat16, device=dev)
+    PREROLL = 200   # untimed steps before the warm-up: brings clocks and caches to their loaded state
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---------------- device-resident timed region ----------------
-    for i in range(W):
-        ops.linattn_decode(q[i % pool], k[i % pool], v[i % pool], kv, ks, out=y)
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    barrier()
-    if sampler:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(K):
-        ops.linattn_decode(q[i % pool], k[i % pool], v[i % pool], kv, ks, out=y)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if sampler else None
-    assert torch.isfinite(y.float()).all()
+    def decode_region(Bd, seed, regions):
+        """W warm-up steps, then `regions` timed regions of exactly K steps each (the first one bracketed by a barrier
+        and a synchronize on both sides).  Returns the per-region times in ms and the clock record of the first."""
+        qh, kh, vh, kv0, ks0 = decode_inputs(Bd, pool, "cpu", seed=seed)
+        q, k, v = qh.to(dev), kh.to(dev), vh.to(dev)
+        kv, ks = kv0.to(dev), ks0.to(dev)
+        y = torch.empty(Bd, 1, H * DV, dtype=torch.bfloat16, device=dev)
+
+        def steps(n):
+            for i in range(n):
+                ops.linattn_decode(q[i % pool], k[i % pool], v[i % pool], kv, ks, out=y)
+
+        steps(PREROLL)
+        steps(W)
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        barrier()
+        if sampler:
+            sampler.start()
+        times = []
+        for r in range(regions):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            steps(K)
+            e1.record()
+            barrier()
+            times.append(e0.elapsed_time(e1))
+            if r == 0 and sampler:
+                clocks = sampler.stop()
+        assert torch.isfinite(y.float()).all()
+        return times, (clocks if rank == 0 else None), (qh, kh, vh, q, k, v, kv, ks)
+
+    # ---------------- device-resident timed region (weak scaling: every rank its own B=256 batch) ----------------
+    Bd = B_DEC // world if args.strong else B_DEC
+    times, clocks, (qh, kh, vh, q, k, v, kv, ks) = decode_region(Bd, rank, max(1, args.regions))
+    ms = times[0]
+    srt = sorted(times)
+    rep_local = [srt[len(srt) // 2] / K, srt[0] / K, srt[-1] / K]
+    if world > 1:
+        allr = [None] * world
+        dist.all_gather_object(allr, rep_local)
+    else:
+        allr = [rep_local]
 
     # ---------------- end to end: host buffers, H2D + kernel + D2H per step ----------------
     # Every step copies its q/k/v from pinned host memory and returns y to pinned host memory through
@@ -391,7 +654,7 @@ def main():
     vd = [torch.empty_like(v[0]) for _ in range(2)]
     yd = [torch.empty(Bd, 1, H * DV, dtype=torch.bfloat16, device=dev) for _ in range(2)]
     Ke = min(K, 400)
-    main = torch.cuda.current_stream()
+    main_s = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_k = [torch.cuda.Event() for _ in range(2)]
@@ -408,23 +671,23 @@ def main():
 
     def e2e_loop(n):
         for b in range(2):
-            ev_k[b].record(main); ev_out[b].record(s_out)
+            ev_k[b].record(main_s); ev_out[b].record(s_out)
         upload(0)
         for i in range(n):
             b = i & 1
             if i + 1 < n:
                 upload(i + 1)
-            main.wait_event(ev_in[b])
-            main.wait_event(ev_out[b])        # y buffer b has been copied out
+            main_s.wait_event(ev_in[b])
+            main_s.wait_event(ev_out[b])        # y buffer b has been copied out
             ops.linattn_decode(qd[b], kd[b], vd[b], kv, ks, out=yd[b])
-            ev_k[b].record(main)
+            ev_k[b].record(main_s)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_k[b])
                 yh[b].copy_(yd[b], non_blocking=True)
                 ev_out[b].record(s_out)
-        main.wait_stream(s_out)
+        main_s.wait_stream(s_out)
 
-    e2e_loop(4)
+    e2e_loop(max(4, W))
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
@@ -433,54 +696,78 @@ def main():
     barrier()
     ms_e2e = f0.elapsed_time(f1)
     assert torch.isfinite(yh[0].float()).all() and torch.isfinite(yh[1].float()).all()
-
-    from based_b200.sharding import max_over_ranks
     ms, ms_e2e = max_over_ranks([ms, ms_e2e], dev)
+    h2d = (qp[0].numel() + kp[0].numel() + vp[0].numel()) * 2
+    d2h = yh[0].numel() * 2
+    del qp, kp, vp, q, k, v, kv, ks
 
+    line = None
     if rank == 0:
         launch_ms = ms / K
         achieved = DEC_BYTES_PER_UNIT * Bd * H / (launch_ms * 1e-3) / 1e9
+        med = max(a[0] for a in allr)
         line = {
             "metric": "decode_tok_per_s", "value": world * Bd * K / (ms * 1e-3), "unit": "tok/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": launch_ms, "higher_is_better": True,
             "scaling": "strong" if args.strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "decode microbench: B=256,H=16,d=16,dv=64, fp32 state [B,H,1,64,273], bf16 q/k/v, "
-                                   "1 token/step; " + ("one batch split across the GPUs" if args.strong else "per-GPU shard fixed")
-                                   + " (batch x heads), no collective",
-                       "l2": "state (286 MB) larger than L2 (126 MB): no flush needed"},
+            "config": workload_config(args.strong), "preroll_steps": PREROLL,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                         "kernel": "linattn_decode_kernel<bf16,float>",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": DECODE_DRAM_TRAFFIC_PER_LAUNCH,
+                         "peak_source": peaks["source"], "kernel": "linattn_decode_kernel<bf16,float>",
                          "algorithmic_bytes_per_launch": DEC_BYTES_PER_UNIT * Bd * H},
+            "repeats": {"regions": len(times), "steps_per_region": K, "what": "the same K-step region run again; "
+                        "ms per step, slowest rank's median, and every rank's (median, min, max)",
+                        "ms_per_step_median": med, "frac_at_median": DEC_BYTES_PER_UNIT * Bd * H / (med * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                        "per_rank_ms_per_step": allr},
             "e2e": {"value": world * Bd * Ke / (ms_e2e * 1e-3), "unit": "tok/s",
-                    "h2d_bytes_per_step": (qp[0].numel() + kp[0].numel() + vp[0].numel()) * 2,
-                    "d2h_bytes_per_step": yh[0].numel() * 2, "steps": Ke},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ke},
             "gpu_launches": K,
             "clocks": clocks,
         }
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu
-        # capture summarised in profiles/linattn_decode_B256_H16.md (291.5 MB + 233.0 MB)
-        line["roofline"]["traffic"] = 524.5e6
-        if world == 1 and not args.no_sweep:
-            lengths = args.sweep_L if args.sweep_L else ([2048] if args.quick else [2048, 8192, 32768])
-            lin, swa = prefill_sweep(ops, peaks, lengths)
-            line["prefill"] = lin
-            line["swa"] = swa
-            line["prefill_small_batch"] = small_batch_prefill(ops, max(lengths))
-            line["gated_conv"] = gated_conv_bench(ops, peaks)
-            line["norm_act"] = norm_act_bench(ops, peaks)
-            if not args.quick:
-                line["generation_360m"] = generation_bench()
-                # the per-GPU share of the 8-GPU generation config: 8 of 64 sequences, prompt 4096, 1024 new tokens
-                line["generation_1b"] = generation_bench(B=8, L=4096, new_tokens=1024, size="1b")
+
+    # ---------------- extra records (every rank takes part; rank 0 keeps the results) ----------------
+    extras = {}
+    if not args.no_sweep:
+        lengths = args.sweep_L if args.sweep_L else ([2048] if args.quick else [2048, 8192, 32768])
+        lin, swa = prefill_sweep(ops, peaks, lengths, dev)
+        extras["prefill"], extras["swa"] = lin, swa
+        if world == 1:
+            extras["prefill_small_batch"] = small_batch_prefill(ops, max(lengths))
+            extras["gated_conv"] = gated_conv_bench(ops, peaks)
+            extras["norm_act"] = norm_act_bench(ops, peaks)
+        if world > 1 and not args.strong:
+            # strong scaling: the ONE B=256 batch split across the ranks
+            st, _, _ = decode_region(B_DEC // world, 100 + rank, 5)
+            st_ms = max_over_ranks([sorted(st)[len(st) // 2]], dev)[0]
+            extras["strong"] = {"B_per_gpu": B_DEC // world, "ms_per_step": st_ms / K,
+                                "tok_per_s": B_DEC * K / (st_ms * 1e-3), "what": "median of 5 regions, slowest rank"}
+        if not args.quick:
+            if world == 1:
+                extras["generation_360m"] = generation_bench()
+            # 8 sequences per GPU, prompt 4096, 1024 new tokens: with 8 GPUs this is the 64-sequence generation config
+            extras["generation_1b"] = generation_bench(B=8, L=4096, new_tokens=1024, size="1b")
+            if world > 1:
+                extras["tp"] = tp_bench(dev, world)
+    torch.cuda.synchronize()
+    status = ops.check_status()   # raises if any tensor-core kernel gave up on a bounded wait
+
+    if rank == 0:
+        line.update(extras)
+        line["status"] = status
         if world == 1 and not args.no_cpu:
             use_all_host_threads()
-            tput, dt = cpu_decode_baseline(B_DEC, 20, 2)
-            line["cpu_baseline"] = {"value": tput, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
-                                    "sample": "20 full-batch recurrent steps (B=256,H=16) of the CPU restatement of "
-                                              "recurrent_forward", "host_cpus": os.cpu_count()}
+            tput, dt, kind = reference_decode(B_DEC, 20, 2)
+            line["cpu_baseline"] = {"value": tput, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": kind,
+                                    "sample": "20 full-batch recurrent steps (B=256,H=16) of the reference's "
+                                              "recurrent_forward on the host cores" if kind == "reference" else
+                                              "20 full-batch recurrent steps of the CPU restatement of recurrent_forward",
+                                    "host_cpus": os.cpu_count()}
+            if not args.quick:
+                line["prefill_cpu"] = reference_prefill_cpu()
+                line["swa_cpu"] = swa_restatement_cpu()
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
