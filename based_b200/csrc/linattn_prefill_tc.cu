@@ -20,6 +20,7 @@
 // equals phi(q).phi(k) of the 273-feature map exactly; the 273-wide reference layout is restored
 // only when the final state is written.
 #include "linattn_tc_shared.cuh"
+#include "tma.cuh"
 
 #include <mutex>
 #include <type_traits>
@@ -40,7 +41,7 @@ using namespace tc;
 using namespace tcp;
 
 
-// Shared memory map (bytes).  One stage = Q [128 tok x 16] K-major (4096) + K (4096) +
+// Shared memory map (bytes).  One stage = Q [2 k-halves][128 tok][16 B] K-major (4096) + K (4096) +
 // V' MN-major [NV/8 groups of 8 columns][128 tok][16 B].  The state-update MMA reads V'^T as an
 // M = 128 operand, i.e. 16 column groups from the stage's V' base; the groups past NV/8 are
 // whatever follows in shared memory and only feed accumulator lanes >= NV, which nobody reads.
@@ -71,7 +72,7 @@ enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_P_READY, B_O_DONE, B_ST_DONE
            B_STB_READY, B_O_FREE, B_PK_FREE, B_PK_FREE1, B_INIT, B_FIN, B_COUNT };
 
 
-__global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params p) {
+__global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_constant__ Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -130,47 +131,27 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   const uint32_t tlane = tmem + ((uint32_t)(qd * 32) << 16);  // this warp's lane window, column 0
 
   if (warp >= W_LOAD) {
-    // ================================================================ loaders: cp.async, 16-byte pieces.
-    // Load warp w owns buffer w and the chunks j = w (mod the buffer count): wait until the buffer is free,
-    // issue the chunk, wait for it to land, publish it.  Three chunks are in flight per CTA.
-    const int st = warp - W_LOAD, NS = lay.nstage;
-    const __nv_bfloat16* qb = p.q + b * p.sq.b + h * p.sq.h + (int64_t)tok_base * p.sq.l;
-    const __nv_bfloat16* kb = p.k + b * p.sk.b + h * p.sk.h + (int64_t)tok_base * p.sk.l;
-    const __nv_bfloat16* vb = p.v + b * p.sv.b + h * p.sv.h + (int64_t)tok_base * p.sv.l;
-    const bool need_q = mode != MODE_SEG_STATE;
-    const uint32_t base = sb + st * lay.stage_bytes;
-    // q/k: piece i = lane + 32 n  ->  token (lane >> 1) + 16 n, half lane & 1
-    const int qk_tk = lane >> 1, qk_half = lane & 1;
-    const uint32_t qk_off = (qk_tk >> 3) * 256 + qk_half * 128 + (qk_tk & 7) * 16;
-    // v: piece i = lane + 32 n  ->  token i / gpt, 16-byte column group i % gpt, advanced incrementally
-    const int gpt = dv >> 3, dq = 32 / gpt, dr = 32 % gpt;
-    for (int j = st; j < nchunks && st < NS; j += NS) {
-      if (j >= NS) wait(B_EMPTY + st, j / NS - 1, 0x100u);
-      const int tok0 = j * C;
-      {
-        const __nv_bfloat16* qp = qb + (int64_t)(tok0 + qk_tk) * p.sq.l + qk_half * 8;
-        const __nv_bfloat16* kp = kb + (int64_t)(tok0 + qk_tk) * p.sk.l + qk_half * 8;
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-          const bool ok = tok0 + qk_tk + 16 * n < L;
-          if (need_q) cp_async16(base + qk_off + n * 512, ok ? qp + (int64_t)(16 * n) * p.sq.l : qb, ok);
-          cp_async16(base + 4096 + qk_off + n * 512, ok ? kp + (int64_t)(16 * n) * p.sk.l : kb, ok);
-        }
+    // ================================================================ producer: one thread, three TMA tile copies per chunk
+    // Q and K land as [k-half][token][16 B], V' as [8-column group][token][16 B]: the no-swizzle UMMA layouts, one
+    // cp.async.bulk.tensor each (the tensor maps cut a row into 16-byte groups and put the group index outside the
+    // token index).  Tokens past the end of the sequence are zero-filled by the copy unit.  Up to `nstage` chunks are
+    // in flight; a stage is refilled when the MMAs that read it have completed (B_EMPTY).
+    if (warp == W_LOAD && lane == 0) {
+      const int NS = lay.nstage;
+      const bool need_q = mode != MODE_SEG_STATE;
+      const uint32_t bytes = (need_q ? 8192u : 4096u) + (uint32_t)dv * 256u;
+      int st = 0;
+      uint32_t round = 0;
+      for (int j = 0; j < nchunks; ++j) {
+        if (j >= NS) mbar_wait_bounded<false>(bar(B_EMPTY + st), (round - 1) & 1u, abort_flag, p.status, 0x100u);
+        const uint32_t base = sb + st * lay.stage_bytes;
+        const int tok = tok_base + j * C;
+        tma::mbar_expect_tx(bar(B_FULL + st), bytes);
+        if (need_q) tma::load_5d(base, &p.mq, bar(B_FULL + st), 0, tok, 0, h, b);
+        tma::load_5d(base + 4096, &p.mk, bar(B_FULL + st), 0, tok, 0, h, b);
+        tma::load_5d(base + 8192, &p.mv, bar(B_FULL + st), 0, tok, 0, h, b);
+        if (++st == NS) { st = 0; ++round; }
       }
-      {
-        int tk = lane / gpt, g = lane - tk * gpt;
-        for (int n = 0; n < 4 * gpt; ++n) {
-          const bool ok = tok0 + tk < L;
-          cp_async16(base + 8192 + g * 2048 + tk * 16, ok ? vb + (int64_t)(tok0 + tk) * p.sv.l + g * 8 : vb, ok);
-          tk += dq; g += dr;
-          if (g >= gpt) { g -= gpt; ++tk; }
-        }
-      }
-      cp_async_commit();
-      cp_async_wait_all();
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_FULL + st));
     }
   } else if (warp == W_MMA) {
     // ================================================================ MMA issue: one thread runs the whole loop
@@ -184,8 +165,8 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       const uint32_t idesc_o_st = make_idesc_bf16(128, NV, 0, 0);   // A = phi'(Q) (TMEM), B = state K-major
       const uint32_t idesc_st = make_idesc_bf16(128, DR, 1, 1);     // A = V'^T MN-major, B = phi'(K) MN-major
       // Descriptors differ between K-steps only in the start address (bits 0-13, units of 16 B).
-      const uint64_t d_q = make_smem_desc(sb, 128, 256);                 // + stage offset
-      const uint64_t d_k = make_smem_desc(sb + 4096, 128, 256);
+      const uint64_t d_q = make_smem_desc(sb, 2048, 128);                // + stage offset; k-halves 2048 B apart
+      const uint64_t d_k = make_smem_desc(sb + 4096, 2048, 128);
       const uint64_t d_v = make_smem_desc(sb + 8192, 128, 2048);         // + stage offset, + 16 per K-step
       const uint64_t d_pk = make_smem_desc(sb + lay.phik, 128, 2048);    // + buffer offset, + 16 per K-step
       const uint64_t d_stb = make_smem_desc(sb + lay.stb, 2048, 128);    // + 256 per K-step
@@ -264,12 +245,12 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
   } else if (warp < 4) {
     // ================================================================ expansion warps: phi'(Q) -> TMEM, phi'(K) -> smem
     for (int c = 0; c < nchunks; ++c) {
-      const uint8_t* stg = smem + (c % lay.nstage) * lay.stage_bytes + (t >> 3) * 256 + (t & 7) * 16;
+      const uint8_t* stg = smem + (c % lay.nstage) * lay.stage_bytes + t * 16;   // [k-half][token][16 B]
       const bool valid = c * C + t < L;
       wait(B_FULL + c % lay.nstage, c / lay.nstage, 0x300u);
       uint32_t X[8];
       {
-        const uint4 a = *reinterpret_cast<const uint4*>(stg), bq = *reinterpret_cast<const uint4*>(stg + 128);
+        const uint4 a = *reinterpret_cast<const uint4*>(stg), bq = *reinterpret_cast<const uint4*>(stg + 2048);
         X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
       }
       if (mode != MODE_SEG_STATE) {
@@ -293,7 +274,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const Params 
       if (lane == 0) mbar_arrive(bar(B_PQ_READY));
       }
       {
-        const uint4 a = *reinterpret_cast<const uint4*>(stg + 4096), bq = *reinterpret_cast<const uint4*>(stg + 4096 + 128);
+        const uint4 a = *reinterpret_cast<const uint4*>(stg + 4096), bq = *reinterpret_cast<const uint4*>(stg + 4096 + 2048);
         X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
       }
       if (!valid) {  // tokens past the end contribute nothing to the state: phi'(K) = 0, also the constant
@@ -615,6 +596,47 @@ size_t linattn_prefill_tc_scratch_bytes(int B, int H, int L, int dv, int nseg) {
   return (size_t)B * H * (n - 1) * (dv + 1) * DR * sizeof(float);
 }
 
+// Once per device: the address of the status word and the kernel's shared-memory limit (both are properties of
+// the device's primary context and stay valid for its lifetime).
+struct DeviceInit {
+  bool done = false;
+  unsigned int* status = nullptr;
+};
+static int device_init(unsigned int** status) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static DeviceInit init[kMaxDevices];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return BASED_ERR_TOO_LARGE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!init[dev].done) {
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&init[dev].status), g_tc_status);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(linattn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem(112).total > Smem(64).total ? Smem(112).total : Smem(64).total);
+    if (e != cudaSuccess) return (int)e;
+    init[dev].done = true;
+  }
+  *status = init[dev].status;
+  return 0;
+}
+
+// Tensor map of a [B][H][L][row] operand whose rows (`groups` x 8 bf16) are cut into 16-byte groups; cached.
+static int grouped_map(CUtensorMap* out, const void* base, int groups, int L, int H, int B, Strides3 s) {
+  static tma::MapCache cache;
+  // an extent of 1 may come with any stride: give it a harmless one
+  const int64_t sh = H == 1 ? 8 : s.h, sbb = B == 1 ? 8 : s.b, sl = L == 1 ? 8 * groups : s.l;
+  if (sh <= 0 || sbb <= 0 || sl <= 0) return BASED_ERR_IMPL;
+  const tma::MapKey key = tma::make_key(base, 8, (uint64_t)L, (uint64_t)groups, (uint64_t)H, (uint64_t)B, sl, 8, sh, sbb, 8, C,
+                                        (uint32_t)groups, 5);
+  if (cache.find(key, out)) return 0;
+  if (tma::encode_bf16_grouped_rows(out, base, (uint64_t)groups, (uint64_t)L, (uint64_t)H, (uint64_t)B, sl, sh, sbb, C))
+    return BASED_ERR_IMPL;
+  cache.put(key, *out);
+  return 0;
+}
+
 int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
                               int B, int H, int L, int dv, Strides3 sq, Strides3 sk, Strides3 sv, Strides3 sy,
                               int state_dtype, float eps, int nseg, void* scratch, size_t scratch_bytes,
@@ -626,6 +648,10 @@ int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void*
   for (int64_t s : all)
     if (s % 8 != 0) return BASED_ERR_IMPL;  // 16-byte vector accesses on every row
   Params p;
+  int rc = grouped_map(&p.mq, q, 2, L, H, B, sq);
+  if (rc == 0) rc = grouped_map(&p.mk, k, 2, L, H, B, sk);
+  if (rc == 0) rc = grouped_map(&p.mv, v, dv / 8, L, H, B, sv);
+  if (rc != 0) return rc;
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k = static_cast<const __nv_bfloat16*>(k);
   p.v = static_cast<const __nv_bfloat16*>(v);
@@ -636,11 +662,9 @@ int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void*
   p.state_bf16 = state_dtype == BASED_BF16;
   p.sq = sq; p.sk = sk; p.sv = sv; p.sy = sy;
   p.eps = eps;
-  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_tc_status);
-  if (e != cudaSuccess) return (int)e;
+  rc = device_init(&p.status);
+  if (rc != 0) return rc;
   const Smem lay(dv);
-  e = cudaFuncSetAttribute(linattn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total);
-  if (e != cudaSuccess) return (int)e;
   int seg_chunks;
   plan_segments(L, nseg, &nseg, &seg_chunks);
   p.nseg = nseg;

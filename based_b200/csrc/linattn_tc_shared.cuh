@@ -6,6 +6,8 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
+#include <cuda.h>
+
 #include <type_traits>
 
 namespace based {
@@ -16,7 +18,7 @@ using namespace tc;
 constexpr int C = 128;     // tokens per chunk
 constexpr int DR = 160;    // packed + padded feature count
 // threads per CTA: 4 expansion warps (0-3), 4 polynomial / state-drain warps (4-7), 4 output warps (8-11),
-// the MMA warp (12), 3 load warps (13-15).  A compute warp w reaches TMEM lanes 32*(w%4)..+31.
+// the MMA warp (12), the TMA producer warp (13; one thread issues the copies), 2 spare warps.  A compute warp w reaches TMEM lanes 32*(w%4)..+31.
 constexpr int NT = 512;
 constexpr int W_OUT = 8, W_MMA = 12, W_LOAD = 13;
 
@@ -118,6 +120,7 @@ __device__ __forceinline__ int packed_index(int f, bool& offdiag) {
 }
 
 struct Params {
+  CUtensorMap mq, mk, mv;   // q, k: [B][H][2 k-halves][L][8]; v: [B][H][dv/8 groups][L][8]; box = 128 tokens
   const __nv_bfloat16 *q, *k, *v;
   __nv_bfloat16* y;
   void *kv_state, *k_state;

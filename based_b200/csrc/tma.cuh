@@ -6,6 +6,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
+
+#include <mutex>
 
 namespace based {
 namespace tma {
@@ -48,6 +51,74 @@ inline int encode_bf16_4d_sw128(CUtensorMap* map, const void* base, uint64_t d0,
   return encode_bf16_4d(map, base, d0, d1, d2, d3, s1, s2, s3, box0, box1, true);
 }
 
+// bf16 rows of `groups * 8` contiguous elements, seen as [d4][d3][groups][rows][8]: the row is cut into 16-byte
+// groups and the GROUP index becomes a tensor dimension outside the row index.  A box of
+// 8 x box_rows x groups x 1 x 1 then lands in shared memory as [group][row][16 bytes] - the no-swizzle canonical
+// layout of a UMMA operand (K-major with the k-halves as groups, or MN-major with 8-column groups) - in ONE copy.
+// Strides of rows, d3, d4 in ELEMENTS (multiples of 8).  Rows past `rows` read as zero.  Returns 0 on success.
+inline int encode_bf16_grouped_rows(CUtensorMap* map, const void* base, uint64_t groups, uint64_t rows, uint64_t d3,
+                                    uint64_t d4, int64_t s_row, int64_t s3, int64_t s4, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -1;
+  const cuuint64_t dims[5] = {8, rows, groups, d3, d4};
+  const cuuint64_t strides[4] = {(cuuint64_t)s_row * 2, 16, (cuuint64_t)s3 * 2, (cuuint64_t)s4 * 2};
+  const cuuint32_t box[5] = {8, box_rows, (cuuint32_t)groups, 1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+// A few recently encoded tensor maps, keyed by everything that went into them.  Encoding costs a driver call per
+// map; a generation loop or a benchmark calls with the same pointers and shapes again and again.
+struct MapKey {
+  const void* base;
+  uint64_t dims[5];
+  int64_t strides[4];
+  uint32_t box[3];
+  uint32_t kind;
+};
+class MapCache {
+ public:
+  // Returns true and fills *out when the key is cached.
+  bool find(const MapKey& k, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(mu_);
+    for (int i = 0; i < kSlots; ++i)
+      if (used_[i] && memcmp(&keys_[i], &k, sizeof(MapKey)) == 0) {
+        *out = maps_[i];
+        return true;
+      }
+    return false;
+  }
+  void put(const MapKey& k, const CUtensorMap& m) {
+    std::lock_guard<std::mutex> lock(mu_);
+    keys_[next_] = k;
+    maps_[next_] = m;
+    used_[next_] = true;
+    next_ = (next_ + 1) % kSlots;
+  }
+
+ private:
+  static constexpr int kSlots = 32;
+  std::mutex mu_;
+  MapKey keys_[kSlots];
+  CUtensorMap maps_[kSlots];
+  bool used_[kSlots] = {};
+  int next_ = 0;
+};
+inline MapKey make_key(const void* base, uint64_t a, uint64_t b, uint64_t c, uint64_t d, uint64_t e, int64_t s0,
+                       int64_t s1, int64_t s2, int64_t s3, uint32_t b0, uint32_t b1, uint32_t b2, uint32_t kind) {
+  MapKey k;
+  memset(&k, 0, sizeof(k));  // padding bytes take part in the comparison
+  k.base = base;
+  k.dims[0] = a; k.dims[1] = b; k.dims[2] = c; k.dims[3] = d; k.dims[4] = e;
+  k.strides[0] = s0; k.strides[1] = s1; k.strides[2] = s2; k.strides[3] = s3;
+  k.box[0] = b0; k.box[1] = b1; k.box[2] = b2;
+  k.kind = kind;
+  return k;
+}
+
 // ---------------------------------------------------------------- device
 __device__ __forceinline__ void mbar_expect_tx(uint32_t mbar_saddr, uint32_t bytes) {
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(mbar_saddr),
@@ -63,6 +134,14 @@ __device__ __forceinline__ void load_4d(uint32_t dst_saddr, const CUtensorMap* m
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n" ::
           "r"(dst_saddr),
       "l"(map), "r"(mbar_saddr), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void load_5d(uint32_t dst_saddr, const CUtensorMap* map, uint32_t mbar_saddr, int c0, int c1,
+                                        int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n" ::
+          "r"(dst_saddr),
+      "l"(map), "r"(mbar_saddr), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
 // Tile store shared -> global (rows past the tensor's extent are clipped); never started at a

@@ -111,6 +111,10 @@ def test_reference_generate_graph_replay_equals_eager(models):
     B, L, N = 2, 50, 20
     ids = torch.randint(0, KW["vocab_size"], (B, L), device="cuda", generator=g)
     m = models["ref_b200"]
+    # The reference keeps one decoding cache per model and reuses it for any batch up to the one it was built for
+    # (generation.py:626-633), but its own LinearAttention / BaseConv states only work at exactly that batch
+    # (linear_attention.py:240, convolution.py:104-106): a run at another batch size starts from a fresh cache.
+    m._decoding_cache = None
     eager = m.generate(ids, max_length=L + N, top_k=1, cg=False, return_dict_in_generate=True, output_scores=True)
     graphed = m.generate(ids, max_length=L + N, top_k=1, cg=True, return_dict_in_generate=True, output_scores=True)
     assert eager.sequences.shape == (B, L + N)
