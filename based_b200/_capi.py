@@ -41,6 +41,12 @@ SIGNATURES = {
     "based_gated_act": (c_int, [c_void_p] * 3 + [c_int64, c_int] + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "based_decode_linear": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_int64] * 2 + [c_int, c_int]
                             + [c_void_p] * 3 + [c_int, c_int, c_void_p]),
+    "based_tp_outproj_workspace_bytes": (ctypes.c_size_t, [c_int] * 3),
+    "based_tp_outproj_workspace_init": (c_int, [c_void_p, ctypes.c_size_t, c_void_p]),
+    "based_tp_outproj_allreduce": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_int64] * 2 + [POINTER(c_void_p), c_int, c_int,
+                                                                                          c_int, c_void_p]),
+    "based_tp_outproj_allreduce_emulated": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_void_p, POINTER(c_void_p)]
+                                            + [c_int] * 3 + [c_int64] * 2 + [POINTER(c_void_p), c_int, c_int, c_void_p]),
     "based_rotary_qkv_cache": (c_int, [c_void_p] + [c_int] * 4 + [_I64P, c_void_p, c_void_p, c_void_p, _I64P, c_void_p]),
 }
 
@@ -73,6 +79,11 @@ def read_status(reset: bool = True) -> int:
     out = ctypes.c_uint(0)
     check(lib().based_read_status(ctypes.byref(out), 1 if reset else 0), "based_read_status")
     return out.value
+
+
+def pointers(vals):
+    """A C array of void* from integers (device addresses)."""
+    return (c_void_p * len(vals))(*[int(v) for v in vals])
 
 
 def strides(*vals):

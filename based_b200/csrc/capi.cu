@@ -1,5 +1,6 @@
 // extern "C" entry points: host-side argument validation, then dispatch to the launchers.
-// Nothing here allocates device memory or synchronises.
+// Nothing here allocates device memory.  The launches are asynchronous; the one call that waits for the device
+// is based_read_status (a blocking copy of the status words).
 #include "common.cuh"
 
 using namespace based;
@@ -35,10 +36,11 @@ const char* based_error_string(int code) {
 }
 
 int based_read_status(unsigned int* out, int reset) {
-  unsigned int a = 0, b = 0;
+  unsigned int a = 0, b = 0, c = 0;
   int rc = read_tc_status(&a, reset);
   if (rc == 0) rc = read_tc_status_swa(&b, reset);
-  if (out) *out = a | b;
+  if (rc == 0) rc = read_tp_status(&c, reset);
+  if (out) *out = a | b | c;
   return rc;
 }
 
@@ -289,6 +291,40 @@ int based_rotary_qkv_cache(void* qkv, int B, int L, int H, int hd, const int64_t
   return launch_rotary_qkv_cache(qkv, B, L, H, hd, qkv_strides[0], qkv_strides[1], qkv_strides[2], qkv_strides[3],
                                  rotary_cos, rotary_sin, kv_cache, cache_strides[0], cache_strides[1],
                                  static_cast<cudaStream_t>(stream));
+}
+
+size_t based_tp_outproj_workspace_bytes(int world, int max_rows, int N) {
+  return tp_outproj_workspace_bytes(world, max_rows, N);
+}
+
+int based_tp_outproj_workspace_init(void* workspace, size_t bytes, void* stream) {
+  if (!workspace) return BASED_ERR_NULL;
+  if (bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return BASED_ERR_SCRATCH;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(workspace, 0, bytes, st);
+  if (e != cudaSuccess) return (int)e;
+  // epoch of the first call = 1: the zero-filled flags then read as "nothing has arrived"
+  e = cudaMemsetAsync(workspace, 1, 1, st);   // little-endian word 0 becomes 0x00000001
+  return (int)e;
+}
+
+int based_tp_outproj_allreduce(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                               int64_t x_row_stride, int64_t out_row_stride, void* const* workspaces, int max_rows,
+                               int rank, int world, void* stream) {
+  if (!x || !w || !out || !workspaces) return BASED_ERR_NULL;
+  const void* xs[1] = {x};
+  const void* ws[1] = {w};
+  void* os[1] = {out};
+  return launch_tp_outproj_allreduce(xs, ws, bias, os, workspaces, M, N, K, x_row_stride, out_row_stride, max_rows, rank,
+                                     world, 0, static_cast<cudaStream_t>(stream));
+}
+
+int based_tp_outproj_allreduce_emulated(const void* const* x, const void* const* w, const void* bias, void* const* out,
+                                        int M, int N, int K, int64_t x_row_stride, int64_t out_row_stride,
+                                        void* const* workspaces, int max_rows, int world, void* stream) {
+  if (!x || !w || !out || !workspaces) return BASED_ERR_NULL;
+  return launch_tp_outproj_allreduce(x, w, bias, out, workspaces, M, N, K, x_row_stride, out_row_stride, max_rows, 0,
+                                     world, 1, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

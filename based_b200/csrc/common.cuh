@@ -91,6 +91,12 @@ int launch_decode_linear(const void* x, const void* w, const void* bias, void* o
                          int64_t so, int epilogue, int act, void* conv_state, const void* conv_weight,
                          const void* conv_bias, int conv_k, int conv_w_dtype, cudaStream_t stream);
 
+int launch_tp_outproj_allreduce(const void* const* x, const void* const* w, const void* bias, void* const* out,
+                                void* const* workspaces, int M, int N, int K, int64_t sx, int64_t so, int Mmax,
+                                int rank, int world, int emulate, cudaStream_t stream);
+size_t tp_outproj_workspace_bytes(int world, int Mmax, int N);
+int read_tp_status(unsigned int* out, int reset);      // fused output projection + all-reduce
+
 int read_tc_status(unsigned int* out, int reset);      // linear-attention prefill kernel
 int read_tc_status_swa(unsigned int* out, int reset);  // sliding-window prefill kernel
 

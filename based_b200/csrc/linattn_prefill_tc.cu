@@ -46,15 +46,17 @@ using namespace tcp;
 // M = 128 operand, i.e. 16 column groups from the stage's V' base; the groups past NV/8 are
 // whatever follows in shared memory and only feed accumulator lanes >= NV, which nobody reads.
 struct Smem {
-  int nstage, npk, stage_bytes, phik, stb, ystage, yrow_bytes, bar, total;
+  int nstage, npk, stage_bytes, phik, stb, stb_bytes, ystage, yrow_bytes, bar, total;
   __host__ __device__ explicit Smem(int dv) {
+    const int nv = dv + 16;
     nstage = dv <= 64 ? 3 : 2;     // what fits in 227 KB
     npk = dv <= 64 ? 2 : 1;        // phi'(K) buffers
-    stage_bytes = 8192 + ((dv + 16) >> 3) * 2048;
+    stage_bytes = 8192 + (nv >> 3) * 2048;
     phik = nstage * stage_bytes;   // npk x 40960  MN-major [20 groups of 8 feats][128 tok][16 B]
-    stb = phik + npk * 40960;      // 40960  K-major  [20 k-units][128 rows][16 B]
-    ystage = stb + 40960;          // output tile [128 rows][dv bf16 + 16 B pad] for the bulk stores
-    yrow_bytes = dv * 2 + 16;      // the pad makes the per-row 16-byte stores bank-conflict free
+    stb = phik + npk * 40960;      // 2 x stb_bytes: bf16 state, K-major [20 k-units][NV rows][16 B], double-buffered
+    stb_bytes = nv * 320;
+    ystage = stb + 2 * stb_bytes;  // output tile [128 rows][32 columns bf16 + 16 B pad], one round of the epilogue
+    yrow_bytes = 64 + 16;          // the pad makes the per-row 16-byte stores bank-conflict free
     bar = ystage + C * yrow_bytes; // mbarriers, TMEM base, abort flag
     total = bar + 256;
   }
@@ -68,10 +70,26 @@ constexpr uint32_t TM_PQ = 416;   // phi'(Q) bf16, 80 columns
 constexpr uint32_t TM_COLS = 512;
 
 // mbarrier slots (8 bytes each) from Smem::bar
-enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_P_READY, B_O_DONE, B_ST_DONE, B_PQ_READY, B_PK_READY,
-           B_STB_READY, B_O_FREE, B_PK_FREE, B_PK_FREE1, B_INIT, B_FIN, B_COUNT };
+//   B_FULL / B_EMPTY   per stage: tile landed (TMA transaction bytes) / the MMAs that read it have completed
+//   B_S_DONE           S(c) = Q K^T complete                                   (tcgen05.commit)
+//   B_A_READY          P(c) written AND O free (O(c-1) read out) AND tile c+1 landed   (poly warps + output warps)
+//   B_X_READY          phase 0: phi'(K_0) written; phase c+1: phi'(Q_c) and phi'(K_{c+1}) written   (expansion warps)
+//   B_O_DONE           readout of chunk c complete: O(c) final, phi'(Q_c) consumed   (commit)
+//   B_ST_DONE          state update of chunk c complete                              (commit)
+//   B_STB_READY        bf16 copy of the state after chunk c written (drain warps)
+//   B_PK_FREE[2]       the update that read this phi'(K) buffer has completed        (commit)
+//   B_INIT             carried-in state preloaded (sequence split)      B_FIN   last update complete (state-only mode)
+enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_A_READY, B_X_READY, B_O_DONE, B_ST_DONE, B_STB_READY, B_PK_FREE,
+           B_PK_FREE1, B_INIT, B_FIN, B_COUNT };
 
-
+// Per 128-token chunk c the MMA thread issues, in this order,
+//   PV(c):  O  = P(c) V'(c)                    8 MMAs  M128 N=NV  K16   A = P in TMEM
+//   S(c+1)                                     1 MMA   M128 N128  K16
+//   R(c):   O += phi'(Q_c) State(c-1)          10 MMAs M128 N=NV  K16   A = phi'(Q) in TMEM, B = bf16 state (smem)
+//   U(c+1): St^T += V'(c+1)^T phi'(K_{c+1})    8 MMAs  M128 N160  K16   (the state update runs ONE CHUNK AHEAD)
+// so that the output warps read O(c) while U(c+1) keeps the tensor pipe busy, the polynomial of chunk c+1 and
+// the expansions run under PV / R, and the only chain carried from chunk to chunk is
+// U(c) -> drain (fp32 state -> bf16 operand) -> U(c+1): the drain reads the accumulator that U(c+1) writes.
 __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_constant__ Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = smem_u32(smem);
@@ -89,12 +107,17 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   const int mode = p.mode;
   const bool has_init = mode == MODE_SEG_OUTPUT && seg > 0;
   const bool write_state = mode != MODE_SEG_STATE && seg == p.nseg - 1 && p.kv_state != nullptr;
+  const bool q3_has_state = 96 < NV;          // TMEM lanes 96..127 hold state rows (dv > 80)
+  const int NS = lay.nstage, NPK = lay.npk;
 
   auto bar = [&](int i) { return sb + lay.bar + 8 * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + lay.bar + 8 * B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + lay.bar + 8 * B_COUNT + 4);
   auto wait = [&](int i, uint32_t parity, unsigned int code) {
     mbar_wait_bounded(bar(i), parity & 1u, abort_flag, p.status, code);
+  };
+  auto wait1 = [&](int i, uint32_t parity, unsigned int code) {   // by one lane of a diverged warp
+    mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
   };
 
   // ------------------------------------------------------------------ set-up
@@ -103,11 +126,10 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
     mbar_init(bar(B_S_DONE), 1);
     mbar_init(bar(B_O_DONE), 1);
     mbar_init(bar(B_ST_DONE), 1);
-    mbar_init(bar(B_P_READY), 4);
-    mbar_init(bar(B_PQ_READY), 4);
-    mbar_init(bar(B_PK_READY), 4);
+    // polynomial warps: 4 (one per quadrant), 5 when quadrant 3 is shared by two warps; + 4 output warps
+    mbar_init(bar(B_A_READY), 4 + (q3_has_state ? 4 : 5));
+    mbar_init(bar(B_X_READY), 4);
     mbar_init(bar(B_STB_READY), 4);
-    mbar_init(bar(B_O_FREE), 4);
     mbar_init(bar(B_PK_FREE), 1);
     mbar_init(bar(B_PK_FREE + 1), 1);
     mbar_init(bar(B_INIT), 4);
@@ -118,7 +140,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TM_COLS);
   // V' column groups dv/8 (ones column) and dv/8 + 1 (zeros) are constant for the whole kernel.
-  for (int i = tid; i < lay.nstage * 2 * C; i += NT) {
+  for (int i = tid; i < NS * 2 * C; i += NT) {
     const int st = i / (2 * C), r = i - st * 2 * C, g = r / C, tk = r - g * C;
     const uint4 val = g == 0 ? make_uint4(0x00003F80u, 0, 0, 0) : make_uint4(0, 0, 0, 0);  // bf16 1.0 in element 0
     *reinterpret_cast<uint4*>(smem + st * lay.stage_bytes + 8192 + ((dv >> 3) + g) * 2048 + tk * 16) = val;
@@ -130,36 +152,84 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   const uint32_t tmem = *tmem_slot;
   const uint32_t tlane = tmem + ((uint32_t)(qd * 32) << 16);  // this warp's lane window, column 0
 
+  // One thread feeds the stages: Q and K land as [k-half][token][16 B], V' as [8-column group][token][16 B] - the
+  // no-swizzle UMMA layouts - by one cp.async.bulk.tensor each (the tensor maps cut a row into 16-byte groups and
+  // put the group index outside the token index).  Tokens past the end of the sequence are zero-filled by the
+  // copy unit.  Chunk j goes to stage j % NS once the MMAs that read chunk j - NS have completed.
+  const bool need_q = mode != MODE_SEG_STATE;
+  auto issue_tile = [&](int j) {
+    const int st = j % NS;
+    if (j >= NS) wait1(B_EMPTY + st, j / NS - 1, 0x100u);
+    const uint32_t base = sb + st * lay.stage_bytes;
+    const int tok = tok_base + j * C;
+    tma::mbar_expect_tx(bar(B_FULL + st), (need_q ? 8192u : 4096u) + (uint32_t)dv * 256u);
+    if (need_q) tma::load_5d(base, &p.mq, bar(B_FULL + st), 0, tok, 0, h, b);
+    tma::load_5d(base + 4096, &p.mk, bar(B_FULL + st), 0, tok, 0, h, b);
+    tma::load_5d(base + 8192, &p.mv, bar(B_FULL + st), 0, tok, 0, h, b);
+  };
+
+  // P(c) = causal(1 + s/4 + s^2/32), evaluated in bf16x2 (two FMAs per pair), in place over S, for the 32-column
+  // pieces [p0, p1) of this warp's 32 rows; pieces right of the diagonal block (> qd) are zeros, no load.
+  auto poly_pieces = [&](int p0, int p1) {
+    constexpr uint32_t k1 = 0x3F803F80u, kq = 0x3E803E80u, k32 = 0x3D003D00u;  // (1,1) (1/4,1/4) (1/32,1/32)
+#pragma unroll 1
+    for (int piece = p0; piece < p1; ++piece) {
+      if (piece <= qd) {
+        uint32_t sreg[32], pk[16];
+        tmem_ld32(tlane + TM_S + piece * 32, sreg);
+        tmem_ld_wait();
+        const int rel = t - piece * 32;  // columns 0..rel of this piece are visible (rel >= 31 left of the diagonal)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+          const uint32_t pv = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
+          const uint32_t mask = (2 * i + 1 <= rel) ? 0xFFFFFFFFu : ((2 * i <= rel) ? 0x0000FFFFu : 0u);
+          pk[i] = pv & mask;
+        }
+        tmem_st16(tlane + TM_S + piece * 16, pk);
+      } else {
+        uint32_t z[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) z[i] = 0;
+        tmem_st16(tlane + TM_S + piece * 16, z);
+      }
+    }
+  };
+  // the polynomial of chunk c by this warp (pieces [p0, p1)), then one arrival on B_A_READY - which also vouches for
+  // tile c + 1 having landed, so the MMA thread need not test that barrier itself
+  auto make_p = [&](int c, int p0, int p1) {
+    wait(B_S_DONE, c, 0x400u);
+    fence_after_sync();
+    poly_pieces(p0, p1);
+    tmem_st_wait();
+    fence_before_sync();
+    if (c + 1 < nchunks) wait(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x403u);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(B_A_READY));
+  };
+
   if (warp >= W_LOAD) {
-    // ================================================================ producer: one thread, three TMA tile copies per chunk
-    // Q and K land as [k-half][token][16 B], V' as [8-column group][token][16 B]: the no-swizzle UMMA layouts, one
-    // cp.async.bulk.tensor each (the tensor maps cut a row into 16-byte groups and put the group index outside the
-    // token index).  Tokens past the end of the sequence are zero-filled by the copy unit.  Up to `nstage` chunks are
-    // in flight; a stage is refilled when the MMAs that read it have completed (B_EMPTY).
-    if (warp == W_LOAD && lane == 0) {
-      const int NS = lay.nstage;
-      const bool need_q = mode != MODE_SEG_STATE;
-      const uint32_t bytes = (need_q ? 8192u : 4096u) + (uint32_t)dv * 256u;
-      int st = 0;
-      uint32_t round = 0;
-      for (int j = 0; j < nchunks; ++j) {
-        if (j >= NS) mbar_wait_bounded<false>(bar(B_EMPTY + st), (round - 1) & 1u, abort_flag, p.status, 0x100u);
-        const uint32_t base = sb + st * lay.stage_bytes;
-        const int tok = tok_base + j * C;
-        tma::mbar_expect_tx(bar(B_FULL + st), bytes);
-        if (need_q) tma::load_5d(base, &p.mq, bar(B_FULL + st), 0, tok, 0, h, b);
-        tma::load_5d(base + 4096, &p.mk, bar(B_FULL + st), 0, tok, 0, h, b);
-        tma::load_5d(base + 8192, &p.mv, bar(B_FULL + st), 0, tok, 0, h, b);
-        if (++st == NS) { st = 0; ++round; }
+    // ================================================================ polynomial warps of quadrants 1-3; warp 13's
+    // lane 0 is also the TMA producer
+    if (mode == MODE_SEG_STATE) {
+      if (warp == W_LOAD && lane == 0)
+        for (int j = 0; j < nchunks; ++j) issue_tile(j);
+    } else {
+      if (warp == W_LOAD && lane == 0)
+        for (int j = 0; j < min(NS, nchunks); ++j) issue_tile(j);
+      __syncwarp();
+      // quadrant 3 is shared with warp 7 when that warp has no state rows to drain
+      const int p0 = (qd == 3 && !q3_has_state) ? 2 : 0;
+      for (int c = 0; c < nchunks; ++c) {
+        make_p(c, p0, 4);
+        // tile c + NS - 1 replaces tile c - 1, whose last reader was the readout of chunk c - 1
+        if (warp == W_LOAD && lane == 0 && c >= 1 && c + NS - 1 < nchunks) issue_tile(c + NS - 1);
+        __syncwarp();
       }
     }
   } else if (warp == W_MMA) {
     // ================================================================ MMA issue: one thread runs the whole loop
     if (lane == 0) {
-      auto mwait = [&](int i, uint32_t parity, unsigned int code) {
-        mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
-      };
-      const int NS = lay.nstage, NPK = lay.npk;
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_o_pv = make_idesc_bf16(128, NV, 0, 1);   // A = P (TMEM), B = V' MN-major
       const uint32_t idesc_o_st = make_idesc_bf16(128, NV, 0, 0);   // A = phi'(Q) (TMEM), B = state K-major
@@ -169,122 +239,98 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       const uint64_t d_k = make_smem_desc(sb + 4096, 2048, 128);
       const uint64_t d_v = make_smem_desc(sb + 8192, 128, 2048);         // + stage offset, + 16 per K-step
       const uint64_t d_pk = make_smem_desc(sb + lay.phik, 128, 2048);    // + buffer offset, + 16 per K-step
-      const uint64_t d_stb = make_smem_desc(sb + lay.stb, 2048, 128);    // + 256 per K-step
-      const uint32_t stage_units = (uint32_t)lay.stage_bytes >> 4;
-      // stage / phase bookkeeping by counters: st = c % NS, st_par = (c / NS) & 1, and the same for c + 1
-      int st = 0, st1 = (1 % NS);
-      uint32_t st1_par = (NS == 1) ? 1u : 0u;
-      int pkb = 0;
+      const uint64_t d_stb = make_smem_desc(sb + lay.stb, NV * 16, 128); // + buffer offset, + 2 NV per K-step
+      const uint32_t stage_units = (uint32_t)lay.stage_bytes >> 4, stb_units = (uint32_t)lay.stb_bytes >> 4;
+      const uint32_t stb_step = 2 * NV;
+      // U(c): St^T (+)= V'(c)^T phi'(K_c)
+      auto issue_update = [&](int c, bool acc0) {
+        const uint64_t dv_c = d_v + (c % NS) * stage_units, d_pk_c = d_pk + (c % NPK) * (40960 >> 4);
+#pragma unroll
+        for (int j = 0; j < C / 16; ++j)
+          mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (acc0 || j > 0) ? 1u : 0u);
+      };
       if (mode == MODE_SEG_STATE) {
         // state only: St += V'(c)^T phi'(K_c) for every chunk of the segment
-        uint32_t st_par = 0;
         for (int c = 0; c < nchunks; ++c) {
-          mwait(B_FULL + st, st_par, 0x210u);
-          mwait(B_PK_READY, c, 0x211u);
+          wait1(B_FULL + c % NS, c / NS, 0x210u);
+          wait1(B_X_READY, c, 0x211u);
           fence_after_sync();
-          const uint64_t dv_c = d_v + st * stage_units, d_pk_c = d_pk + pkb * (40960 >> 4);
-#pragma unroll
-          for (int j = 0; j < C / 16; ++j)
-            mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (c > 0 || j > 0) ? 1u : 0u);
-          mma_commit(bar(B_EMPTY + st));
-          mma_commit(bar(B_PK_FREE + pkb));
-          if (++st == NS) { st = 0; st_par ^= 1u; }
-          if (++pkb == NPK) pkb = 0;
+          issue_update(c, c > 0);
+          mma_commit(bar(B_EMPTY + c % NS));
+          mma_commit(bar(B_PK_FREE + c % NPK));
         }
         mma_commit(bar(B_FIN));
       } else {
-      mwait(B_FULL + 0, 0, 0x200u);
-      fence_after_sync();
-      mma_ss(tmem + TM_S, d_q, d_k, idesc_s, 0);
-      mma_commit(bar(B_S_DONE));
-      for (int c = 0; c < nchunks; ++c) {
-        const uint64_t dv_c = d_v + st * stage_units;
-        // O(c) = P(c) V'(c): needs P(c) written and the previous chunk's O read out
-        mwait(B_P_READY, c, 0x201u);
-        if (c > 0) mwait(B_O_FREE, c - 1, 0x202u);
+        wait1(B_FULL + 0, 0, 0x200u);
         fence_after_sync();
-#pragma unroll
-        for (int j = 0; j < C / 16; ++j)
-          mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
-        // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
-        if (c + 1 < nchunks) {
-          mwait(B_FULL + st1, st1_par, 0x203u);
+        mma_ss(tmem + TM_S, d_q, d_k, idesc_s, 0);
+        mma_commit(bar(B_S_DONE));
+        wait1(B_X_READY, 0, 0x208u);                       // phi'(K_0)
+        if (has_init) wait1(B_INIT, 0, 0x207u);            // state^T and its bf16 copy were preloaded
+        fence_after_sync();
+        issue_update(0, has_init);
+        mma_commit(bar(B_ST_DONE));
+        mma_commit(bar(B_PK_FREE + 0));
+        for (int c = 0; c < nchunks; ++c) {
+          const int st = c % NS;
+          // PV(c): needs P(c) and a free O; the same barrier covers tile c + 1
+          wait1(B_A_READY, c, 0x201u);
           fence_after_sync();
-          const uint32_t so = st1 * stage_units;
-          mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
-          mma_commit(bar(B_S_DONE));
-        }
-        // O(c) += phi'(Q_c) State(c-1) and State^T += V'(c)^T phi'(K_c), issued alternately: the two
-        // accumulation chains are independent, so one fills the other's latency gaps.  The drain that
-        // rewrites the bf16 state waits for the commit below, i.e. for the readout to be complete.
-        mwait(B_PQ_READY, c, 0x204u);
-        if (c > 0) mwait(B_STB_READY, c - 1, 0x205u);
-        else if (has_init) mwait(B_INIT, 0, 0x207u);  // state^T and its bf16 copy were preloaded
-        mwait(B_PK_READY, c, 0x206u);
-        fence_after_sync();
-        {
-          const uint64_t d_pk_c = d_pk + pkb * (40960 >> 4);
+          {
+            const uint64_t dv_c = d_v + st * stage_units;
 #pragma unroll
-          for (int j = 0; j < DR / 16; ++j) {
-            if (c > 0 || has_init)
-              mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb + 256 * j, idesc_o_st, 1);
-            if (j < C / 16)
-              mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (c > 0 || j > 0 || has_init) ? 1u : 0u);
+            for (int j = 0; j < C / 16; ++j)
+              mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
+          }
+          // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
+          if (c + 1 < nchunks) {
+            const uint32_t so = ((c + 1) % NS) * stage_units;
+            mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
+            mma_commit(bar(B_S_DONE));
+          }
+          // R(c): O(c) += phi'(Q_c) State(c-1).  The bf16 state of chunk c-1 sits in buffer (c-1) & 1 and was
+          // awaited before U(c) was issued (see below); a carried-in state was preloaded into buffer 1.
+          wait1(B_X_READY, c + 1, 0x204u);                 // phi'(Q_c) and phi'(K_{c+1})
+          fence_after_sync();
+          if (c > 0 || has_init) {
+            const uint64_t d_stb_c = d_stb + ((c + 1) & 1) * stb_units;
+#pragma unroll
+            for (int j = 0; j < DR / 16; ++j)
+              mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb_c + stb_step * j, idesc_o_st, 1);
+          }
+          mma_commit(bar(B_O_DONE));
+          mma_commit(bar(B_EMPTY + st));
+          // U(c+1): must not start before the drain of State(c) has read the accumulator
+          if (c + 1 < nchunks) {
+            wait1(B_STB_READY, c, 0x205u);
+            fence_after_sync();
+            issue_update(c + 1, true);
+            mma_commit(bar(B_ST_DONE));
+            mma_commit(bar(B_PK_FREE + (c + 1) % NPK));
           }
         }
-        mma_commit(bar(B_O_DONE));
-        mma_commit(bar(B_ST_DONE));
-        mma_commit(bar(B_EMPTY + st));
-        mma_commit(bar(B_PK_FREE + pkb));
-        st = st1;
-        if (++st1 == NS) { st1 = 0; st1_par ^= 1u; }
-        if (++pkb == NPK) pkb = 0;
-      }
       }
     }
   } else if (warp < 4) {
-    // ================================================================ expansion warps: phi'(Q) -> TMEM, phi'(K) -> smem
-    for (int c = 0; c < nchunks; ++c) {
-      const uint8_t* stg = smem + (c % lay.nstage) * lay.stage_bytes + t * 16;   // [k-half][token][16 B]
-      const bool valid = c * C + t < L;
-      wait(B_FULL + c % lay.nstage, c / lay.nstage, 0x300u);
+    // ================================================================ expansion warps: phi'(K) -> smem, phi'(Q) -> TMEM
+    auto load_x = [&](int c, int off, uint32_t (&X)[8]) {
+      const uint8_t* stg = smem + (c % NS) * lay.stage_bytes + off + t * 16;   // [k-half][token][16 B]
+      const uint4 a = *reinterpret_cast<const uint4*>(stg), bq = *reinterpret_cast<const uint4*>(stg + 2048);
+      X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
+    };
+    auto expand_k = [&](int c) {
+      wait(B_FULL + c % NS, c / NS, 0x300u);
       uint32_t X[8];
-      {
-        const uint4 a = *reinterpret_cast<const uint4*>(stg), bq = *reinterpret_cast<const uint4*>(stg + 2048);
-        X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
-      }
-      if (mode != MODE_SEG_STATE) {
-      if (c > 0) wait(B_O_DONE, c - 1, 0x301u);  // the previous phi'(Q) has been consumed
-      fence_after_sync();
-      {
-        uint32_t hold[4];
-        expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
-          constexpr int g = decltype(G)::value;
-          if constexpr ((g & 1) == 0) {
-            hold[0] = w0; hold[1] = w1; hold[2] = w2; hold[3] = w3;
-          } else {
-            const uint32_t r[8] = {hold[0], hold[1], hold[2], hold[3], w0, w1, w2, w3};
-            tmem_st8(tlane + TM_PQ + 4 * (g - 1), r);
-          }
-        });
-      }
-      tmem_st_wait();
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PQ_READY));
-      }
-      {
-        const uint4 a = *reinterpret_cast<const uint4*>(stg + 4096), bq = *reinterpret_cast<const uint4*>(stg + 4096 + 2048);
-        X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
-      }
+      load_x(c, 4096, X);
+      const bool valid = c * C + t < L;
       if (!valid) {  // tokens past the end contribute nothing to the state: phi'(K) = 0, also the constant
 #pragma unroll
         for (int m = 0; m < 8; ++m) X[m] = 0;
       }
       const uint32_t one = valid ? 0xFFFFFFFFu : 0u;
       // the phi'(K) buffer is free once the state update that read it (NPK chunks ago) has completed
-      const int pkb = c % lay.npk;
-      if (c >= lay.npk) wait(B_PK_FREE + pkb, c / lay.npk - 1, 0x302u);
+      const int pkb = c % NPK;
+      if (c >= NPK) wait(B_PK_FREE + pkb, c / NPK - 1, 0x302u);
       uint8_t* dst = smem + lay.phik + pkb * 40960 + t * 16;
       expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
         constexpr int g = decltype(G)::value;
@@ -292,8 +338,42 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
         *reinterpret_cast<uint4*>(dst + g * 2048) = make_uint4(w0, w1, w2, w3);
       });
       fence_proxy_async();
+    };
+    auto expand_q = [&](int c) {
+      wait(B_FULL + c % NS, c / NS, 0x303u);
+      uint32_t X[8];
+      load_x(c, 0, X);
+      if (c > 0) wait(B_O_DONE, c - 1, 0x301u);  // the previous phi'(Q) has been consumed
+      fence_after_sync();
+      uint32_t hold[4];
+      expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+        constexpr int g = decltype(G)::value;
+        if constexpr ((g & 1) == 0) {
+          hold[0] = w0; hold[1] = w1; hold[2] = w2; hold[3] = w3;
+        } else {
+          const uint32_t r[8] = {hold[0], hold[1], hold[2], hold[3], w0, w1, w2, w3};
+          tmem_st8(tlane + TM_PQ + 4 * (g - 1), r);
+        }
+      });
+      tmem_st_wait();
+      fence_before_sync();
+    };
+    if (mode == MODE_SEG_STATE) {
+      for (int c = 0; c < nchunks; ++c) {
+        expand_k(c);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_X_READY));
+      }
+    } else {
+      expand_k(0);
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PK_READY));
+      if (lane == 0) mbar_arrive(bar(B_X_READY));        // phase 0
+      for (int c = 0; c < nchunks; ++c) {
+        if (c + 1 < nchunks) expand_k(c + 1);            // does not depend on the readout: runs ahead
+        expand_q(c);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_X_READY));      // phase c + 1
+      }
     }
   } else if (warp >= W_OUT && warp < W_MMA) {
     // ================================================================ output warps: O -> y
@@ -308,117 +388,76 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       hi.z = pack_bf16(__uint_as_float(r[12]) * sc, __uint_as_float(r[13]) * sc);
       hi.w = pack_bf16(__uint_as_float(r[14]) * sc, __uint_as_float(r[15]) * sc);
     };
-    for (int c = 0; c < (mode == MODE_SEG_STATE ? 0 : nchunks); ++c) {
-      // ---- epilogue: y = O[:, :dv] / (O[:, dv] + eps), 32 columns per round trip ----
-      wait(B_O_DONE, c, 0x401u);
-      fence_after_sync();
-      {
+    if (mode != MODE_SEG_STATE) {
+      if (lane == 0) mbar_arrive(bar(B_A_READY));          // O is free before the first chunk
+      // Each thread parks 32 columns of its normalised row in this warp's 32-row staging tile; the warp then copies
+      // the tile out with every store instruction covering whole 64-byte row segments (row-per-thread stores would
+      // touch 32 different lines per instruction).
+      uint8_t* ytile = smem + lay.ystage + (qd * 32) * lay.yrow_bytes;
+      uint8_t* yrow_s = ytile + lane * lay.yrow_bytes;
+      const int n16 = dv >> 4;
+      for (int c = 0; c < nchunks; ++c) {
+        // ---- epilogue: y = O[:, :dv] / (O[:, dv] + eps), 32 columns per round trip ----
+        wait(B_O_DONE, c, 0x401u);
+        fence_after_sync();
         uint32_t dreg;
         tmem_ld1(tlane + TM_O + dv, dreg);
-        // Each thread parks its normalised row in this warp's 32-row staging tile; the warp then
-        // copies the tile out with every store instruction covering whole 128-byte lines
-        // (row-per-thread stores would touch 32 different lines per instruction).
-        uint8_t* ytile = smem + lay.ystage + (qd * 32) * lay.yrow_bytes;
-        uint8_t* yrow_s = ytile + lane * lay.yrow_bytes;
-        const int n16 = dv >> 4;
+        const int tok_w = c * C + qd * 32;           // first token of this warp's tile
+        __nv_bfloat16* ytok = yb + (int64_t)tok_w * p.sy.l;
         float inv = 0.f;
 #pragma unroll 1
         for (int i0 = 0; i0 < n16; i0 += 2) {
+          const bool two = i0 + 1 < n16;
           uint32_t r0[16], r1[16];
           tmem_ld16(tlane + TM_O + 16 * i0, r0);
-          if (i0 + 1 < n16) tmem_ld16(tlane + TM_O + 16 * (i0 + 1), r1);
+          if (two) tmem_ld16(tlane + TM_O + 16 * (i0 + 1), r1);
           tmem_ld_wait();
+          if (i0 + 2 >= n16) {                       // the last TMEM read of O(c): the next chunk may overwrite it
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_A_READY));
+          }
           if (i0 == 0) inv = 1.0f / (__uint_as_float(dreg) + p.eps);
           uint4 lo, hi;
           cvt16(r0, inv, lo, hi);
-          *reinterpret_cast<uint4*>(yrow_s + 32 * i0) = lo;
-          *reinterpret_cast<uint4*>(yrow_s + 32 * i0 + 16) = hi;
-          if (i0 + 1 < n16) {
+          *reinterpret_cast<uint4*>(yrow_s) = lo;
+          *reinterpret_cast<uint4*>(yrow_s + 16) = hi;
+          if (two) {
             cvt16(r1, inv, lo, hi);
-            *reinterpret_cast<uint4*>(yrow_s + 32 * i0 + 32) = lo;
-            *reinterpret_cast<uint4*>(yrow_s + 32 * i0 + 48) = hi;
+            *reinterpret_cast<uint4*>(yrow_s + 32) = lo;
+            *reinterpret_cast<uint4*>(yrow_s + 48) = hi;
           }
-        }
-        fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_O_FREE));  // O has been read; the next chunk may overwrite it
-        const int cpr = dv >> 3;                     // 16-byte pieces per row
-        const int tok_w = c * C + qd * 32;           // first token of this warp's tile
-        __nv_bfloat16* ytok = yb + (int64_t)tok_w * p.sy.l;
-        // piece idx = lane + 32 n -> (row idx / cpr, piece idx % cpr), advanced incrementally;
-        // four loads are issued before their four stores so their latencies overlap
-        {
-          const int dq = 32 / cpr, dr = 32 % cpr;
-          int r = lane / cpr, cc = lane - r * cpr;
-          const int total = cpr;  // 32 * cpr pieces / 32 lanes
-          for (int n0 = 0; n0 < total; n0 += 4) {
-            uint4 val[4];
-            int rr[4], cq[4];
+          __syncwarp();
+          // 16-byte pieces of the tile: ppr per row; piece idx = lane + 32 n -> row idx / ppr, piece idx % ppr
+          const int ppr = two ? 4 : 2, sh = two ? 2 : 1;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              rr[u] = r; cq[u] = cc;
-              if (n0 + u < total) val[u] = *reinterpret_cast<const uint4*>(ytile + r * lay.yrow_bytes + cc * 16);
-              r += dq; cc += dr;
-              if (cc >= cpr) { cc -= cpr; ++r; }
+          for (int n = 0; n < 4; ++n) {
+            if (n < ppr) {
+              const int idx = lane + 32 * n, r = idx >> sh, cc = idx & (ppr - 1);
+              const uint4 val = *reinterpret_cast<const uint4*>(ytile + r * lay.yrow_bytes + cc * 16);
+              if (tok_w + r < L) *reinterpret_cast<uint4*>(ytok + (int64_t)r * p.sy.l + 16 * i0 + cc * 8) = val;
             }
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (n0 + u < total && tok_w + rr[u] < L)
-                *reinterpret_cast<uint4*>(ytok + (int64_t)rr[u] * p.sy.l + cq[u] * 8) = val[u];
           }
+          __syncwarp();  // the tile is rewritten in the next round
         }
-        __syncwarp();  // the tile is rewritten by other lanes in the next chunk
       }
     }
   } else {
-    // ================================================================ polynomial / state-drain warps
-    // P(c) = causal(1 + s/4 + s^2/32), evaluated in bf16x2 (two FMAs per pair), in place over S.
-    // Column pieces right of this warp's diagonal block are all masked: zeros, no load; only the
-    // diagonal piece needs the per-element mask.
-    auto make_p = [&](int c) {
-      wait(B_S_DONE, c, 0x400u);
-      fence_after_sync();
-      constexpr uint32_t k1 = 0x3F803F80u, kq = 0x3E803E80u, k32 = 0x3D003D00u;  // (1,1) (1/4,1/4) (1/32,1/32)
-#pragma unroll 1
-      for (int piece = 0; piece <= qd; ++piece) {
-        uint32_t sreg[32], pk[16];
-        tmem_ld32(tlane + TM_S + piece * 32, sreg);
-        tmem_ld_wait();
-        const int rel = t - piece * 32;  // columns 0..rel of this piece are visible (rel >= 31 left of the diagonal)
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
-          const uint32_t pv = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
-          const uint32_t mask = (2 * i + 1 <= rel) ? 0xFFFFFFFFu : ((2 * i <= rel) ? 0x0000FFFFu : 0u);
-          pk[i] = pv & mask;
-        }
-        tmem_st16(tlane + TM_S + piece * 16, pk);
-      }
-      {
-        uint32_t z[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) z[i] = 0;
-#pragma unroll 1
-        for (int piece = qd + 1; piece < 4; ++piece) tmem_st16(tlane + TM_S + piece * 16, z);
-      }
-      tmem_st_wait();
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_P_READY));
+    // ================================================================ state-drain warps (4-7); warp 4 also evaluates
+    // the polynomial of quadrant 0 (its rows see one 32-column piece), warp 7 half of quadrant 3's when it has no
+    // state rows to drain
+    auto cvt16 = [&](const uint32_t (&r)[16], uint4& lo, uint4& hi) {
+      lo.x = pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1]));
+      lo.y = pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3]));
+      lo.z = pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5]));
+      lo.w = pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7]));
+      hi.x = pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9]));
+      hi.y = pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11]));
+      hi.z = pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13]));
+      hi.w = pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15]));
     };
-    auto cvt16 = [&](const uint32_t (&r)[16], float sc, uint4& lo, uint4& hi) {
-      lo.x = pack_bf16(__uint_as_float(r[0]) * sc, __uint_as_float(r[1]) * sc);
-      lo.y = pack_bf16(__uint_as_float(r[2]) * sc, __uint_as_float(r[3]) * sc);
-      lo.z = pack_bf16(__uint_as_float(r[4]) * sc, __uint_as_float(r[5]) * sc);
-      lo.w = pack_bf16(__uint_as_float(r[6]) * sc, __uint_as_float(r[7]) * sc);
-      hi.x = pack_bf16(__uint_as_float(r[8]) * sc, __uint_as_float(r[9]) * sc);
-      hi.y = pack_bf16(__uint_as_float(r[10]) * sc, __uint_as_float(r[11]) * sc);
-      hi.z = pack_bf16(__uint_as_float(r[12]) * sc, __uint_as_float(r[13]) * sc);
-      hi.w = pack_bf16(__uint_as_float(r[14]) * sc, __uint_as_float(r[15]) * sc);
-    };
-    // final fp32 state^T -> shared memory at offset 0 (every MMA and every other warp's use of
-    // shared memory is over by then).  The TMEM loads are warp-collective, so every lane issues
-    // them; only rows < NV are kept.
+    // final fp32 state^T -> shared memory at offset 0 (every MMA and every other warp's use of the stages is
+    // over by then).  The TMEM loads are warp-collective, so every lane issues them; only rows < NV are kept.
     auto stage_state = [&]() {
       float* stg = reinterpret_cast<float*>(smem) + t * STAGE_STRIDE_F;
 #pragma unroll 1
@@ -433,71 +472,88 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
         }
       }
     };
+    // bf16 copy of 32 feature columns of this thread's state row into operand buffer `buf`
+    auto store_stb = [&](int buf, int i, const uint32_t (&r0)[16], const uint32_t (&r1)[16]) {
+      uint4 a0, a1, b0, b1;
+      cvt16(r0, a0, a1);
+      cvt16(r1, b0, b1);
+      if (t < NV) {  // rows >= NV of the B operand do not exist (N = NV)
+        uint8_t* dst = smem + lay.stb + buf * lay.stb_bytes + (4 * i) * (NV * 16) + t * 16;
+        *reinterpret_cast<uint4*>(dst) = a0;
+        *reinterpret_cast<uint4*>(dst + NV * 16) = a1;
+        *reinterpret_cast<uint4*>(dst + 2 * NV * 16) = b0;
+        *reinterpret_cast<uint4*>(dst + 3 * NV * 16) = b1;
+      }
+    };
+    const bool my_rows = qd * 32 < NV;                       // warp-uniform: this quadrant holds state rows
+    // polynomial pieces [0, pp1) of this warp: all of quadrant 0 (one piece to evaluate, three to clear), the first
+    // two of quadrant 3 when warp 15 shares it
+    const int pp1 = qd == 0 ? 4 : ((qd == 3 && !q3_has_state) ? 2 : 0);
     if (mode == MODE_SEG_STATE) {
       wait(B_FIN, 0, 0x410u);
       fence_after_sync();
       stage_state();
     } else {
-    make_p(0);
-    if (has_init) {
-      // Preload state^T (fp32, TMEM) and its bf16 operand copy with the sum over the earlier segments.
-      const float* src = p.seg_state + ((size_t)bh * (p.nseg - 1) + (seg - 1)) * (size_t)((dv + 1) * DR) + (size_t)t * DR;
-      const bool row = t <= dv;
+      if (pp1 > 0) make_p(0, 0, pp1);
+      if (has_init) {
+        // Preload state^T (fp32, TMEM) and its bf16 operand copy (buffer 1) with the sum over the earlier segments.
+        const float* src = p.seg_state + ((size_t)bh * (p.nseg - 1) + (seg - 1)) * (size_t)((dv + 1) * DR) + (size_t)t * DR;
+        const bool row = t <= dv;
 #pragma unroll 1
-      for (int i = 0; i < 10; ++i) {
-        uint32_t r[16];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint4 x = row ? __ldg(reinterpret_cast<const uint4*>(src + 16 * i + 4 * e)) : make_uint4(0, 0, 0, 0);
-          r[4 * e] = x.x; r[4 * e + 1] = x.y; r[4 * e + 2] = x.z; r[4 * e + 3] = x.w;
-        }
-        tmem_st16(tlane + TM_ST + 16 * i, r);
-        if (t < NV) {
-          uint4 a0, a1;
-          cvt16(r, 1.0f, a0, a1);
-          uint8_t* dst = smem + lay.stb + (2 * i) * 2048 + t * 16;
-          *reinterpret_cast<uint4*>(dst) = a0;
-          *reinterpret_cast<uint4*>(dst + 2048) = a1;
-        }
-      }
-      tmem_st_wait();
-      fence_proxy_async();
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_INIT));
-    }
-    for (int c = 0; c < nchunks; ++c) {
-      const bool last = c + 1 == nchunks;
-      if (!last) make_p(c + 1);
-      // ---- state: fp32 TMEM -> bf16 smem operand for the next chunk, or fp32 staging at the end ----
-      wait(B_ST_DONE, c, 0x402u);
-      fence_after_sync();
-      if (!last) {
-#pragma unroll 1
-        for (int i = 0; i < (qd * 32 < NV ? 5 : 0); ++i) {  // 32 feature columns per round trip; warp-uniform skip of a quadrant without state rows
+        for (int i = 0; i < 5; ++i) {
           uint32_t r0[16], r1[16];
-          tmem_ld16(tlane + TM_ST + 32 * i, r0);
-          tmem_ld16(tlane + TM_ST + 32 * i + 16, r1);
-          tmem_ld_wait();
-          uint4 a0, a1, b0, b1;
-          cvt16(r0, 1.0f, a0, a1);
-          cvt16(r1, 1.0f, b0, b1);
-          if (t < NV) {  // rows >= NV of the B operand are never read (N = NV)
-            uint8_t* dst = smem + lay.stb + (4 * i) * 2048 + t * 16;
-            *reinterpret_cast<uint4*>(dst) = a0;
-            *reinterpret_cast<uint4*>(dst + 2048) = a1;
-            *reinterpret_cast<uint4*>(dst + 4096) = b0;
-            *reinterpret_cast<uint4*>(dst + 6144) = b1;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint4 x = row ? __ldg(reinterpret_cast<const uint4*>(src + 32 * i + 4 * e)) : make_uint4(0, 0, 0, 0);
+            const uint4 y2 = row ? __ldg(reinterpret_cast<const uint4*>(src + 32 * i + 16 + 4 * e)) : make_uint4(0, 0, 0, 0);
+            r0[4 * e] = x.x; r0[4 * e + 1] = x.y; r0[4 * e + 2] = x.z; r0[4 * e + 3] = x.w;
+            r1[4 * e] = y2.x; r1[4 * e + 1] = y2.y; r1[4 * e + 2] = y2.z; r1[4 * e + 3] = y2.w;
           }
+          tmem_st16(tlane + TM_ST + 32 * i, r0);
+          tmem_st16(tlane + TM_ST + 32 * i + 16, r1);
+          store_stb(1, i, r0, r1);
         }
+        tmem_st_wait();
         fence_proxy_async();
         fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_STB_READY));
-      } else if (write_state) {
-        stage_state();
+        if (lane == 0) mbar_arrive(bar(B_INIT));
       }
-    }
+      for (int c = 0; c < nchunks; ++c) {
+        const bool last = c + 1 == nchunks;
+        // ---- state after chunk c: fp32 TMEM -> bf16 smem operand (buffer c & 1), or fp32 staging at the end ----
+        wait(B_ST_DONE, c, 0x402u);
+        fence_after_sync();
+        if (!last) {
+          if (my_rows) {
+            // 32 feature columns per round trip, the next round's loads in flight while this one is converted
+            uint32_t ra[16], rb[16], rc[16], rd[16];
+            tmem_ld16(tlane + TM_ST, ra);
+            tmem_ld16(tlane + TM_ST + 16, rb);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 5; ++i) {
+              if (i & 1) {
+                if (i < 4) { tmem_ld16(tlane + TM_ST + 32 * (i + 1), ra); tmem_ld16(tlane + TM_ST + 32 * (i + 1) + 16, rb); }
+                store_stb(c & 1, i, rc, rd);
+              } else {
+                if (i < 4) { tmem_ld16(tlane + TM_ST + 32 * (i + 1), rc); tmem_ld16(tlane + TM_ST + 32 * (i + 1) + 16, rd); }
+                store_stb(c & 1, i, ra, rb);
+              }
+              if (i < 4) tmem_ld_wait();
+            }
+          }
+          fence_proxy_async();
+          fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_STB_READY));
+          if (pp1 > 0) make_p(c + 1, 0, pp1);
+        } else if (write_state) {
+          wait(B_O_DONE, c, 0x404u);   // the last chunk's P V' and readout still read the stages and the operand buffers
+          fence_after_sync();
+          stage_state();
+        }
+      }
     }
   }
 

@@ -494,3 +494,73 @@ def rotary_qkv_cache_(qkv: torch.Tensor, rotary_cos: torch.Tensor, rotary_sin: t
             kv_cache.data_ptr(), _capi.strides(*kv_cache.stride()[:2]), _stream())
     _capi.check(code, "based_rotary_qkv_cache")
     return qkv
+
+
+def tp_outproj_workspace_bytes(world: int, max_rows: int, n_out: int) -> int:
+    """Size of one rank's receive workspace for :func:`tp_outproj_allreduce`."""
+    n = _capi.lib().based_tp_outproj_workspace_bytes(int(world), int(max_rows), int(n_out))
+    if n == 0:
+        raise ValueError("tp_outproj: world must be 1..8, max_rows >= 1 and n_out a multiple of 8")
+    return n
+
+
+def tp_outproj_workspace_init_(ws: torch.Tensor) -> torch.Tensor:
+    """Prepare a workspace (zero flags, call counter = 1).  Once, by its owner, before any rank's first call."""
+    _need_cuda(ws)
+    with torch.cuda.device(ws.device):
+        _capi.check(_capi.lib().based_tp_outproj_workspace_init(ws.data_ptr(), ws.numel() * ws.element_size(), _stream()),
+                    "based_tp_outproj_workspace_init")
+    return ws
+
+
+def tp_outproj_allreduce(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], workspace_ptrs, max_rows: int,
+                         rank: int, world: int, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-parallel ``x W^T`` summed over the tensor-parallel ranks (+ bias), one kernel per rank
+    (based/ops/fused_dense.py:239-246 as GEMM + all-reduce in one launch).  ``x [..., K_local]`` bf16 with at most
+    ``max_rows`` rows, ``weight [N, K_local]`` bf16 contiguous; ``workspace_ptrs`` the device addresses of every rank's
+    workspace as mapped in this process.  A collective: every rank calls it with the same shapes."""
+    _need_cuda(x, weight, bias)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise TypeError("tp_outproj_allreduce takes bfloat16 activations and weights")
+    K = x.shape[-1]
+    x2 = x.reshape(-1, K)
+    _inner_contig(x2, "x")
+    M, N = x2.shape[0], weight.shape[0]
+    if weight.shape[1] != K or not weight.is_contiguous():
+        raise ValueError("weight must be a contiguous [N, K] tensor")
+    if not 0 < M <= max_rows:
+        raise ValueError(f"tp_outproj_allreduce: {M} rows, workspace built for at most {max_rows}")
+    if len(workspace_ptrs) != world:
+        raise ValueError("one workspace address per rank is needed")
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    o2 = out.reshape(-1, N)
+    with torch.cuda.device(x.device):
+        code = _capi.lib().based_tp_outproj_allreduce(
+            x2.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, o2.data_ptr(), M, N, K,
+            x2.stride(0), o2.stride(0), _capi.pointers(workspace_ptrs), int(max_rows), int(rank), int(world), _stream())
+    _capi.check(code, "based_tp_outproj_allreduce")
+    return out.reshape(*x.shape[:-1], N)
+
+
+def tp_outproj_allreduce_emulated(xs, weights, bias, workspaces, max_rows: int):
+    """All ranks of :func:`tp_outproj_allreduce` inside one cooperative launch on one GPU: ``xs[r] [M, K]``,
+    ``weights[r] [N, K]``, ``workspaces[r]`` (prepared uint8 tensors), all on the same device.  Returns the list of the
+    ranks' outputs.  For checking the exchange protocol with a single GPU."""
+    world = len(xs)
+    _need_cuda(*xs, *weights, bias, *workspaces)
+    M, K = xs[0].shape
+    N = weights[0].shape[0]
+    outs = [torch.empty(M, N, dtype=torch.bfloat16, device=xs[0].device) for _ in range(world)]
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    with torch.cuda.device(xs[0].device):
+        code = _capi.lib().based_tp_outproj_allreduce_emulated(
+            _capi.pointers([t.data_ptr() for t in xs]), _capi.pointers([t.data_ptr() for t in weights]),
+            bias.data_ptr() if bias is not None else None, _capi.pointers([t.data_ptr() for t in outs]), M, N, K,
+            xs[0].stride(0), outs[0].stride(0), _capi.pointers([t.data_ptr() for t in workspaces]), int(max_rows), world,
+            _stream())
+    _capi.check(code, "based_tp_outproj_allreduce_emulated")
+    return outs

@@ -84,3 +84,45 @@ def all_reduce_sum_(t: torch.Tensor, group=None) -> torch.Tensor:
     if group is not None and dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
     return t
+
+
+# --------------------------------------------------------------------------- fused out_proj + all-reduce (decode steps)
+class PeerWorkspace:
+    """One device buffer per rank of a process group, each mapped into every rank's address space, so that a kernel
+    can store into its peers' buffers over NVLink.  The mapping is torch's: symmetric memory
+    (``torch.distributed._symmetric_memory``) — allocation, handle exchange through the group's store and mapping are
+    its job; this class only keeps the tensor alive and hands out the addresses.  Creating one is a collective."""
+
+    def __init__(self, nbytes: int, group, device):
+        import os
+
+        import torch.distributed._symmetric_memory as symm
+        # the kernels here use plain peer loads / stores only: no NVLink multicast object needs to be bound
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.tensor = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.tensor, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.ptrs) != self.world or self.ptrs[self.rank] != self.tensor.data_ptr():
+            raise RuntimeError("symmetric memory returned an unexpected address table")
+
+
+class FusedRowParallel:
+    """Decode-step ``all_reduce(x W^T)`` of a row-parallel projection as ONE kernel per rank
+    (:func:`based_b200.ops.tp_outproj_allreduce`).  Built lazily by the mixers on their first decode step; the set-up is
+    a collective (every rank of the group must reach it), and so is every call."""
+
+    def __init__(self, n_out: int, max_rows: int, group, device):
+        from . import ops
+        self.max_rows, self.n_out = int(max_rows), int(n_out)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.ws = PeerWorkspace(ops.tp_outproj_workspace_bytes(self.world, self.max_rows, self.n_out), group, device)
+        ops.tp_outproj_workspace_init_(self.ws.tensor)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)            # nobody pushes into a workspace that its owner is still clearing
+
+    def __call__(self, x, weight, bias=None):
+        from . import ops
+        return ops.tp_outproj_allreduce(x, weight, bias, self.ws.ptrs, self.max_rows, self.rank, self.world)

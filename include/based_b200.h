@@ -123,21 +123,24 @@ int based_linattn_prefill_split(const void* q, const void* k, const void* v, voi
 /*
  * based_linattn_prefill_split without a workspace argument and without any allocation: the
  * per-segment states live in an array built into the library, BASED_STATIC_SCRATCH_BYTES
- * (8 MiB) of device memory per GPU, reserved when the library's module is loaded.  No
- * counterpart in the reference; it serves callers that must not allocate, e.g. inside a
- * captured stream or a serving loop with a fixed memory plan.
+ * (8 MiB) of device memory on every GPU that loads the library, held until the process exits.
+ * No counterpart in the reference.  It is for callers that cannot call cudaMalloc (or an
+ * allocating library routine) where they run: a serving loop whose memory plan is fixed at
+ * start-up, a callback that runs while the framework's allocator is locked, a real-time path
+ * that may not take the driver's allocation lock.
  *
  *  - Arguments and results are those of based_linattn_prefill_split (bit-identical outputs).
  *  - A call whose based_linattn_prefill_scratch_bytes(B, H, L, dv, nseg) exceeds
  *    BASED_STATIC_SCRATCH_BYTES returns BASED_ERR_TOO_LARGE before any launch.
  *  - Nothing in the array has to start at zero and no call leaves state behind in it: every
  *    word a call reads, it has written first.
- *  - The first call on each device looks up the array's address (cudaGetSymbolAddress, return
- *    code checked) and keeps it; make that first call before any stream capture begins.  Later
- *    calls only launch kernels and may be captured.
+ *  - The first call on each device, with that device current, looks up the array's device
+ *    address (cudaGetSymbolAddress, return code checked) and the kernel's launch attributes and
+ *    keeps them; make that first call before any stream capture begins.  The address belongs
+ *    to the device's primary context: it is not valid across a cudaDeviceReset.
  *  - All calls on one device share the one array: two calls that can run at the same time
- *    (different streams, or graphs replayed concurrently) race on it.  Order them on one stream,
- *    or give the overlapping ones their own workspace through based_linattn_prefill_split.
+ *    (different streams) race on it.  Order them on one stream, or give the overlapping ones
+ *    their own workspace through based_linattn_prefill_split.
  */
 #define BASED_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
 int based_linattn_prefill_split_static(const void* q, const void* k, const void* v, void* y,
@@ -354,6 +357,47 @@ int based_decode_linear(const void* x, const void* w, const void* bias, void* ou
                         int epilogue, int act,
                         void* conv_state, const void* conv_weight, const void* conv_bias,
                         int conv_k, int conv_w_dtype, void* stream);
+
+/*
+ * Tensor-parallel decode step: row-parallel output projection fused with the all-reduce that follows it.
+ *
+ *   out[M, N] = sum over ranks r of x_r[M, K] W_r[N, K]^T (+ bias)        bf16 in / out, fp32 partials and sum
+ *
+ * Modelled on RowParallelLinear.forward (based/ops/fused_dense.py:239-246: local GEMM, then all_reduce of the
+ * [B, L, d_model] output), the layer the head-sharded variant of LinearAttention / SlidingAttention ends with
+ * (out_proj, based/models/mixers/linear_attention.py:252, slide_attention.py:599).  The reference's mixers have no
+ * tensor parallelism; the unfused form here is a cuBLAS GEMM followed by ncclAllReduce.  One kernel per rank:
+ * the rank's partial tile is pushed into EVERY rank's receive workspace with plain stores to peer memory (NVLink),
+ * a per-tile flag follows, each rank then waits (bounded, ~1 s, reported through based_read_status; the affected
+ * outputs become NaN) for the same tile of every rank and adds the partials in rank order, so all ranks hold
+ * bit-identical results.  Built for decode sizes (M <= max_rows <= a few hundred single-token rows), where the
+ * collective is latency-bound; prompt-size outputs stay on NCCL.
+ *
+ *   workspaces[world]  device pointers to every rank's workspace AS MAPPED IN THIS PROCESS (peer mappings from
+ *                      CUDA IPC or a symmetric-memory allocator); entry `rank` is this rank's own.  Each is
+ *                      based_tp_outproj_workspace_bytes(world, max_rows, N) bytes, 256-byte aligned, prepared ONCE with
+ *                      based_tp_outproj_workspace_init (on its owner, before any rank's first call), and must not be
+ *                      used by two calls that overlap in time.  The call counter lives in the workspace and is
+ *                      advanced by the kernel, so a captured launch can be replayed.
+ *   max_rows           fixes the tile count and the workspace layout: the same value on every rank and every call.
+ *   N a multiple of 8, K a multiple of 32, x and W 16-byte aligned, x_row_stride a multiple of 8, out_row_stride
+ *   even; world <= 8.  Every rank must make the call (same M, N) at about the same time, like any collective.
+ *   Returns BASED_ERR_TOO_LARGE when the launch could not be fully resident (its blocks wait for their
+ *   counterparts on the other ranks).
+ */
+size_t based_tp_outproj_workspace_bytes(int world, int max_rows, int N);
+int based_tp_outproj_workspace_init(void* workspace, size_t bytes, void* stream);
+int based_tp_outproj_allreduce(const void* x, const void* w, const void* bias, void* out,
+                               int M, int N, int K, int64_t x_row_stride, int64_t out_row_stride,
+                               void* const* workspaces, int max_rows, int rank, int world, void* stream);
+/*
+ * The same kernel with all `world` ranks inside ONE cooperative launch on one GPU (x, w, out: one pointer per rank;
+ * workspaces: all local).  For checking the exchange protocol where fewer GPUs than ranks are at hand; two separate
+ * launches that wait on one another must never share a GPU.  No counterpart in the reference.
+ */
+int based_tp_outproj_allreduce_emulated(const void* const* x, const void* const* w, const void* bias, void* const* out,
+                                        int M, int N, int K, int64_t x_row_stride, int64_t out_row_stride,
+                                        void* const* workspaces, int max_rows, int world, void* stream);
 
 #ifdef __cplusplus
 }
