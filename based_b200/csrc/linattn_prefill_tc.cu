@@ -70,14 +70,18 @@ constexpr uint32_t TM_PQ = 416;   // phi'(Q) bf16, 80 columns
 constexpr uint32_t TM_COLS = 512;
 
 // mbarrier slots (8 bytes each) from Smem::bar
-//   B_FULL / B_EMPTY   per stage: tile landed (TMA transaction bytes) / the MMAs that read it have completed
+//   B_FULL / B_EMPTY   per stage: tile landed (TMA transaction bytes) / the MMAs that read it have completed (B_EMPTY
+//                      only in the state-only mode; otherwise a stage is free when B_O_DONE of its chunk completes)
 //   B_S_DONE           S(c) = Q K^T complete                                   (tcgen05.commit)
 //   B_A_READY          P(c) written AND O free (O(c-1) read out) AND tile c+1 landed   (poly warps + output warps)
 //   B_X_READY          phase 0: phi'(K_0) written; phase c+1: phi'(Q_c) and phi'(K_{c+1}) written   (expansion warps)
 //   B_O_DONE           readout of chunk c complete: O(c) final, phi'(Q_c) consumed   (commit)
-//   B_ST_DONE          state update of chunk c complete                              (commit)
+//   B_ST_DONE          state update of chunk c complete: the accumulator may be drained              (commit)
+//   B_PK_FREE[2]       the update that read this phi'(K) buffer has completed.  A parity wait can only tell the
+//                      current phase from the one before, so a waiter two chunks behind B_ST_DONE could not use
+//                      that barrier; these advance once per use of their buffer.  Arrived on by a drain warp that
+//                      has just seen B_ST_DONE (by a commit in the state-only mode, which has no drain per chunk).
 //   B_STB_READY        bf16 copy of the state after chunk c written (drain warps)
-//   B_PK_FREE[2]       the update that read this phi'(K) buffer has completed        (commit)
 //   B_INIT             carried-in state preloaded (sequence split)      B_FIN   last update complete (state-only mode)
 enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_A_READY, B_X_READY, B_O_DONE, B_ST_DONE, B_STB_READY, B_PK_FREE,
            B_PK_FREE1, B_INIT, B_FIN, B_COUNT };
@@ -119,6 +123,9 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   auto wait1 = [&](int i, uint32_t parity, unsigned int code) {   // by one lane of a diverged warp
     mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
   };
+  auto spin1 = [&](int i, uint32_t parity, unsigned int code) {   // the MMA thread: polls, never suspends
+    mbar_spin_bounded(bar(i), parity & 1u, abort_flag, p.status, code);
+  };
 
   // ------------------------------------------------------------------ set-up
   if (tid == 0) {
@@ -157,9 +164,8 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   // put the group index outside the token index).  Tokens past the end of the sequence are zero-filled by the
   // copy unit.  Chunk j goes to stage j % NS once the MMAs that read chunk j - NS have completed.
   const bool need_q = mode != MODE_SEG_STATE;
-  auto issue_tile = [&](int j) {
+  auto issue_tile = [&](int j) {   // the caller knows that stage j % NS is free
     const int st = j % NS;
-    if (j >= NS) wait1(B_EMPTY + st, j / NS - 1, 0x100u);
     const uint32_t base = sb + st * lay.stage_bytes;
     const int tok = tok_base + j * C;
     tma::mbar_expect_tx(bar(B_FULL + st), (need_q ? 8192u : 4096u) + (uint32_t)dv * 256u);
@@ -170,7 +176,12 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
 
   // P(c) = causal(1 + s/4 + s^2/32), evaluated in bf16x2 (two FMAs per pair), in place over S, for the 32-column
   // pieces [p0, p1) of this warp's 32 rows; pieces right of the diagonal block (> qd) are zeros, no load.
-  auto poly_pieces = [&](int p0, int p1) {
+  // P is half as wide as S: piece k of P lands on S columns [16k, 16k + 16), i.e. inside S piece k / 2.  One warp
+  // going through its pieces in ascending order never overwrites what it has not read.  When two warps share a
+  // quadrant (pieces [0, 2) and [2, 4)), the second one's first store lands inside S piece 1, which belongs to
+  // the first warp: the first warp arrives on a named barrier once it has piece 1 in registers (share == 1), the
+  // second waits there before its first store (share == 2).
+  auto poly_pieces = [&](int p0, int p1, int share) {
     constexpr uint32_t k1 = 0x3F803F80u, kq = 0x3E803E80u, k32 = 0x3D003D00u;  // (1,1) (1/4,1/4) (1/32,1/32)
 #pragma unroll 1
     for (int piece = p0; piece < p1; ++piece) {
@@ -178,14 +189,23 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
         uint32_t sreg[32], pk[16];
         tmem_ld32(tlane + TM_S + piece * 32, sreg);
         tmem_ld_wait();
-        const int rel = t - piece * 32;  // columns 0..rel of this piece are visible (rel >= 31 left of the diagonal)
+        if (share == 1 && piece == 1) asm volatile("bar.arrive 1, 64;\n" ::: "memory");
+        if (piece < qd) {   // left of the diagonal block: every column is visible
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
-          const uint32_t pv = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
-          const uint32_t mask = (2 * i + 1 <= rel) ? 0xFFFFFFFFu : ((2 * i <= rel) ? 0x0000FFFFu : 0u);
-          pk[i] = pv & mask;
+          for (int i = 0; i < 16; ++i) {
+            const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+            pk[i] = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
+          }
+        } else {            // the diagonal block: columns 0..lane of this piece are visible
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+            const uint32_t pv = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
+            const uint32_t mask = (2 * i + 1 <= lane) ? 0xFFFFFFFFu : ((2 * i <= lane) ? 0x0000FFFFu : 0u);
+            pk[i] = pv & mask;
+          }
         }
+        if (share == 2 && piece == p0) asm volatile("bar.sync 1, 64;\n" ::: "memory");
         tmem_st16(tlane + TM_S + piece * 16, pk);
       } else {
         uint32_t z[16];
@@ -195,37 +215,36 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       }
     }
   };
-  // the polynomial of chunk c by this warp (pieces [p0, p1)), then one arrival on B_A_READY - which also vouches for
-  // tile c + 1 having landed, so the MMA thread need not test that barrier itself
-  auto make_p = [&](int c, int p0, int p1) {
+  // the polynomial of chunk c by this warp (pieces [p0, p1)), then one arrival on B_A_READY - which, with three
+  // stages, also vouches for tile c + 1 having landed (it was requested two chunks earlier), so the MMA thread need
+  // not test that barrier itself; with two stages the tile is younger and the MMA thread waits for it where it
+  // needs it
+  const bool full_via_a = NS >= 3;
+  auto make_p = [&](int c, int p0, int p1, int share) {
     wait(B_S_DONE, c, 0x400u);
     fence_after_sync();
-    poly_pieces(p0, p1);
+    poly_pieces(p0, p1, share);
     tmem_st_wait();
     fence_before_sync();
-    if (c + 1 < nchunks) wait(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x403u);
+    if (full_via_a && c + 1 < nchunks) wait(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x403u);
     __syncwarp();
     if (lane == 0) mbar_arrive(bar(B_A_READY));
   };
 
   if (warp >= W_LOAD) {
-    // ================================================================ polynomial warps of quadrants 1-3; warp 13's
-    // lane 0 is also the TMA producer
+    // ================================================================ polynomial warps of quadrants 1-3
     if (mode == MODE_SEG_STATE) {
+      // state-only mode: warp 13's lane 0 is the TMA producer
       if (warp == W_LOAD && lane == 0)
-        for (int j = 0; j < nchunks; ++j) issue_tile(j);
+        for (int j = 0; j < nchunks; ++j) {
+          if (j >= NS) wait1(B_EMPTY + j % NS, j / NS - 1, 0x100u);
+          issue_tile(j);
+        }
     } else {
-      if (warp == W_LOAD && lane == 0)
-        for (int j = 0; j < min(NS, nchunks); ++j) issue_tile(j);
-      __syncwarp();
       // quadrant 3 is shared with warp 7 when that warp has no state rows to drain
-      const int p0 = (qd == 3 && !q3_has_state) ? 2 : 0;
-      for (int c = 0; c < nchunks; ++c) {
-        make_p(c, p0, 4);
-        // tile c + NS - 1 replaces tile c - 1, whose last reader was the readout of chunk c - 1
-        if (warp == W_LOAD && lane == 0 && c >= 1 && c + NS - 1 < nchunks) issue_tile(c + NS - 1);
-        __syncwarp();
-      }
+      const bool shared_q3 = qd == 3 && !q3_has_state;
+      const int p0 = shared_q3 ? 2 : 0;
+      for (int c = 0; c < nchunks; ++c) make_p(c, p0, 4, shared_q3 ? 2 : 0);
     }
   } else if (warp == W_MMA) {
     // ================================================================ MMA issue: one thread runs the whole loop
@@ -252,8 +271,8 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       if (mode == MODE_SEG_STATE) {
         // state only: St += V'(c)^T phi'(K_c) for every chunk of the segment
         for (int c = 0; c < nchunks; ++c) {
-          wait1(B_FULL + c % NS, c / NS, 0x210u);
-          wait1(B_X_READY, c, 0x211u);
+          spin1(B_FULL + c % NS, c / NS, 0x210u);
+          spin1(B_X_READY, c, 0x211u);
           fence_after_sync();
           issue_update(c, c > 0);
           mma_commit(bar(B_EMPTY + c % NS));
@@ -261,20 +280,19 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
         }
         mma_commit(bar(B_FIN));
       } else {
-        wait1(B_FULL + 0, 0, 0x200u);
+        spin1(B_FULL + 0, 0, 0x200u);
         fence_after_sync();
         mma_ss(tmem + TM_S, d_q, d_k, idesc_s, 0);
         mma_commit(bar(B_S_DONE));
-        wait1(B_X_READY, 0, 0x208u);                       // phi'(K_0)
-        if (has_init) wait1(B_INIT, 0, 0x207u);            // state^T and its bf16 copy were preloaded
+        spin1(B_X_READY, 0, 0x208u);                       // phi'(K_0)
+        if (has_init) spin1(B_INIT, 0, 0x207u);            // state^T and its bf16 copy were preloaded
         fence_after_sync();
         issue_update(0, has_init);
         mma_commit(bar(B_ST_DONE));
-        mma_commit(bar(B_PK_FREE + 0));
         for (int c = 0; c < nchunks; ++c) {
           const int st = c % NS;
           // PV(c): needs P(c) and a free O; the same barrier covers tile c + 1
-          wait1(B_A_READY, c, 0x201u);
+          spin1(B_A_READY, c, 0x201u);
           fence_after_sync();
           {
             const uint64_t dv_c = d_v + st * stage_units;
@@ -284,13 +302,17 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
           }
           // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
           if (c + 1 < nchunks) {
+            if (!full_via_a) {
+              spin1(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x203u);
+              fence_after_sync();
+            }
             const uint32_t so = ((c + 1) % NS) * stage_units;
             mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
             mma_commit(bar(B_S_DONE));
           }
           // R(c): O(c) += phi'(Q_c) State(c-1).  The bf16 state of chunk c-1 sits in buffer (c-1) & 1 and was
           // awaited before U(c) was issued (see below); a carried-in state was preloaded into buffer 1.
-          wait1(B_X_READY, c + 1, 0x204u);                 // phi'(Q_c) and phi'(K_{c+1})
+          spin1(B_X_READY, c + 1, 0x204u);                 // phi'(Q_c) and phi'(K_{c+1})
           fence_after_sync();
           if (c > 0 || has_init) {
             const uint64_t d_stb_c = d_stb + ((c + 1) & 1) * stb_units;
@@ -298,17 +320,16 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
             for (int j = 0; j < DR / 16; ++j)
               mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb_c + stb_step * j, idesc_o_st, 1);
           }
-          mma_commit(bar(B_O_DONE));
-          mma_commit(bar(B_EMPTY + st));
+          mma_commit(bar(B_O_DONE));                       // also: stage c % NS is free
           // U(c+1): must not start before the drain of State(c) has read the accumulator
           if (c + 1 < nchunks) {
-            wait1(B_STB_READY, c, 0x205u);
+            spin1(B_STB_READY, c, 0x205u);
             fence_after_sync();
             issue_update(c + 1, true);
             mma_commit(bar(B_ST_DONE));
-            mma_commit(bar(B_PK_FREE + (c + 1) % NPK));
           }
         }
+        mma_commit(bar(B_FIN));
       }
     }
   } else if (warp < 4) {
@@ -376,19 +397,18 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       }
     }
   } else if (warp >= W_OUT && warp < W_MMA) {
-    // ================================================================ output warps: O -> y
+    // ================================================================ output warps: O -> y; warp 8's lane 0 also feeds
+    // the stages (it is the thread that sees B_O_DONE(c), which is when stage c % NS becomes free)
     __nv_bfloat16* yb = p.y + b * p.sy.b + h * p.sy.h + (int64_t)tok_base * p.sy.l;
-    auto cvt16 = [&](const uint32_t (&r)[16], float sc, uint4& lo, uint4& hi) {
-      lo.x = pack_bf16(__uint_as_float(r[0]) * sc, __uint_as_float(r[1]) * sc);
-      lo.y = pack_bf16(__uint_as_float(r[2]) * sc, __uint_as_float(r[3]) * sc);
-      lo.z = pack_bf16(__uint_as_float(r[4]) * sc, __uint_as_float(r[5]) * sc);
-      lo.w = pack_bf16(__uint_as_float(r[6]) * sc, __uint_as_float(r[7]) * sc);
-      hi.x = pack_bf16(__uint_as_float(r[8]) * sc, __uint_as_float(r[9]) * sc);
-      hi.y = pack_bf16(__uint_as_float(r[10]) * sc, __uint_as_float(r[11]) * sc);
-      hi.z = pack_bf16(__uint_as_float(r[12]) * sc, __uint_as_float(r[13]) * sc);
-      hi.w = pack_bf16(__uint_as_float(r[14]) * sc, __uint_as_float(r[15]) * sc);
+    // 16 fp32 accumulator columns -> 8 packed bf16 pairs, scaled by the row's normaliser
+    auto pack16 = [&](const uint32_t (&r)[16], float sc, uint32_t* o) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = pack_bf16(__uint_as_float(r[2 * e]) * sc, __uint_as_float(r[2 * e + 1]) * sc);
     };
     if (mode != MODE_SEG_STATE) {
+      if (warp == W_OUT && lane == 0)
+        for (int j = 0; j < min(NS, nchunks); ++j) issue_tile(j);
+      __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_A_READY));          // O is free before the first chunk
       // Each thread parks 32 columns of its normalised row in this warp's 32-row staging tile; the warp then copies
       // the tile out with every store instruction covering whole 64-byte row segments (row-per-thread stores would
@@ -397,48 +417,70 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       uint8_t* yrow_s = ytile + lane * lay.yrow_bytes;
       const int n16 = dv >> 4;
       for (int c = 0; c < nchunks; ++c) {
-        // ---- epilogue: y = O[:, :dv] / (O[:, dv] + eps), 32 columns per round trip ----
         wait(B_O_DONE, c, 0x401u);
         fence_after_sync();
-        uint32_t dreg;
-        tmem_ld1(tlane + TM_O + dv, dreg);
-        const int tok_w = c * C + qd * 32;           // first token of this warp's tile
-        __nv_bfloat16* ytok = yb + (int64_t)tok_w * p.sy.l;
-        float inv = 0.f;
-#pragma unroll 1
-        for (int i0 = 0; i0 < n16; i0 += 2) {
-          const bool two = i0 + 1 < n16;
-          uint32_t r0[16], r1[16];
-          tmem_ld16(tlane + TM_O + 16 * i0, r0);
-          if (two) tmem_ld16(tlane + TM_O + 16 * (i0 + 1), r1);
+        if (warp == W_OUT && lane == 0 && c + NS < nchunks) issue_tile(c + NS);
+        // ---- O(c) into registers as fast as the loads go, so that the accumulator is free again early:
+        // y = O[:, :dv] / (O[:, dv] + eps), kept as packed bf16 pairs (8 per 16 columns)
+        uint32_t pk[56];
+        {
+          uint32_t dreg, r0[16], r1[16], r2[16], r3[16];
+          tmem_ld1(tlane + TM_O + dv, dreg);
+          tmem_ld16(tlane + TM_O, r0);
+          if (n16 > 1) tmem_ld16(tlane + TM_O + 16, r1);
+          if (n16 > 2) tmem_ld16(tlane + TM_O + 32, r2);
+          if (n16 > 3) tmem_ld16(tlane + TM_O + 48, r3);
           tmem_ld_wait();
-          if (i0 + 2 >= n16) {                       // the last TMEM read of O(c): the next chunk may overwrite it
+          const float inv = 1.0f / (__uint_as_float(dreg) + p.eps);
+          if (n16 <= 4) {                      // that was all of it
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_A_READY));
           }
-          if (i0 == 0) inv = 1.0f / (__uint_as_float(dreg) + p.eps);
-          uint4 lo, hi;
-          cvt16(r0, inv, lo, hi);
-          *reinterpret_cast<uint4*>(yrow_s) = lo;
-          *reinterpret_cast<uint4*>(yrow_s + 16) = hi;
-          if (two) {
-            cvt16(r1, inv, lo, hi);
-            *reinterpret_cast<uint4*>(yrow_s + 32) = lo;
-            *reinterpret_cast<uint4*>(yrow_s + 48) = hi;
+          pack16(r0, inv, pk);
+          if (n16 > 1) pack16(r1, inv, pk + 8);
+          if (n16 > 2) pack16(r2, inv, pk + 16);
+          if (n16 > 3) pack16(r3, inv, pk + 24);
+          if (n16 > 4) {                       // columns 64 .. dv - 1 (dv <= 112)
+            tmem_ld16(tlane + TM_O + 64, r0);
+            if (n16 > 5) tmem_ld16(tlane + TM_O + 80, r1);
+            if (n16 > 6) tmem_ld16(tlane + TM_O + 96, r2);
+            tmem_ld_wait();
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_A_READY));
+            pack16(r0, inv, pk + 32);
+            if (n16 > 5) pack16(r1, inv, pk + 40);
+            if (n16 > 6) pack16(r2, inv, pk + 48);
           }
-          __syncwarp();
-          // 16-byte pieces of the tile: ppr per row; piece idx = lane + 32 n -> row idx / ppr, piece idx % ppr
-          const int ppr = two ? 4 : 2, sh = two ? 2 : 1;
+        }
+        // ---- out through the staging tile, 32 columns per round
+        const int tok_w = c * C + qd * 32;           // first token of this warp's tile
+        __nv_bfloat16* ytok = yb + (int64_t)tok_w * p.sy.l;
 #pragma unroll
-          for (int n = 0; n < 4; ++n) {
-            if (n < ppr) {
-              const int idx = lane + 32 * n, r = idx >> sh, cc = idx & (ppr - 1);
-              const uint4 val = *reinterpret_cast<const uint4*>(ytile + r * lay.yrow_bytes + cc * 16);
-              if (tok_w + r < L) *reinterpret_cast<uint4*>(ytok + (int64_t)r * p.sy.l + 16 * i0 + cc * 8) = val;
+        for (int rd = 0; rd < 4; ++rd) {
+          const int i0 = 2 * rd;
+          if (i0 < n16) {
+            const bool two = i0 + 1 < n16;
+            *reinterpret_cast<uint4*>(yrow_s) = make_uint4(pk[16 * rd], pk[16 * rd + 1], pk[16 * rd + 2], pk[16 * rd + 3]);
+            *reinterpret_cast<uint4*>(yrow_s + 16) = make_uint4(pk[16 * rd + 4], pk[16 * rd + 5], pk[16 * rd + 6], pk[16 * rd + 7]);
+            if (two) {
+              *reinterpret_cast<uint4*>(yrow_s + 32) = make_uint4(pk[16 * rd + 8], pk[16 * rd + 9], pk[16 * rd + 10], pk[16 * rd + 11]);
+              *reinterpret_cast<uint4*>(yrow_s + 48) = make_uint4(pk[16 * rd + 12], pk[16 * rd + 13], pk[16 * rd + 14], pk[16 * rd + 15]);
             }
+            __syncwarp();
+            // 16-byte pieces of the tile: ppr per row; piece idx = lane + 32 n -> row idx / ppr, piece idx % ppr
+            const int ppr = two ? 4 : 2, sh = two ? 2 : 1;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+              if (n < ppr) {
+                const int idx = lane + 32 * n, r = idx >> sh, cc = idx & (ppr - 1);
+                const uint4 val = *reinterpret_cast<const uint4*>(ytile + r * lay.yrow_bytes + cc * 16);
+                if (tok_w + r < L) *reinterpret_cast<uint4*>(ytok + (int64_t)r * p.sy.l + 16 * i0 + cc * 8) = val;
+              }
+            }
+            __syncwarp();  // the tile is rewritten in the next round
           }
-          __syncwarp();  // the tile is rewritten in the next round
         }
       }
     }
@@ -494,7 +536,8 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       fence_after_sync();
       stage_state();
     } else {
-      if (pp1 > 0) make_p(0, 0, pp1);
+      const int share = (qd == 3 && pp1 > 0) ? 1 : 0;
+      if (pp1 > 0) make_p(0, 0, pp1, share);
       if (has_init) {
         // Preload state^T (fp32, TMEM) and its bf16 operand copy (buffer 1) with the sum over the earlier segments.
         const float* src = p.seg_state + ((size_t)bh * (p.nseg - 1) + (seg - 1)) * (size_t)((dv + 1) * DR) + (size_t)t * DR;
@@ -524,6 +567,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
         // ---- state after chunk c: fp32 TMEM -> bf16 smem operand (buffer c & 1), or fp32 staging at the end ----
         wait(B_ST_DONE, c, 0x402u);
         fence_after_sync();
+        if (warp == 4 && lane == 0) mbar_arrive(bar(B_PK_FREE + c % NPK));   // U(c) is complete: its phi'(K) buffer is free
         if (!last) {
           if (my_rows) {
             // 32 feature columns per round trip, the next round's loads in flight while this one is converted
@@ -547,9 +591,9 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
           fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(B_STB_READY));
-          if (pp1 > 0) make_p(c + 1, 0, pp1);
+          if (pp1 > 0) make_p(c + 1, 0, pp1, share);
         } else if (write_state) {
-          wait(B_O_DONE, c, 0x404u);   // the last chunk's P V' and readout still read the stages and the operand buffers
+          wait(B_FIN, 0, 0x404u);   // the last chunk's P V' and readout still read the stages and the operand buffers
           fence_after_sync();
           stage_state();
         }

@@ -22,6 +22,8 @@
 #include "tcgen05.cuh"
 #include "tma.cuh"
 
+#include <mutex>
+
 namespace based {
 
 __device__ unsigned int g_tc_status_swa = 0;
@@ -132,22 +134,9 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
     if (lo > hi) return 0u;
     return (0xFFFFFFFFu << lo) & (0xFFFFFFFFu >> (31 - hi));
   };
-  float m = -INFINITY;
-  for (int pc = 0; pc < npieces; ++pc) {
-    uint32_t r[32];
-    tmem_ld32(tlane + TM_S + c_lo + 32 * pc, r);
-    tmem_ld_wait();
-    const uint32_t mask = piece_mask(pc);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) m = fmaxf(m, (mask & (1u << i)) ? __uint_as_float(r[i]) : -INFINITY);
-  }
-  const float msc = m * p.scale_log2e;
+  // one probability pair -> bf16x2, and what the MMA will see of it added to the normaliser
   float sum = 0.f;
-  for (int pc = 0; pc < npieces; ++pc) {
-    uint32_t r[32];
-    tmem_ld32(tlane + TM_S + c_lo + 32 * pc, r);
-    tmem_ld_wait();
-    const uint32_t mask = piece_mask(pc);
+  auto exp_piece = [&](const uint32_t (&r)[32], uint32_t mask, float msc, int pc) {
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -164,6 +153,43 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
       sum += __uint_as_float(pk[i] << 16) + __uint_as_float(pk[i] & 0xffff0000u);
     }
     tmem_st16(tlane + TM_S + ((c_lo + 32 * pc) >> 1), pk);
+  };
+  auto max_piece = [&](const uint32_t (&r)[32], uint32_t mask, float m) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) m = fmaxf(m, (mask & (1u << i)) ? __uint_as_float(r[i]) : -INFINITY);
+    return m;
+  };
+  if (npieces <= 3) {
+    // window <= 64: the row's 96 scores stay in registers between the max and the exponentials, so S is read from
+    // TMEM once, with all loads in flight together
+    uint32_t r0[32], r1[32], r2[32];
+    tmem_ld32(tlane + TM_S + c_lo, r0);
+    if (npieces > 1) tmem_ld32(tlane + TM_S + c_lo + 32, r1);
+    if (npieces > 2) tmem_ld32(tlane + TM_S + c_lo + 64, r2);
+    tmem_ld_wait();
+    const uint32_t m0 = piece_mask(0), m1 = npieces > 1 ? piece_mask(1) : 0u, m2 = npieces > 2 ? piece_mask(2) : 0u;
+    float m = max_piece(r0, m0, -INFINITY);
+    if (npieces > 1) m = max_piece(r1, m1, m);
+    if (npieces > 2) m = max_piece(r2, m2, m);
+    const float msc = m * p.scale_log2e;
+    exp_piece(r0, m0, msc, 0);
+    if (npieces > 1) exp_piece(r1, m1, msc, 1);
+    if (npieces > 2) exp_piece(r2, m2, msc, 2);
+  } else {
+    float m = -INFINITY;
+    for (int pc = 0; pc < npieces; ++pc) {
+      uint32_t r[32];
+      tmem_ld32(tlane + TM_S + c_lo + 32 * pc, r);
+      tmem_ld_wait();
+      m = max_piece(r, piece_mask(pc), m);
+    }
+    const float msc = m * p.scale_log2e;
+    for (int pc = 0; pc < npieces; ++pc) {
+      uint32_t r[32];
+      tmem_ld32(tlane + TM_S + c_lo + 32 * pc, r);
+      tmem_ld_wait();
+      exp_piece(r, piece_mask(pc), msc, pc);
+    }
   }
   // zero the P columns of keys this warp's rows cannot see
   {
@@ -263,22 +289,45 @@ int launch_swa_prefill_tc(const void* q, const void* k, const void* v, void* o, 
   if (tiles > 2147483647LL) return BASED_ERR_TOO_LARGE;
   Params p;
   // tensor maps over [B][H][L][hd] (dims innermost first: hd, L, H, B); a batch or head extent of 1
-  // may come with any stride, so give those a harmless one
+  // may come with any stride, so give those a harmless one.  Maps are cached by pointer and geometry.
+  static tma::MapCache cache;
   auto fix = [&](int64_t s, int extent) { return extent == 1 ? (int64_t)8 : s; };
-  if (tma::encode_bf16_4d_sw128(&p.mq, q, hd, L, H, B, sq.l, fix(sq.h, H), fix(sq.b, B), 64, TQ) ||
-      tma::encode_bf16_4d_sw128(&p.mk, k, hd, L, H, B, sk.l, fix(sk.h, H), fix(sk.b, B), 64, NK) ||
-      tma::encode_bf16_4d_sw128(&p.mv, v, hd, L, H, B, sv.l, fix(sv.h, H), fix(sv.b, B), 64, NK) ||
-      tma::encode_bf16_4d_sw128(&p.mo, o, hd, L, H, B, so.l, fix(so.h, H), fix(so.b, B), 64, TQ))
+  auto get_map = [&](CUtensorMap* out, const void* base, Strides3 s, int rows) -> int {
+    const tma::MapKey key = tma::make_key(base, (uint64_t)hd, (uint64_t)L, (uint64_t)H, (uint64_t)B, 0, s.l, fix(s.h, H),
+                                          fix(s.b, B), 0, 64, (uint32_t)rows, 0, 4);
+    if (cache.find(key, out)) return 0;
+    if (tma::encode_bf16_4d_sw128(out, base, hd, L, H, B, s.l, fix(s.h, H), fix(s.b, B), 64, rows)) return BASED_ERR_IMPL;
+    cache.put(key, *out);
+    return 0;
+  };
+  if (get_map(&p.mq, q, sq, TQ) || get_map(&p.mk, k, sk, NK) || get_map(&p.mv, v, sv, NK) || get_map(&p.mo, o, so, TQ))
     return BASED_ERR_IMPL;
   p.L = L; p.H = H; p.hd = hd; p.W = window_left; p.tiles_per_seq = tiles_per_seq;
   p.tmem_cols = (NK + hd <= 256) ? 256 : 512;
   p.scale_log2e = scale * 1.4426950408889634f;
-  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_tc_status_swa);
-  if (e != cudaSuccess) return (int)e;
   const int natom = (hd + 63) / 64;
   const int smem = natom * (TQ + 2 * NK) * 128 + 64 + 1024;  // + slack to align the tiles to 1024 bytes
-  e = cudaFuncSetAttribute(swa_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return (int)e;
+  {
+    // once per device: the status word's address and the largest shared-memory size this kernel is launched with
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static unsigned int* status[kMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return BASED_ERR_TOO_LARGE;
+    std::lock_guard<std::mutex> lock(mu);
+    if (status[dev] == nullptr) {
+      unsigned int* addr = nullptr;
+      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_tc_status_swa);
+      if (e != cudaSuccess) return (int)e;
+      const int max_smem = 2 * (TQ + 2 * (TQ + 128)) * 128 + 64 + 1024;   // head_dim 128, window 128
+      e = cudaFuncSetAttribute(swa_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+      if (e != cudaSuccess) return (int)e;
+      status[dev] = addr;
+    }
+    p.status = status[dev];
+  }
   swa_prefill_tc_kernel<<<(unsigned)tiles, NT, smem, stream>>>(p);
   return (int)cudaGetLastError();
 }

@@ -14,7 +14,8 @@
 //
 // Receive workspace of one rank (symmetric: same layout on every rank, zero-filled once):
 //   [0, 256)                         control: word 0 = epoch of the NEXT call, word 1 = finished-block ticket
-//   [256, 256 + 2*W*T*4)             flags[parity][src rank][tile]   (uint32: the epoch whose data is complete)
+//   [256, 256 + 2*W*T*4)             flags[parity][src rank][tile]   (uint32: the epoch whose data is complete;
+//                                    a tile = 8 output columns, all rows)
 //   then                             data[parity][src rank][Mmax rows][N] fp32
 // with W = world size, T = tile count.  The epoch lives on the device and is advanced by the last
 // block of a launch, so a captured launch can be replayed; parity = epoch & 1 alternates two sets of
@@ -69,72 +70,94 @@ __host__ __device__ inline size_t data_offset(int world, int tiles) {
   return (kCtrlBytes + (size_t)2 * world * tiles * 4 + 255) / 256 * 256;
 }
 
-// grid = (N / 8, ceil(M / 16), ranks emulated in this launch (1 in real use)); block = WARPS x 32
+constexpr int kMaxRowTiles = 4;   // 16-row tiles per block: max_rows <= 64
+
+// grid = (N / 8, 1, ranks emulated in this launch (1 in real use)); block = WARPS x 32.  A block owns 8 output
+// columns for ALL rows: its weight rows are read once and applied to every 16-row tile.
 __global__ void __launch_bounds__(WARPS * 32) tp_outproj_allreduce_kernel(const TpParams p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int slot = p.emulate ? (int)blockIdx.z : 0;          // which of the pointer sets this block uses
   const int rank = p.emulate ? (int)blockIdx.z : p.rank;
-  const int n0 = blockIdx.x * 8, m0 = blockIdx.y * 16;
-  const int tiles = gridDim.x * gridDim.y, tile = blockIdx.y * gridDim.x + blockIdx.x;
+  const int n0 = blockIdx.x * 8;
+  const int tiles = gridDim.x, tile = blockIdx.x;
+  const int mtiles = (p.M + 15) >> 4;
   unsigned char* my_ws = p.ws[rank];
   unsigned int* ctrl = reinterpret_cast<unsigned int*>(my_ws);
-  // the epoch of this call: written by the last block of the previous launch (or 1 after zero-filling + set-up)
+  // the epoch of this call: written by the last block of the previous launch (1 after the workspace was prepared)
   const unsigned int epoch = ld_acquire_sys(ctrl);
   const int parity = epoch & 1u;
 
-  // ---- partial tile of this rank: rows m0..m0+15, columns n0..n0+7 over the rank's K slice
+  // ---- partial products of this rank: all rows, columns n0..n0+7, over the rank's K slice (split over the warps)
   const int kblocks = p.K / 32, per = (kblocks + WARPS - 1) / WARPS;
   const int kb0 = warp * per, kb1 = min(kb0 + per, kblocks);
-  const int r0 = m0 + g, r1 = m0 + g + 8;
-  const bool v0 = r0 < p.M, v1 = r1 < p.M;
-  const __nv_bfloat16* xa = p.x[slot] + (int64_t)(v0 ? r0 : 0) * p.sx + 8 * t;
-  const __nv_bfloat16* xb = p.x[slot] + (int64_t)(v1 ? r1 : 0) * p.sx + 8 * t;
   const __nv_bfloat16* wr = p.w[slot] + (int64_t)(n0 + g) * p.K + 8 * t;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const __nv_bfloat16* xr = p.x[slot] + 8 * t;
+  float acc[kMaxRowTiles][4];
+#pragma unroll
+  for (int m = 0; m < kMaxRowTiles; ++m)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[m][e] = 0.f;
   constexpr int U = 4;
   const uint4 zero = make_uint4(0, 0, 0, 0);
   for (int kb = kb0; kb < kb1; kb += U) {
-    uint4 wv[U], a0[U], a1[U];
+    uint4 wv[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const bool ok = kb + u < kb1;
-      const int ko = (kb + u) * 32;
-      wv[u] = ok ? __ldg(reinterpret_cast<const uint4*>(wr + ko)) : zero;
-      a0[u] = (ok && v0) ? __ldg(reinterpret_cast<const uint4*>(xa + ko)) : zero;
-      a1[u] = (ok && v1) ? __ldg(reinterpret_cast<const uint4*>(xb + ko)) : zero;
-    }
+    for (int u = 0; u < U; ++u) wv[u] = (kb + u < kb1) ? __ldg(reinterpret_cast<const uint4*>(wr + (kb + u) * 32)) : zero;
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const uint32_t fa[4] = {a0[u].x, a1[u].x, a0[u].y, a1[u].y};
-      const uint32_t fb[4] = {a0[u].z, a1[u].z, a0[u].w, a1[u].w};
-      mma_16816(acc, fa, wv[u].x, wv[u].y);
-      mma_16816(acc, fb, wv[u].z, wv[u].w);
+    for (int m = 0; m < kMaxRowTiles; ++m) {
+      if (m < mtiles) {
+        const int r0 = 16 * m + g, r1 = r0 + 8;
+        const bool v0 = r0 < p.M, v1 = r1 < p.M;
+        uint4 a0[U], a1[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const bool ok = kb + u < kb1;
+          const int ko = (kb + u) * 32;
+          a0[u] = (ok && v0) ? __ldg(reinterpret_cast<const uint4*>(xr + (int64_t)r0 * p.sx + ko)) : zero;
+          a1[u] = (ok && v1) ? __ldg(reinterpret_cast<const uint4*>(xr + (int64_t)r1 * p.sx + ko)) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t fa[4] = {a0[u].x, a1[u].x, a0[u].y, a1[u].y};
+          const uint32_t fb[4] = {a0[u].z, a1[u].z, a0[u].w, a1[u].w};
+          mma_16816(acc[m], fa, wv[u].x, wv[u].y);
+          mma_16816(acc[m], fb, wv[u].z, wv[u].w);
+        }
+      }
     }
   }
-  __shared__ float red[WARPS][4][32];
+  __shared__ float red[WARPS][kMaxRowTiles][4][32];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) red[warp][e][lane] = acc[e];
+  for (int m = 0; m < kMaxRowTiles; ++m)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) red[warp][m][e][lane] = acc[m][e];
   __syncthreads();
   if (warp == 0) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float s = 0.f;
+    for (int m = 0; m < kMaxRowTiles; ++m)
 #pragma unroll
-      for (int w = 0; w < WARPS; ++w) s += red[w][e][lane];
-      acc[e] = s;
-    }
-    // this lane holds rows r0 (acc 0, 1) and r1 (acc 2, 3), columns c0 and c0 + 1
+      for (int e = 0; e < 4; ++e) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) s += red[w][m][e][lane];
+        acc[m][e] = s;
+      }
+    // this lane holds, per row tile m, rows 16m + g (acc 0, 1) and 16m + g + 8 (acc 2, 3), columns c0 and c0 + 1
     const int c0 = n0 + 2 * t;
     const size_t doff = data_offset(p.world, tiles);
     const size_t slab = (size_t)p.Mmax * p.N;                               // floats per (parity, src rank)
     const size_t my_slab = ((size_t)parity * p.world + rank) * slab;
-    // ---- push the tile into every rank's receive buffer (own included), then publish its flag there
+    // ---- push the tile column into every rank's receive buffer (own included), then publish its flag there
     for (int d = 0; d < p.world; ++d) {
       const int dst = (rank + d) % p.world;                                  // spread the first stores over the peers
       float* data = reinterpret_cast<float*>(p.ws[dst] + doff) + my_slab;
-      if (v0) *reinterpret_cast<float2*>(data + (size_t)r0 * p.N + c0) = make_float2(acc[0], acc[1]);
-      if (v1) *reinterpret_cast<float2*>(data + (size_t)r1 * p.N + c0) = make_float2(acc[2], acc[3]);
+#pragma unroll
+      for (int m = 0; m < kMaxRowTiles; ++m) {
+        const int r0 = 16 * m + g, r1 = r0 + 8;
+        if (r0 < p.M) *reinterpret_cast<float2*>(data + (size_t)r0 * p.N + c0) = make_float2(acc[m][0], acc[m][1]);
+        if (r1 < p.M) *reinterpret_cast<float2*>(data + (size_t)r1 * p.N + c0) = make_float2(acc[m][2], acc[m][3]);
+      }
     }
     __threadfence_system();
     __syncwarp();
@@ -143,7 +166,7 @@ __global__ void __launch_bounds__(WARPS * 32) tp_outproj_allreduce_kernel(const 
       unsigned int* flags = reinterpret_cast<unsigned int*>(p.ws[dst] + flags_offset());
       st_release_sys(flags + ((size_t)parity * p.world + rank) * tiles + tile, epoch);
     }
-    // ---- wait for this tile from every rank (lane s watches source rank s), bounded
+    // ---- wait for this tile column from every rank (lane s watches source rank s), bounded
     bool ok = true;
     if (lane < p.world) {
       const unsigned int* flag =
@@ -162,21 +185,24 @@ __global__ void __launch_bounds__(WARPS * 32) tp_outproj_allreduce_kernel(const 
     }
     ok = __all_sync(0xffffffffu, ok);
     // ---- sum the partials in rank order, add the bias, round once
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
     const float* mine = reinterpret_cast<const float*>(my_ws + doff) + (size_t)parity * p.world * slab;
-    for (int src = 0; src < p.world; ++src) {
-      const float* data = mine + (size_t)src * slab;
-      if (v0) { const float2 a = ld_peer_written(data + (size_t)r0 * p.N + c0); s[0] += a.x; s[1] += a.y; }
-      if (v1) { const float2 a = ld_peer_written(data + (size_t)r1 * p.N + c0); s[2] += a.x; s[3] += a.y; }
-    }
-    if (p.bias) {
-      const float b0 = __bfloat162float(p.bias[c0]), b1 = __bfloat162float(p.bias[c0 + 1]);
-      s[0] += b0; s[1] += b1; s[2] += b0; s[3] += b1;
-    }
-    if (!ok) { s[0] = s[1] = s[2] = s[3] = __int_as_float(0x7fc00000); }   // a partial never came: NaN, not a silent sum
+    float b0 = 0.f, b1 = 0.f;
+    if (p.bias) { b0 = __bfloat162float(p.bias[c0]); b1 = __bfloat162float(p.bias[c0 + 1]); }
     __nv_bfloat16* out = p.out[slot];
-    if (v0) *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)r0 * p.so + c0) = __floats2bfloat162_rn(s[0], s[1]);
-    if (v1) *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)r1 * p.so + c0) = __floats2bfloat162_rn(s[2], s[3]);
+#pragma unroll
+    for (int m = 0; m < kMaxRowTiles; ++m) {
+      const int r0 = 16 * m + g, r1 = r0 + 8;
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int src = 0; src < p.world; ++src) {
+        const float* data = mine + (size_t)src * slab;
+        if (r0 < p.M) { const float2 a = ld_peer_written(data + (size_t)r0 * p.N + c0); s[0] += a.x; s[1] += a.y; }
+        if (r1 < p.M) { const float2 a = ld_peer_written(data + (size_t)r1 * p.N + c0); s[2] += a.x; s[3] += a.y; }
+      }
+      s[0] += b0; s[1] += b1; s[2] += b0; s[3] += b1;
+      if (!ok) { s[0] = s[1] = s[2] = s[3] = __int_as_float(0x7fc00000); }   // a partial never came: NaN, not a silent sum
+      if (r0 < p.M) *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)r0 * p.so + c0) = __floats2bfloat162_rn(s[0], s[1]);
+      if (r1 < p.M) *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)r1 * p.so + c0) = __floats2bfloat162_rn(s[2], s[3]);
+    }
     // ---- the last block of this rank's launch advances the epoch for the next call
     if (lane == 0) {
       __threadfence();
@@ -206,7 +232,8 @@ int read_tp_status(unsigned int* out, int reset) {
 
 size_t tp_outproj_workspace_bytes(int world, int Mmax, int N) {
   if (world < 1 || world > kMaxWorld || Mmax < 1 || N < 8 || N % 8 != 0) return 0;
-  const int tiles = (N / 8) * ((Mmax + 15) / 16);
+  if (Mmax > 16 * kMaxRowTiles) return 0;
+  const int tiles = N / 8;
   return data_offset(world, tiles) + (size_t)2 * world * Mmax * N * sizeof(float);
 }
 
@@ -214,7 +241,8 @@ int launch_tp_outproj_allreduce(const void* const* x, const void* const* w, cons
                                 void* const* workspaces, int M, int N, int K, int64_t sx, int64_t so, int Mmax,
                                 int rank, int world, int emulate, cudaStream_t stream) {
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return BASED_ERR_SHAPE;
-  if (M < 1 || M > Mmax || N % 8 != 0 || K % 32 != 0 || sx % 8 != 0 || so % 2 != 0) return BASED_ERR_SHAPE;
+  if (M < 1 || M > Mmax || Mmax > 16 * kMaxRowTiles || N % 8 != 0 || K % 32 != 0 || sx % 8 != 0 || so % 2 != 0)
+    return BASED_ERR_SHAPE;
   TpParams p;
   const int sets = emulate ? world : 1;
   for (int i = 0; i < kMaxWorld; ++i) { p.x[i] = nullptr; p.w[i] = nullptr; p.out[i] = nullptr; p.ws[i] = nullptr; }
@@ -236,8 +264,7 @@ int launch_tp_outproj_allreduce(const void* const* x, const void* const* w, cons
   p.max_wait_cycles = 2000000000LL;
   cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_tp_status);
   if (e != cudaSuccess) return (int)e;
-  // The tile count (hence the flag layout) is fixed by Mmax, not by this call's M: the grid always covers Mmax rows.
-  const dim3 grid(N / 8, (Mmax + 15) / 16, sets);
+  const dim3 grid(N / 8, 1, sets);
   // Blocks wait for blocks of other ranks that handle the same tile: every block of the launch must be resident.
   int dev = 0, sms = 0, per_sm = 0;
   if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;

@@ -14,7 +14,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
-from ..sharding import all_reduce_sum_, head_slice
+from ..sharding import all_reduce_sum_, head_slice, row_parallel_decode_linear
 
 
 class FeatureMap(nn.Module):
@@ -63,6 +63,7 @@ class LinearAttention(nn.Module):
         state_dtype: torch.dtype = None,
         process_group=None,
         fuse_qkv: bool = False,
+        fused_allreduce: bool = False,
         device=None,
         dtype=None,
         **kwargs,
@@ -102,6 +103,9 @@ class LinearAttention(nn.Module):
         # extension: in eval mode run proj_q, proj_k, proj_v as ONE GEMM over their concatenated weights
         # (the parameters stay separate, so reference checkpoints still load)
         self.fuse_qkv = fuse_qkv
+        # extension (tensor parallelism only): decode steps run out_proj and the all-reduce as ONE kernel per rank
+        # that exchanges partial tiles through peer memory; prompt passes keep GEMM + NCCL
+        self.fused_allreduce = fused_allreduce
         fk = {"device": device, "dtype": dtype}
         self.proj_q = nn.Linear(self.d_model, self.feature_dim * self.num_heads, bias=False, **fk)
         self.proj_k = nn.Linear(self.d_model, self.feature_dim * self.num_heads, bias=False, **fk)
@@ -177,7 +181,7 @@ class LinearAttention(nn.Module):
         assert l == 1, f"q.shape is {q.shape} but should be ({b}, {h}, 1, {d})"
         eps = 1e-6 if "fla" in self.parallel_implementation else 1e-12
         y = ops.linattn_decode(q, k, v, kv_state, k_state, eps=eps)
-        return all_reduce_sum_(ops.linear(y, self.out_proj.weight, self.out_proj.bias), self.process_group)
+        return row_parallel_decode_linear(self, y, self.out_proj.weight, self.out_proj.bias, self.process_group)
 
     def expanded_size(self):
         return self.feature_dim ** 2 + self.feature_dim + 1

@@ -11,7 +11,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
-from ..sharding import all_reduce_sum_, head_slice
+from ..sharding import all_reduce_sum_, head_slice, row_parallel_decode_linear
 
 
 class RotaryEmbedding(nn.Module):
@@ -76,6 +76,7 @@ class SlidingAttention(nn.Module):
         checkpointing=False,
         window_size=128,
         process_group=None,
+        fused_allreduce=False,
         device=None,
         dtype=None,
     ) -> None:
@@ -101,6 +102,8 @@ class SlidingAttention(nn.Module):
         # extension (the reference class takes no process group): head-sharded tensor parallelism,
         # Wqkv column-parallel, out_proj row-parallel, one all-reduce of the output
         self.process_group = process_group
+        # extension (tensor parallelism only): single-token steps run out_proj and the all-reduce as one kernel
+        self.fused_allreduce = fused_allreduce
         self.num_heads_total = num_heads
         if process_group is not None:
             import torch.distributed as dist
@@ -184,5 +187,8 @@ class SlidingAttention(nn.Module):
             context = ops.swa_decode(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], cache, lens, w, self.softmax_scale,
                                      rotary_cos=cos, rotary_sin=sin)
         context = context.to(in_dtype).reshape(batch, seqlen, self.num_heads * self.head_dim)
-        out = all_reduce_sum_(ops.linear(context, self.out_proj.weight, self.out_proj.bias), self.process_group)
+        if seqlen == 1 and inference_params is not None and inference_params.seqlen_offset > 0:
+            out = row_parallel_decode_linear(self, context, self.out_proj.weight, self.out_proj.bias, self.process_group)
+        else:
+            out = all_reduce_sum_(ops.linear(context, self.out_proj.weight, self.out_proj.bias), self.process_group)
         return out if not self.return_residual else (out, x)

@@ -126,3 +126,22 @@ class FusedRowParallel:
     def __call__(self, x, weight, bias=None):
         from . import ops
         return ops.tp_outproj_allreduce(x, weight, bias, self.ws.ptrs, self.max_rows, self.rank, self.world)
+
+
+def row_parallel_decode_linear(owner, x, weight, bias, group, max_rows: int = 64):
+    """``all_reduce(x W^T (+ bias))`` for a decode step of a row-parallel projection.  With ``owner.fused_allreduce`` set,
+    bf16 tensors, no bias and at most ``max_rows`` rows it is the one-kernel form (the :class:`FusedRowParallel` is built
+    on first use and kept on ``owner``); otherwise a GEMM followed by an NCCL all-reduce."""
+    from . import ops
+    rows = x.numel() // x.shape[-1] if x.numel() else 0
+    fused_ok = (group is not None and getattr(owner, "fused_allreduce", False) and bias is None and x.is_cuda
+                and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < rows <= max_rows
+                and x.shape[-1] % 32 == 0 and weight.shape[0] % 8 == 0 and weight.is_contiguous()
+                and not torch.is_grad_enabled() and dist.get_world_size(group) <= 8)
+    if not fused_ok:
+        return all_reduce_sum_(ops.linear(x, weight, bias), group)
+    fused = getattr(owner, "_fused_row_parallel", None)
+    if fused is None:
+        fused = FusedRowParallel(weight.shape[0], max_rows, group, x.device)
+        owner._fused_row_parallel = fused
+    return fused(x, weight)

@@ -555,6 +555,25 @@ def tp_bench(dev, world):
                          "prompt_allreduce_share": ar_p / tp_ms,
                          "decode_step_ms": td_ms, "decode_tok_per_s": B / (td_ms * 1e-3),
                          "decode_allreduce_share": ar_d / td_ms, "decode_timing": "eager launches, device time"}
+            # the same step with out_proj and the all-reduce as ONE kernel per rank (partial tiles pushed through peer
+            # memory); the output projection + collective alone, both ways, captured in CUDA graphs of 20 calls
+            try:
+                m.fused_allreduce = True
+                step()                                    # builds the peer workspace (a collective)
+                out[name]["decode_step_fused_ms"] = timed(step, 50)
+                from based_b200.sharding import all_reduce_sum_
+                yl = torch.randn(B, 1, m.out_proj.weight.shape[1], device=dev, dtype=torch.bfloat16)
+                w = m.out_proj.weight
+                fused = m._fused_row_parallel
+                t_f = max_over_ranks([time_graph(lambda: fused(yl, w), 20)], dev)[0]
+                t_n = max_over_ranks([time_graph(lambda: all_reduce_sum_(torch.nn.functional.linear(yl, w),
+                                                                       dist.group.WORLD), 20)], dev)[0]
+                out[name]["outproj_allreduce_fused_us"] = t_f * 1e3
+                out[name]["outproj_allreduce_cublas_nccl_us"] = t_n * 1e3
+            except Exception as exc:   # peer mapping unavailable on this machine: the NCCL figures above stand
+                out[name]["fused_error"] = repr(exc)
+            finally:
+                m.fused_allreduce = False
     return out
 
 

@@ -370,8 +370,8 @@ int based_decode_linear(const void* x, const void* w, const void* bias, void* ou
  * the rank's partial tile is pushed into EVERY rank's receive workspace with plain stores to peer memory (NVLink),
  * a per-tile flag follows, each rank then waits (bounded, ~1 s, reported through based_read_status; the affected
  * outputs become NaN) for the same tile of every rank and adds the partials in rank order, so all ranks hold
- * bit-identical results.  Built for decode sizes (M <= max_rows <= a few hundred single-token rows), where the
- * collective is latency-bound; prompt-size outputs stay on NCCL.
+ * bit-identical results.  Built for decode sizes (M <= max_rows <= 64 single-token rows), where the collective is
+ * latency-bound; prompt-size outputs stay on NCCL.
  *
  *   workspaces[world]  device pointers to every rank's workspace AS MAPPED IN THIS PROCESS (peer mappings from
  *                      CUDA IPC or a symmetric-memory allocator); entry `rank` is this rank's own.  Each is
@@ -379,7 +379,7 @@ int based_decode_linear(const void* x, const void* w, const void* bias, void* ou
  *                      based_tp_outproj_workspace_init (on its owner, before any rank's first call), and must not be
  *                      used by two calls that overlap in time.  The call counter lives in the workspace and is
  *                      advanced by the kernel, so a captured launch can be replayed.
- *   max_rows           fixes the tile count and the workspace layout: the same value on every rank and every call.
+ *   max_rows           (<= 64) fixes the workspace layout: the same value on every rank and every call.
  *   N a multiple of 8, K a multiple of 32, x and W 16-byte aligned, x_row_stride a multiple of 8, out_row_stride
  *   even; world <= 8.  Every rank must make the call (same M, N) at about the same time, like any collective.
  *   Returns BASED_ERR_TOO_LARGE when the launch could not be fully resident (its blocks wait for their
