@@ -179,38 +179,6 @@ __device__ __forceinline__ void mbar_wait_bounded(uint32_t saddr, uint32_t parit
   if (kWarpSync) __syncwarp();  // kWarpSync = false: called by a single lane of a diverged warp
 }
 
-// Non-blocking test of a phase (no hardware suspension): for the one thread whose wake-up latency matters.
-__device__ __forceinline__ bool mbar_test_wait(uint32_t saddr, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok)
-      : "r"(saddr), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Busy-polling form of mbar_wait_bounded for a single thread (the MMA issuer): the phase is seen within a few
-// cycles of its completion instead of after a suspended thread's wake-up.  Same bound and error reporting.
-__device__ __forceinline__ void mbar_spin_bounded(uint32_t saddr, uint32_t parity, volatile int* abort_flag,
-                                                  unsigned int* status, unsigned int code,
-                                                  long long max_cycles = 2000000000LL) {
-  if (mbar_test_wait(saddr, parity)) return;
-  const long long t0 = clock64();
-  int n = 0;
-  while (!mbar_test_wait(saddr, parity)) {
-    if ((++n & 63) == 0) {
-      if (*abort_flag) return;
-      if (clock64() - t0 > max_cycles) {
-        *abort_flag = 1;
-        if (status) atomicOr(status, code);
-        return;
-      }
-    }
-  }
-}
-
 // ---------------------------------------------------------------- cp.async (16-byte, zero-fill when !valid)
 __device__ __forceinline__ void cp_async16(uint32_t dst_saddr, const void* src, bool valid) {
   const int sz = valid ? 16 : 0;
