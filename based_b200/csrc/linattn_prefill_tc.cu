@@ -35,32 +35,39 @@ __device__ unsigned int g_tc_status = 0;  // ORed with a code when a bounded wai
 static __device__ __align__(256) unsigned char g_static_scratch[BASED_STATIC_SCRATCH_BYTES];
 
 
+#ifndef K1_MMA_UNROLL
+#define K1_MMA_UNROLL 1
+#endif
+#ifndef K1_OUT_FAST
+#define K1_OUT_FAST 1
+#endif
+#ifndef K1_QFIRST
+#define K1_QFIRST 0
+#endif
+#ifndef K1_OUT_DIRECT
+#define K1_OUT_DIRECT 0
+#endif
 namespace {
 
 using namespace tc;
 using namespace tcp;
 
 
-// Shared memory map (bytes).  One stage = Q [2 k-halves][128 tok][16 B] K-major (4096) + K (4096) + the V tile as
-// 128-byte-swizzled MN-major atoms of 64 columns ([128 tok][128 B] each, what a TMA tile copy with 128-byte swizzle
-// writes: one copy request per token row).  V' = [V | 1 | 0...]: the ones column is column dv.  When dv is a
-// multiple of 64 it opens an atom of its own, which is constant ([1, 0, ..., 0] in every row) and shared by all
-// stages (`cst`); otherwise it falls inside the last loaded atom, past the columns the copy fills with zeros, and
-// is set after each copy lands.  The state-update MMA reads V'^T as an M = 128 operand = two atoms; with one atom
-// (dv < 48) the second is whatever follows and only feeds accumulator lanes >= 64, which nobody reads.
+// Shared memory map (bytes).  One stage = Q [2 k-halves][128 tok][16 B] K-major (4096) + K (4096) +
+// V' MN-major [NV/8 groups of 8 columns][128 tok][16 B].  The state-update MMA reads V'^T as an
+// M = 128 operand, i.e. 16 column groups from the stage's V' base; the groups past NV/8 are
+// whatever follows in shared memory and only feed accumulator lanes >= NV, which nobody reads.
 struct Smem {
-  int nstage, npk, vatoms, stage_bytes, cst, phik, stb, stb_bytes, ystage, yrow_bytes, bar, total;
+  int nstage, npk, stage_bytes, phik, stb, stb_bytes, ystage, yrow_bytes, bar, total;
   __host__ __device__ explicit Smem(int dv) {
     const int nv = dv + 16;
-    nstage = 3;
-    npk = dv <= 64 ? 2 : 1;        // phi'(K) buffers (what fits in 227 KB)
-    vatoms = (dv + 63) >> 6;       // atoms the copy fills
-    stage_bytes = 8192 + vatoms * 16384;
-    cst = nstage * stage_bytes;    // the constant atom (used when dv % 64 == 0)
-    phik = cst + ((dv & 63) == 0 ? 16384 : 0);   // npk x 40960  MN-major [20 groups of 8 feats][128 tok][16 B]
-    stb = phik + npk * 40960;      // bf16 state operand, K-major [20 k-units][NV rows][16 B]
+    nstage = dv <= 64 ? 3 : 2;     // what fits in 227 KB
+    npk = dv <= 64 ? 2 : 1;        // phi'(K) buffers
+    stage_bytes = 8192 + (nv >> 3) * 2048;
+    phik = nstage * stage_bytes;   // npk x 40960  MN-major [20 groups of 8 feats][128 tok][16 B]
+    stb = phik + npk * 40960;      // 2 x stb_bytes: bf16 state, K-major [20 k-units][NV rows][16 B], double-buffered
     stb_bytes = nv * 320;
-    ystage = stb + stb_bytes;      // output tile [128 rows][32 columns bf16 + 16 B pad], one round of the epilogue
+    ystage = stb + 2 * stb_bytes;  // output tile [128 rows][32 columns bf16 + 16 B pad], one round of the epilogue
     yrow_bytes = 64 + 16;          // the pad makes the per-row 16-byte stores bank-conflict free
     bar = ystage + C * yrow_bytes; // mbarriers, TMEM base, abort flag
     total = bar + 256;
@@ -75,26 +82,70 @@ constexpr uint32_t TM_PQ = 416;   // phi'(Q) bf16, 80 columns
 constexpr uint32_t TM_COLS = 512;
 
 // mbarrier slots (8 bytes each) from Smem::bar
-//   B_FULL / B_EMPTY   per stage: tile landed (TMA transaction bytes) / the MMAs that read it have completed (B_EMPTY
-//                      only in the state-only mode; otherwise a stage is free when the burst that read it is done)
-//   B_BURST            phase 0: S(0) complete; phase c+1: the MMAs of chunk c complete            (tcgen05.commit)
-//   B_GAP              phase c: everything the MMAs of chunk c read from TMEM / the operand buffers is written and
-//                      everything they overwrite has been read out (one arrival per warp, 15 warps)
-//   B_X_READY, B_PK_FREE[2], B_FIN   state-only mode: phi'(K_c) written / its buffer free again / last update done
-enum Bar { B_FULL = 0, B_EMPTY = 3, B_BURST = 6, B_GAP, B_X_READY, B_PK_FREE, B_PK_FREE1, B_FIN, B_COUNT };
+//   B_FULL / B_EMPTY   per stage: tile landed (TMA transaction bytes) / the MMAs that read it have completed
+//   B_S_DONE           S(c) = Q K^T complete                                   (tcgen05.commit)
+//   B_A_READY          P(c) written AND O free (O(c-1) read out) AND tile c+1 landed   (poly warps + output warps)
+//   B_X_READY          phase 0: phi'(K_0) written; phase c+1: phi'(Q_c) and phi'(K_{c+1}) written   (expansion warps)
+//   B_O_DONE           readout of chunk c complete: O(c) final, phi'(Q_c) consumed   (commit)
+//   B_ST_DONE          state update of chunk c complete                              (commit)
+//   B_STB_READY        bf16 copy of the state after chunk c written (drain warps)
+//   B_PK_FREE[2]       the update that read this phi'(K) buffer has completed        (commit)
+//   B_INIT             carried-in state preloaded (sequence split)      B_FIN   last update complete (state-only mode)
+enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_A_READY, B_X_READY, B_O_DONE, B_ST_DONE, B_STB_READY, B_PK_FREE,
+           B_PK_FREE1, B_INIT, B_FIN, B_COUNT };
 
-// The tensor pipe serves tcgen05.mma ahead of tcgen05.ld / st: a TMEM load issued while MMAs are queued completes
-// when the queue has drained.  Work on TMEM by the CUDA cores therefore does not overlap the MMAs; spreading it
-// over the chunk only multiplies the stalls.  The chunk is run in two phases instead:
-//   burst(c)  one thread issues, back to back,
-//               PV(c):  O   = P(c) V'(c)                  8 MMAs  M128 N=NV  K16   A = P in TMEM
-//               R(c):   O  += phi'(Q_c) State(c-1)        10 MMAs M128 N=NV  K16   A = phi'(Q) in TMEM, B = bf16 state
-//               U(c):   St^T += V'(c)^T phi'(K_c)         8 MMAs  M128 N160  K16
-//               S(c+1) = Q(c+1) K(c+1)^T                  1 MMA   M128 N128  K16
-//             and commits once (B_BURST).  Meanwhile the CUDA cores do what needs no TMEM: phi'(K_{c+1}) into
-//             shared memory, y(c-1) from registers out to global memory, TMA refills.
-//   gap(c+1)  all 15 other warps, at once: O(c) -> registers, S(c+1) -> P(c+1), phi'(Q_{c+1}) -> TMEM, State(c) -> bf16
-//             operand; each warp arrives on B_GAP when its part is done, and the next burst starts.
+// P(c) = causal(1 + s/4 + s^2/32), evaluated in bf16x2 (two FMAs per pair), in place over S, for the 32-column
+// pieces [p0, p1) of this warp's 32 rows; pieces right of the diagonal block (> qd) are zeros, no load.
+// P is half as wide as S: piece k of P lands on S columns [16k, 16k + 16), i.e. inside S piece k / 2.  One warp
+// going through its pieces in ascending order never overwrites what it has not read.  When two warps share a
+// quadrant (pieces [0, 2) and [2, 4)), the second one's first store lands inside S piece 1, which belongs to
+// the first warp: the first warp arrives on a named barrier once it has piece 1 in registers (share == 1), the
+// second waits there before its first store (share == 2).
+// A function of its own, not inlined: two roles call it, and the kernel's hot code has to stay inside the SM's
+// instruction cache.
+__device__ __noinline__ void poly_pieces(uint32_t tlane, int qd, int lane, int p0, int p1, int share) {
+  constexpr uint32_t k1 = 0x3F803F80u, kq = 0x3E803E80u, k32 = 0x3D003D00u;  // (1,1) (1/4,1/4) (1/32,1/32)
+#pragma unroll 1
+  for (int piece = p0; piece < p1; ++piece) {
+    if (piece <= qd) {
+      uint32_t sreg[32], pk[16];
+      tmem_ld32(tlane + TM_S + piece * 32, sreg);
+      tmem_ld_wait();
+      if (share == 1 && piece == 1) asm volatile("bar.arrive 1, 64;\n" ::: "memory");
+      if (piece < qd) {   // left of the diagonal block: every column is visible
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+          pk[i] = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
+        }
+      } else {            // the diagonal block: columns 0..lane of this piece are visible
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
+          const uint32_t pv = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
+          const uint32_t mask = (2 * i + 1 <= lane) ? 0xFFFFFFFFu : ((2 * i <= lane) ? 0x0000FFFFu : 0u);
+          pk[i] = pv & mask;
+        }
+      }
+      if (share == 2 && piece == p0) asm volatile("bar.sync 1, 64;\n" ::: "memory");
+      tmem_st16(tlane + TM_S + piece * 16, pk);
+    } else {
+      uint32_t z[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) z[i] = 0;
+      tmem_st16(tlane + TM_S + piece * 16, z);
+    }
+  }
+}
+
+// Per 128-token chunk c the MMA thread issues, in this order,
+//   PV(c):  O  = P(c) V'(c)                    8 MMAs  M128 N=NV  K16   A = P in TMEM
+//   S(c+1)                                     1 MMA   M128 N128  K16
+//   R(c):   O += phi'(Q_c) State(c-1)          10 MMAs M128 N=NV  K16   A = phi'(Q) in TMEM, B = bf16 state (smem)
+//   U(c+1): St^T += V'(c+1)^T phi'(K_{c+1})    8 MMAs  M128 N160  K16   (the state update runs ONE CHUNK AHEAD)
+// so that the output warps read O(c) while U(c+1) keeps the tensor pipe busy, the polynomial of chunk c+1 and
+// the expansions run under PV / R, and the only chain carried from chunk to chunk is
+// U(c) -> drain (fp32 state -> bf16 operand) -> U(c+1): the drain reads the accumulator that U(c+1) writes.
 __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_constant__ Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = smem_u32(smem);
@@ -124,35 +175,32 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   auto wait1 = [&](int i, uint32_t parity, unsigned int code) {   // by one lane of a diverged warp
     mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
   };
-  // end of a warp's part of a gap: its TMEM / shared-memory writes are ordered before the arrival
-  auto gap_arrive = [&]() {
-    fence_before_sync();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar(B_GAP));
-  };
 
   // ------------------------------------------------------------------ set-up
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
-    mbar_init(bar(B_BURST), 1);
-    mbar_init(bar(B_GAP), NT / 32 - 1);
+    mbar_init(bar(B_S_DONE), 1);
+    mbar_init(bar(B_O_DONE), 1);
+    mbar_init(bar(B_ST_DONE), 1);
+    // polynomial warps: 4 (one per quadrant), 5 when quadrant 3 is shared by two warps; + 4 output warps
+    mbar_init(bar(B_A_READY), 4 + (q3_has_state ? 4 : 5));
     mbar_init(bar(B_X_READY), 4);
+    mbar_init(bar(B_STB_READY), 4);
     mbar_init(bar(B_PK_FREE), 1);
     mbar_init(bar(B_PK_FREE + 1), 1);
+    mbar_init(bar(B_INIT), 4);
     mbar_init(bar(B_FIN), 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TM_COLS);
-  // The constant atom: row r holds [1, 0, ..., 0]; its first 16-byte chunk sits at chunk r & 7 (128-byte swizzle).
-  const bool ones_atom = (dv & 63) == 0;
-  if (ones_atom)
-    for (int i = tid; i < C * 8; i += NT) {
-      const int r = i >> 3, ch = i & 7;
-      const uint4 val = ch == (r & 7) ? make_uint4(0x00003F80u, 0, 0, 0) : make_uint4(0, 0, 0, 0);  // bf16 1.0 in element 0
-      *reinterpret_cast<uint4*>(smem + lay.cst + r * 128 + ch * 16) = val;
-    }
+  // V' column groups dv/8 (ones column) and dv/8 + 1 (zeros) are constant for the whole kernel.
+  for (int i = tid; i < NS * 2 * C; i += NT) {
+    const int st = i / (2 * C), r = i - st * 2 * C, g = r / C, tk = r - g * C;
+    const uint4 val = g == 0 ? make_uint4(0x00003F80u, 0, 0, 0) : make_uint4(0, 0, 0, 0);  // bf16 1.0 in element 0
+    *reinterpret_cast<uint4*>(smem + st * lay.stage_bytes + 8192 + ((dv >> 3) + g) * 2048 + tk * 16) = val;
+  }
   fence_proxy_async();
   fence_before_sync();
   __syncthreads();
@@ -160,164 +208,60 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   const uint32_t tmem = *tmem_slot;
   const uint32_t tlane = tmem + ((uint32_t)(qd * 32) << 16);  // this warp's lane window, column 0
 
-  // One thread feeds the stages: Q and K land as [k-half][token][16 B] - the no-swizzle K-major UMMA layout - by one
-  // cp.async.bulk.tensor each (the tensor maps cut a row into 16-byte groups and put the group index outside the
-  // token index); V lands as 128-byte-swizzled 64-column atoms, one copy per atom.  Tokens past the end of the
-  // sequence are zero-filled by the copy unit.  Chunk j goes to stage j % NS; the caller knows that the stage is free.
+  // One thread feeds the stages: Q and K land as [k-half][token][16 B], V' as [8-column group][token][16 B] - the
+  // no-swizzle UMMA layouts - by one cp.async.bulk.tensor each (the tensor maps cut a row into 16-byte groups and
+  // put the group index outside the token index).  Tokens past the end of the sequence are zero-filled by the
+  // copy unit.  Chunk j goes to stage j % NS once the MMAs that read chunk j - NS have completed.
   const bool need_q = mode != MODE_SEG_STATE;
   auto issue_tile = [&](int j) {
     const int st = j % NS;
+    if (j >= NS) wait1(B_EMPTY + st, j / NS - 1, 0x100u);
     const uint32_t base = sb + st * lay.stage_bytes;
     const int tok = tok_base + j * C;
-    // every V box is 64 columns wide (columns past dv are out of bounds: zero-filled, and counted)
-    tma::mbar_expect_tx(bar(B_FULL + st), (need_q ? 8192u : 4096u) + (uint32_t)lay.vatoms * 16384u);
+    tma::mbar_expect_tx(bar(B_FULL + st), (need_q ? 8192u : 4096u) + (uint32_t)dv * 256u);
     if (need_q) tma::load_5d(base, &p.mq, bar(B_FULL + st), 0, tok, 0, h, b);
     tma::load_5d(base + 4096, &p.mk, bar(B_FULL + st), 0, tok, 0, h, b);
-    for (int a = 0; a < lay.vatoms; ++a) tma::load_4d(base + 8192 + a * 16384, &p.mv, bar(B_FULL + st), 64 * a, tok, h, b);
+    tma::load_5d(base + 8192, &p.mv, bar(B_FULL + st), 0, tok, 0, h, b);
   };
 
-  // P(c) = causal(1 + s/4 + s^2/32), evaluated in bf16x2 (two FMAs per pair), in place over S, for the 32-column
-  // pieces [p0, p1) of this warp's 32 rows; pieces right of the diagonal block (> qd) are zeros, no load.
-  // P is half as wide as S: piece k of P lands on S columns [16k, 16k + 16), i.e. inside S piece k / 2.  One warp
-  // going through its pieces in ascending order never overwrites what it has not read.  When two warps share a
-  // quadrant (pieces [0, 2) and [2, 4)), the second one's first store lands inside S piece 1, which belongs to
-  // the first warp: the first warp arrives on a named barrier once it has its two pieces in registers (share == 1),
-  // the second waits there before its first store (share == 2).
-  auto poly_pieces = [&](int p0, int p1, int share) {
-    constexpr uint32_t k1 = 0x3F803F80u, kq = 0x3E803E80u, k32 = 0x3D003D00u;  // (1,1) (1/4,1/4) (1/32,1/32)
-    // one piece: 32 fp32 scores -> 16 packed bf16x2 polynomial values, stored over the left half of what was read
-    auto eval_store = [&](const uint32_t (&sreg)[32], int piece) {
-      uint32_t pk[16];
-      if (piece < qd) {   // left of the diagonal block: every column is visible
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
-          pk[i] = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
-        }
-      } else {            // the diagonal block: columns 0..lane of this piece are visible
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint32_t w = pack_bf16(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1]));
-          const uint32_t pv = fma_bf16x2(w, fma_bf16x2(w, k32, kq), k1);
-          const uint32_t mask = (2 * i + 1 <= lane) ? 0xFFFFFFFFu : ((2 * i <= lane) ? 0x0000FFFFu : 0u);
-          pk[i] = pv & mask;
-        }
-      }
-      tmem_st16(tlane + TM_S + piece * 16, pk);
-    };
-    // two pieces per round trip: both loads in flight together
-#pragma unroll 1
-    for (int piece = p0; piece < p1; piece += 2) {
-      const bool two = piece + 1 < p1;
-      const bool real0 = piece <= qd, real1 = two && piece + 1 <= qd;
-      uint32_t sa[32], sc[32];
-      if (real0) tmem_ld32(tlane + TM_S + piece * 32, sa);
-      if (real1) tmem_ld32(tlane + TM_S + (piece + 1) * 32, sc);
-      if (real0) tmem_ld_wait();
-      if (share == 1 && piece == 0) asm volatile("bar.arrive 1, 64;\n" ::: "memory");   // pieces 0 and 1 are in registers
-      if (share == 2 && piece == p0) asm volatile("bar.sync 1, 64;\n" ::: "memory");
-      if (real0) {
-        eval_store(sa, piece);
-      } else {
-        uint32_t z[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) z[i] = 0;
-        tmem_st16(tlane + TM_S + piece * 16, z);
-      }
-      if (two) {
-        if (real1) {
-          eval_store(sc, piece + 1);
-        } else {
-          uint32_t z[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) z[i] = 0;
-          tmem_st16(tlane + TM_S + (piece + 1) * 16, z);
-        }
-      }
-    }
+  // the polynomial of chunk c by this warp (pieces [p0, p1)), then one arrival on B_A_READY - which, with three
+  // stages, also vouches for tile c + 1 having landed (it was requested two chunks earlier), so that the MMA thread
+  // need not test that barrier itself; with two stages the tile is requested only after this arrival, and the MMA
+  // thread waits for it where it needs it
+  const bool full_via_a = NS >= 3;
+  auto make_p = [&](int c, int p0, int p1, int share) {
+    wait(B_S_DONE, c, 0x400u);
+    fence_after_sync();
+    poly_pieces(tlane, qd, lane, p0, p1, share);
     tmem_st_wait();
+    fence_before_sync();
+    if (full_via_a && c + 1 < nchunks) wait(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x403u);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(B_A_READY));
   };
 
-  // V' of a stage as an MN-major 128-byte-swizzled operand (B of P V', A of the state update): groups of 8 tokens
-  // 1024 B apart, the second 64-column atom `lbo` bytes after the first - the constant atom when dv is a multiple of
-  // 64, else the stage's own second atom; a K-step of 16 tokens advances the start address by 2048 B (128 units)
-  auto v_desc = [&](int st) -> uint64_t {
-    const uint32_t base = sb + st * lay.stage_bytes + 8192;
-    const uint32_t lbo = ones_atom ? (sb + lay.cst) - (base + (lay.vatoms - 1) * 16384) : 16384u;
-    return make_smem_desc_sw128(base, lbo, 1024);
-  };
-
-  if (mode == MODE_SEG_STATE) {
-    // ================================================================ state-only pass of the sequence split:
-    // St += V'(c)^T phi'(K_c) for every chunk of the segment, the packed fp32 state written out at the end
-    if (warp == W_LOAD) {
-      if (lane == 0)
-        for (int j = 0; j < nchunks; ++j) {
-          if (j >= NS) wait1(B_EMPTY + j % NS, j / NS - 1, 0x100u);
-          issue_tile(j);
-        }
-    } else if (warp == W_MMA) {
-      if (lane == 0) {
-        const uint32_t idesc_st = make_idesc_bf16(128, DR, 1, 1);
-        const uint64_t d_pk = make_smem_desc(sb + lay.phik, 128, 2048);
-        for (int c = 0; c < nchunks; ++c) {
-          wait1(B_FULL + c % NS, c / NS, 0x210u);
-          wait1(B_X_READY, c, 0x211u);
-          fence_after_sync();
-          const uint64_t dv_c = v_desc(c % NS), d_pk_c = d_pk + (c % NPK) * (40960 >> 4);
-#pragma unroll
-          for (int j = 0; j < C / 16; ++j)
-            mma_ss(tmem + TM_ST, dv_c + 128 * j, d_pk_c + 16 * j, idesc_st, (c > 0 || j > 0) ? 1u : 0u);
-          mma_commit(bar(B_EMPTY + c % NS));
-          mma_commit(bar(B_PK_FREE + c % NPK));
-        }
-        mma_commit(bar(B_FIN));
-      }
-    }
-  }
-
-  // phi'(K_c) -> shared memory (MN-major operand of the state update); rows past the sequence end are zero
-  auto expand_k = [&](int c) {
-    wait(B_FULL + c % NS, c / NS, 0x300u);
-    const uint8_t* stg = smem + (c % NS) * lay.stage_bytes + 4096 + t * 16;   // [k-half][token][16 B]
-    uint32_t X[8];
-    {
-      const uint4 a = *reinterpret_cast<const uint4*>(stg), bq = *reinterpret_cast<const uint4*>(stg + 2048);
-      X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
-    }
-    const bool valid = c * C + t < L;
-    if (!valid) {  // tokens past the end contribute nothing to the state: phi'(K) = 0, also the constant
-#pragma unroll
-      for (int m = 0; m < 8; ++m) X[m] = 0;
-    }
-    const uint32_t one = valid ? 0xFFFFFFFFu : 0u;
-    if (!ones_atom) {
-      // the ones column of V' (column dv) inside the last loaded atom, where the copy left zeros: this token's row
-      const int col = dv & 63;
-      *reinterpret_cast<uint4*>(smem + (c % NS) * lay.stage_bytes + 8192 + (dv >> 6) * 16384 + t * 128 +
-                                (((col >> 3) ^ (t & 7)) << 4)) = make_uint4(0x00003F80u, 0, 0, 0);
-    }
-    uint8_t* dst = smem + lay.phik + (c % NPK) * 40960 + t * 16;
-    expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
-      constexpr int g = decltype(G)::value;
-      if constexpr (g == 0) w0 &= one;
-      *reinterpret_cast<uint4*>(dst + g * 2048) = make_uint4(w0, w1, w2, w3);
-    });
-    fence_proxy_async();
-  };
-
-  if (mode == MODE_SEG_STATE) {
-    if (warp < 4) {
+  if (warp >= W_LOAD) {
+    // ================================================================ polynomial warps of quadrants 1-3; warp 13's
+    // lane 0 is also the TMA producer
+    if (mode == MODE_SEG_STATE) {
+      if (warp == W_LOAD && lane == 0)
+        for (int j = 0; j < nchunks; ++j) issue_tile(j);
+    } else {
+      if (warp == W_LOAD && lane == 0)
+        for (int j = 0; j < min(NS, nchunks); ++j) issue_tile(j);
+      __syncwarp();
+      // quadrant 3 is shared with warp 7 when that warp has no state rows to drain
+      const bool shared_q3 = qd == 3 && !q3_has_state;
+      const int p0 = shared_q3 ? 2 : 0;
       for (int c = 0; c < nchunks; ++c) {
-        // the phi'(K) buffer is free once the state update that read it (NPK chunks ago) has completed
-        if (c >= NPK) wait(B_PK_FREE + c % NPK, c / NPK - 1, 0x302u);
-        expand_k(c);
+        make_p(c, p0, 4, shared_q3 ? 2 : 0);
+        // tile c + NS - 1 replaces tile c - 1, whose last reader was the readout of chunk c - 1
+        if (warp == W_LOAD && lane == 0 && c >= 1 && c + NS - 1 < nchunks) issue_tile(c + NS - 1);
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_X_READY));
       }
     }
   } else if (warp == W_MMA) {
-    // ================================================================ MMA issue: one thread, one burst per chunk
+    // ================================================================ MMA issue: one thread runs the whole loop
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_o_pv = make_idesc_bf16(128, NV, 0, 1);   // A = P (TMEM), B = V' MN-major
@@ -326,159 +270,261 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       // Descriptors differ between K-steps only in the start address (bits 0-13, units of 16 B).
       const uint64_t d_q = make_smem_desc(sb, 2048, 128);                // + stage offset; k-halves 2048 B apart
       const uint64_t d_k = make_smem_desc(sb + 4096, 2048, 128);
+      const uint64_t d_v = make_smem_desc(sb + 8192, 128, 2048);         // + stage offset, + 16 per K-step
       const uint64_t d_pk = make_smem_desc(sb + lay.phik, 128, 2048);    // + buffer offset, + 16 per K-step
-      const uint64_t d_stb = make_smem_desc(sb + lay.stb, NV * 16, 128); // + 2 NV per K-step
-      const uint32_t stage_units = (uint32_t)lay.stage_bytes >> 4;
+      const uint64_t d_stb = make_smem_desc(sb + lay.stb, NV * 16, 128); // + buffer offset, + 2 NV per K-step
+      const uint32_t stage_units = (uint32_t)lay.stage_bytes >> 4, stb_units = (uint32_t)lay.stb_bytes >> 4;
       const uint32_t stb_step = 2 * NV;
-      wait1(B_FULL + 0, 0, 0x200u);
-      fence_after_sync();
-      mma_ss(tmem + TM_S, d_q, d_k, idesc_s, 0);
-      mma_commit(bar(B_BURST));                            // phase 0
-      for (int c = 0; c < nchunks; ++c) {
-        wait1(B_GAP, c, 0x201u);                           // P(c), phi'(Q_c), phi'(K_c), State(c-1) ready; O free; tile c+1 in
+      // U(c): St^T (+)= V'(c)^T phi'(K_c)
+      auto issue_update = [&](int c, bool acc0) {
+        const uint64_t dv_c = d_v + (c % NS) * stage_units, d_pk_c = d_pk + (c % NPK) * (40960 >> 4);
+#if K1_MMA_UNROLL
+#pragma unroll
+#else
+#pragma unroll 1
+#endif
+        for (int j = 0; j < C / 16; ++j)
+          mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (acc0 || j > 0) ? 1u : 0u);
+      };
+      if (mode == MODE_SEG_STATE) {
+        // state only: St += V'(c)^T phi'(K_c) for every chunk of the segment
+        for (int c = 0; c < nchunks; ++c) {
+          wait1(B_FULL + c % NS, c / NS, 0x210u);
+          wait1(B_X_READY, c, 0x211u);
+          fence_after_sync();
+          issue_update(c, c > 0);
+          mma_commit(bar(B_EMPTY + c % NS));
+          mma_commit(bar(B_PK_FREE + c % NPK));
+        }
+        mma_commit(bar(B_FIN));
+      } else {
+        wait1(B_FULL + 0, 0, 0x200u);
         fence_after_sync();
-        const uint64_t dv_c = v_desc(c % NS), d_pk_c = d_pk + (c % NPK) * (40960 >> 4);
+        mma_ss(tmem + TM_S, d_q, d_k, idesc_s, 0);
+        mma_commit(bar(B_S_DONE));
+        wait1(B_X_READY, 0, 0x208u);                       // phi'(K_0)
+        if (has_init) wait1(B_INIT, 0, 0x207u);            // state^T and its bf16 copy were preloaded
+        fence_after_sync();
+        issue_update(0, has_init);
+        mma_commit(bar(B_ST_DONE));
+        mma_commit(bar(B_PK_FREE + 0));
+        for (int c = 0; c < nchunks; ++c) {
+          const int st = c % NS;
+          // PV(c): needs P(c) and a free O; the same barrier covers tile c + 1
+          wait1(B_A_READY, c, 0x201u);
+          fence_after_sync();
+          {
+            const uint64_t dv_c = d_v + st * stage_units;
+#if K1_MMA_UNROLL
 #pragma unroll
-        for (int j = 0; j < C / 16; ++j)
-          mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 128 * j, idesc_o_pv, j > 0);
-        if (c > 0 || has_init) {
+#else
+#pragma unroll 1
+#endif
+            for (int j = 0; j < C / 16; ++j)
+              mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
+          }
+          // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
+          if (c + 1 < nchunks) {
+            if (!full_via_a) {
+              wait1(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x203u);
+              fence_after_sync();
+            }
+            const uint32_t so = ((c + 1) % NS) * stage_units;
+            mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
+            mma_commit(bar(B_S_DONE));
+          }
+          // R(c): O(c) += phi'(Q_c) State(c-1).  The bf16 state of chunk c-1 sits in buffer (c-1) & 1 and was
+          // awaited before U(c) was issued (see below); a carried-in state was preloaded into buffer 1.
+          wait1(B_X_READY, c + 1, 0x204u);                 // phi'(Q_c) and phi'(K_{c+1})
+          fence_after_sync();
+          if (c > 0 || has_init) {
+            const uint64_t d_stb_c = d_stb + ((c + 1) & 1) * stb_units;
+#if K1_MMA_UNROLL
 #pragma unroll
-          for (int j = 0; j < DR / 16; ++j)
-            mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb + stb_step * j, idesc_o_st, 1);
+#else
+#pragma unroll 1
+#endif
+            for (int j = 0; j < DR / 16; ++j)
+              mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb_c + stb_step * j, idesc_o_st, 1);
+          }
+          mma_commit(bar(B_O_DONE));
+          mma_commit(bar(B_EMPTY + st));
+          // U(c+1): must not start before the drain of State(c) has read the accumulator
+          if (c + 1 < nchunks) {
+            wait1(B_STB_READY, c, 0x205u);
+            fence_after_sync();
+            issue_update(c + 1, true);
+            mma_commit(bar(B_ST_DONE));
+            mma_commit(bar(B_PK_FREE + (c + 1) % NPK));
+          }
         }
-#pragma unroll
-        for (int j = 0; j < C / 16; ++j)
-          mma_ss(tmem + TM_ST, dv_c + 128 * j, d_pk_c + 16 * j, idesc_st, (c > 0 || j > 0 || has_init) ? 1u : 0u);
-        if (c + 1 < nchunks) {
-          const uint32_t so = ((c + 1) % NS) * stage_units;
-          mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
-        }
-        mma_commit(bar(B_BURST));                          // phase c + 1
+        mma_commit(bar(B_FIN));   // every MMA is complete: the stages may be reused for the final state
       }
     }
   } else if (warp < 4) {
-    // ================================================================ expansion warps: phi'(K) -> smem (under the
-    // bursts), phi'(Q) -> TMEM (in the gaps)
-    expand_k(0);
-    for (int c = 0; c < nchunks; ++c) {
-      wait(B_BURST, c, 0x301u);                            // the previous phi'(Q) has been consumed
-      fence_after_sync();
-      {
-        wait(B_FULL + c % NS, c / NS, 0x303u);
-        const uint8_t* stg = smem + (c % NS) * lay.stage_bytes + t * 16;
-        uint32_t X[8];
-        const uint4 a = *reinterpret_cast<const uint4*>(stg), bq = *reinterpret_cast<const uint4*>(stg + 2048);
-        X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
-        uint32_t hold[4];
-        expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
-          constexpr int g = decltype(G)::value;
-          if constexpr ((g & 1) == 0) {
-            hold[0] = w0; hold[1] = w1; hold[2] = w2; hold[3] = w3;
-          } else {
-            const uint32_t r[8] = {hold[0], hold[1], hold[2], hold[3], w0, w1, w2, w3};
-            tmem_st8(tlane + TM_PQ + 4 * (g - 1), r);
-          }
-        });
-        tmem_st_wait();
+    // ================================================================ expansion warps: phi'(K) -> smem, phi'(Q) -> TMEM
+    auto load_x = [&](int c, int off, uint32_t (&X)[8]) {
+      const uint8_t* stg = smem + (c % NS) * lay.stage_bytes + off + t * 16;   // [k-half][token][16 B]
+      const uint4 a = *reinterpret_cast<const uint4*>(stg), bq = *reinterpret_cast<const uint4*>(stg + 2048);
+      X[0] = a.x; X[1] = a.y; X[2] = a.z; X[3] = a.w; X[4] = bq.x; X[5] = bq.y; X[6] = bq.z; X[7] = bq.w;
+    };
+    auto expand_k = [&](int c) {
+      wait(B_FULL + c % NS, c / NS, 0x300u);
+      uint32_t X[8];
+      load_x(c, 4096, X);
+      const bool valid = c * C + t < L;
+      if (!valid) {  // tokens past the end contribute nothing to the state: phi'(K) = 0, also the constant
+#pragma unroll
+        for (int m = 0; m < 8; ++m) X[m] = 0;
       }
-      // with one phi'(K) buffer, the next chunk's expansion has to wait for the update that has just finished,
-      // i.e. it is part of the gap; with two it runs under the burst
-      if (NPK == 1 && c > 0) expand_k(c);
-      gap_arrive();
-      if (NPK > 1 && c + 1 < nchunks) expand_k(c + 1);
+      const uint32_t one = valid ? 0xFFFFFFFFu : 0u;
+      // the phi'(K) buffer is free once the state update that read it (NPK chunks ago) has completed
+      const int pkb = c % NPK;
+      if (c >= NPK) wait(B_PK_FREE + pkb, c / NPK - 1, 0x302u);
+      uint8_t* dst = smem + lay.phik + pkb * 40960 + t * 16;
+      expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+        constexpr int g = decltype(G)::value;
+        if constexpr (g == 0) w0 &= one;
+        *reinterpret_cast<uint4*>(dst + g * 2048) = make_uint4(w0, w1, w2, w3);
+      });
+      fence_proxy_async();
+    };
+    auto expand_q = [&](int c) {
+      wait(B_FULL + c % NS, c / NS, 0x303u);
+      uint32_t X[8];
+      load_x(c, 0, X);
+      if (c > 0) wait(B_O_DONE, c - 1, 0x301u);  // the previous phi'(Q) has been consumed
+      fence_after_sync();
+      uint32_t hold[4];
+      expand_packed(X, [&](auto G, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+        constexpr int g = decltype(G)::value;
+        if constexpr ((g & 1) == 0) {
+          hold[0] = w0; hold[1] = w1; hold[2] = w2; hold[3] = w3;
+        } else {
+          const uint32_t r[8] = {hold[0], hold[1], hold[2], hold[3], w0, w1, w2, w3};
+          tmem_st8(tlane + TM_PQ + 4 * (g - 1), r);
+        }
+      });
+      tmem_st_wait();
+      fence_before_sync();
+    };
+    if (mode == MODE_SEG_STATE) {
+      for (int c = 0; c < nchunks; ++c) {
+        expand_k(c);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_X_READY));
+      }
+    } else {
+      expand_k(0);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_X_READY));        // phase 0
+      for (int c = 0; c < nchunks; ++c) {
+#if K1_QFIRST
+        // phi'(Q_c) first: it only waits for the readout of chunk c - 1, while phi'(K_{c+1}) also needs tile c + 1,
+        // the youngest load in flight
+        expand_q(c);
+        if (c + 1 < nchunks) expand_k(c + 1);
+#else
+        if (c + 1 < nchunks) expand_k(c + 1);            // does not depend on the readout: runs ahead
+        expand_q(c);
+#endif
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_X_READY));      // phase c + 1
+      }
     }
   } else if (warp >= W_OUT && warp < W_MMA) {
-    // ================================================================ output warps: O -> y; warp 8's lane 0 also feeds
-    // the stages
+    // ================================================================ output warps: O -> y
     __nv_bfloat16* yb = p.y + b * p.sy.b + h * p.sy.h + (int64_t)tok_base * p.sy.l;
     // 16 fp32 accumulator columns -> 8 packed bf16 pairs, scaled by the row's normaliser
     auto pack16 = [&](const uint32_t (&r)[16], float sc, uint32_t* o) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) o[e] = pack_bf16(__uint_as_float(r[2 * e]) * sc, __uint_as_float(r[2 * e + 1]) * sc);
     };
-    if (warp == W_OUT && lane == 0)
-      for (int j = 0; j < min(NS, nchunks); ++j) issue_tile(j);
-    __syncwarp();
-    // Each thread parks 32 columns of its normalised row in this warp's 32-row staging tile; the warp then copies
-    // the tile out with every store instruction covering whole 64-byte row segments (row-per-thread stores would
-    // touch 32 different lines per instruction).
-    uint8_t* ytile = smem + lay.ystage + (qd * 32) * lay.yrow_bytes;
-    uint8_t* yrow_s = ytile + lane * lay.yrow_bytes;
-    const int n16 = dv >> 4;
-    wait(B_BURST, 0, 0x400u);
-    gap_arrive();                                          // gap 0: O is free before the first chunk
-    for (int c = 0; c < nchunks; ++c) {
-      wait(B_BURST, c + 1, 0x401u);                        // O(c) is final; stage c % NS is free
-      fence_after_sync();
-      if (warp == W_OUT && lane == 0 && c + NS < nchunks) issue_tile(c + NS);
-      // ---- O(c) into registers: y = O[:, :dv] / (O[:, dv] + eps), kept as packed bf16 pairs (8 per 16 columns)
-      uint32_t pk[56];
-      {
-        uint32_t dreg, r0[16], r1[16], r2[16], r3[16];
-        tmem_ld1(tlane + TM_O + dv, dreg);
-        tmem_ld16(tlane + TM_O, r0);
-        if (n16 > 1) tmem_ld16(tlane + TM_O + 16, r1);
-        if (n16 > 2) tmem_ld16(tlane + TM_O + 32, r2);
-        if (n16 > 3) tmem_ld16(tlane + TM_O + 48, r3);
-        tmem_ld_wait();
-        const float inv = 1.0f / (__uint_as_float(dreg) + p.eps);
-        if (n16 <= 4 && c + 1 < nchunks) gap_arrive();     // that was all of it
-        pack16(r0, inv, pk);
-        if (n16 > 1) pack16(r1, inv, pk + 8);
-        if (n16 > 2) pack16(r2, inv, pk + 16);
-        if (n16 > 3) pack16(r3, inv, pk + 24);
-        if (n16 > 4) {                       // columns 64 .. dv - 1 (dv <= 112)
-          tmem_ld16(tlane + TM_O + 64, r0);
-          if (n16 > 5) tmem_ld16(tlane + TM_O + 80, r1);
-          if (n16 > 6) tmem_ld16(tlane + TM_O + 96, r2);
-          tmem_ld_wait();
-          if (c + 1 < nchunks) gap_arrive();
-          pack16(r0, inv, pk + 32);
-          if (n16 > 5) pack16(r1, inv, pk + 40);
-          if (n16 > 6) pack16(r2, inv, pk + 48);
-        }
-      }
-      // ---- out through the staging tile, 32 columns per round (under the next burst)
-      const int tok_w = c * C + qd * 32;           // first token of this warp's tile
-      __nv_bfloat16* ytok = yb + (int64_t)tok_w * p.sy.l;
-#pragma unroll
-      for (int rd = 0; rd < 4; ++rd) {
-        const int i0 = 2 * rd;
-        if (i0 < n16) {
-          const bool two = i0 + 1 < n16;
-          *reinterpret_cast<uint4*>(yrow_s) = make_uint4(pk[16 * rd], pk[16 * rd + 1], pk[16 * rd + 2], pk[16 * rd + 3]);
-          *reinterpret_cast<uint4*>(yrow_s + 16) = make_uint4(pk[16 * rd + 4], pk[16 * rd + 5], pk[16 * rd + 6], pk[16 * rd + 7]);
+    auto free_o = [&]() {   // the last TMEM read of O(c) is done: the next chunk may overwrite it
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_A_READY));
+    };
+    if (mode != MODE_SEG_STATE) {
+      if (lane == 0) mbar_arrive(bar(B_A_READY));          // O is free before the first chunk
+      // Each thread parks 32 columns of its normalised row in this warp's 32-row staging tile; the warp then copies
+      // the tile out with every store instruction covering whole 64-byte row segments (row-per-thread stores would
+      // touch 32 different lines per instruction).
+      uint8_t* ytile = smem + lay.ystage + (qd * 32) * lay.yrow_bytes;
+      uint8_t* yrow_s = ytile + lane * lay.yrow_bytes;
+      const int n16 = dv >> 4;
+      const int nrd = (n16 + 1) >> 1;                // rounds of 32 columns
+      for (int c = 0; c < nchunks; ++c) {
+        wait(B_O_DONE, c, 0x401u);
+        fence_after_sync();
+        const int tok_w = c * C + qd * 32;           // first token of this warp's tile
+        __nv_bfloat16* ytok = yb + (int64_t)tok_w * p.sy.l;
+        uint32_t dreg;
+        tmem_ld1(tlane + TM_O + dv, dreg);           // the row's normaliser; completes with the first round's loads
+        float inv = 0.f;
+        // one round: 32 (or 16) normalised columns -> staging tile -> global, whole 64-byte row segments per store
+        auto round_out = [&](int rd, bool two, const uint32_t (&r0)[16], const uint32_t (&r1)[16]) {
+          uint32_t pk[16];
+          pack16(r0, inv, pk);
+          *reinterpret_cast<uint4*>(yrow_s) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(yrow_s + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
           if (two) {
-            *reinterpret_cast<uint4*>(yrow_s + 32) = make_uint4(pk[16 * rd + 8], pk[16 * rd + 9], pk[16 * rd + 10], pk[16 * rd + 11]);
-            *reinterpret_cast<uint4*>(yrow_s + 48) = make_uint4(pk[16 * rd + 12], pk[16 * rd + 13], pk[16 * rd + 14], pk[16 * rd + 15]);
+            pack16(r1, inv, pk + 8);
+            *reinterpret_cast<uint4*>(yrow_s + 32) = make_uint4(pk[8], pk[9], pk[10], pk[11]);
+            *reinterpret_cast<uint4*>(yrow_s + 48) = make_uint4(pk[12], pk[13], pk[14], pk[15]);
           }
           __syncwarp();
           // 16-byte pieces of the tile: ppr per row; piece idx = lane + 32 n -> row idx / ppr, piece idx % ppr
           const int ppr = two ? 4 : 2, sh = two ? 2 : 1;
-#pragma unroll
-          for (int n = 0; n < 4; ++n) {
-            if (n < ppr) {
-              const int idx = lane + 32 * n, r = idx >> sh, cc = idx & (ppr - 1);
-              const uint4 val = *reinterpret_cast<const uint4*>(ytile + r * lay.yrow_bytes + cc * 16);
-              if (tok_w + r < L) *reinterpret_cast<uint4*>(ytok + (int64_t)r * p.sy.l + 16 * i0 + cc * 8) = val;
-            }
+#pragma unroll 1
+          for (int n = 0; n < ppr; ++n) {
+            const int idx = lane + 32 * n, r = idx >> sh, cc = idx & (ppr - 1);
+            const uint4 val = *reinterpret_cast<const uint4*>(ytile + r * lay.yrow_bytes + cc * 16);
+            if (tok_w + r < L) *reinterpret_cast<uint4*>(ytok + (int64_t)r * p.sy.l + 32 * rd + cc * 8) = val;
           }
           __syncwarp();  // the tile is rewritten in the next round
+        };
+#if K1_OUT_FAST
+        if (n16 == 4) {
+          // dv = 64: all of O(c) into registers first, so that the accumulator is free again as early as possible
+          uint32_t r0[16], r1[16], r2[16], r3[16];
+          tmem_ld16(tlane + TM_O, r0);
+          tmem_ld16(tlane + TM_O + 16, r1);
+          tmem_ld16(tlane + TM_O + 32, r2);
+          tmem_ld16(tlane + TM_O + 48, r3);
+          tmem_ld_wait();
+          free_o();
+          inv = 1.0f / (__uint_as_float(dreg) + p.eps);
+#if K1_OUT_DIRECT
+          if (tok_w + lane < L) {
+            uint4* yrow_g = reinterpret_cast<uint4*>(ytok + (int64_t)lane * p.sy.l);
+            uint32_t pk[8];
+            pack16(r0, inv, pk); yrow_g[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]); yrow_g[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            pack16(r1, inv, pk); yrow_g[2] = make_uint4(pk[0], pk[1], pk[2], pk[3]); yrow_g[3] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            pack16(r2, inv, pk); yrow_g[4] = make_uint4(pk[0], pk[1], pk[2], pk[3]); yrow_g[5] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            pack16(r3, inv, pk); yrow_g[6] = make_uint4(pk[0], pk[1], pk[2], pk[3]); yrow_g[7] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          }
+#else
+          round_out(0, true, r0, r1);
+          round_out(1, true, r2, r3);
+#endif
+          continue;
+        }
+#endif
+        // y = O[:, :dv] / (O[:, dv] + eps), 32 columns per round.  The loop is kept rolled: this kernel's hot
+        // code has to stay inside the SM's instruction cache.
+#pragma unroll 1
+        for (int rd = 0; rd < nrd; ++rd) {
+          const bool two = 2 * rd + 1 < n16;
+          uint32_t r0[16], r1[16];
+          tmem_ld16(tlane + TM_O + 32 * rd, r0);
+          if (two) tmem_ld16(tlane + TM_O + 32 * rd + 16, r1);
+          tmem_ld_wait();
+          if (rd == 0) inv = 1.0f / (__uint_as_float(dreg) + p.eps);
+          if (rd == nrd - 1) free_o();               // that was the last read of O(c)
+          round_out(rd, two, r0, r1);
         }
       }
-    }
-  } else if (warp >= W_LOAD) {
-    // ================================================================ polynomial warps of quadrants 1-3
-    // quadrant 3 is shared with warp 7 when that warp has no state rows to drain
-    const bool shared_q3 = qd == 3 && !q3_has_state;
-    const int p0 = shared_q3 ? 2 : 0;
-    for (int c = 0; c < nchunks; ++c) {
-      wait(B_BURST, c, 0x402u);                            // S(c) complete
-      fence_after_sync();
-      poly_pieces(p0, 4, shared_q3 ? 2 : 0);
-      // tile c + 1 (requested two chunks ago) is in: vouched for here, so that the MMA thread need not test it
-      if (c + 1 < nchunks) wait(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x403u);
-      gap_arrive();
     }
   } else {
     // ================================================================ state-drain warps (4-7); warp 4 also evaluates
@@ -494,13 +540,29 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       hi.z = pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13]));
       hi.w = pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15]));
     };
-    // bf16 copy of 32 feature columns of this thread's state row into the operand buffer
-    auto store_stb = [&](int i, const uint32_t (&r0)[16], const uint32_t (&r1)[16]) {
+    // final fp32 state^T -> shared memory at offset 0 (every MMA and every other warp's use of the stages is
+    // over by then).  The TMEM loads are warp-collective, so every lane issues them; only rows < NV are kept.
+    auto stage_state = [&]() {
+      float* stg = reinterpret_cast<float*>(smem) + t * STAGE_STRIDE_F;
+#pragma unroll 1
+      for (int i = 0; i < 10; ++i) {
+        uint32_t r[16];
+        tmem_ld16(tlane + TM_ST + 16 * i, r);
+        tmem_ld_wait();
+        if (t < NV) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            *reinterpret_cast<uint4*>(stg + 16 * i + 4 * e) = make_uint4(r[4 * e], r[4 * e + 1], r[4 * e + 2], r[4 * e + 3]);
+        }
+      }
+    };
+    // bf16 copy of 32 feature columns of this thread's state row into operand buffer `buf`
+    auto store_stb = [&](int buf, int i, const uint32_t (&r0)[16], const uint32_t (&r1)[16]) {
       uint4 a0, a1, b0, b1;
       cvt16(r0, a0, a1);
       cvt16(r1, b0, b1);
       if (t < NV) {  // rows >= NV of the B operand do not exist (N = NV)
-        uint8_t* dst = smem + lay.stb + (4 * i) * (NV * 16) + t * 16;
+        uint8_t* dst = smem + lay.stb + buf * lay.stb_bytes + (4 * i) * (NV * 16) + t * 16;
         *reinterpret_cast<uint4*>(dst) = a0;
         *reinterpret_cast<uint4*>(dst + NV * 16) = a1;
         *reinterpret_cast<uint4*>(dst + 2 * NV * 16) = b0;
@@ -511,92 +573,71 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
     // polynomial pieces [0, pp1) of this warp: all of quadrant 0 (one piece to evaluate, three to clear), the first
     // two of quadrant 3 when warp 15 shares it
     const int pp1 = qd == 0 ? 4 : ((qd == 3 && !q3_has_state) ? 2 : 0);
-    const int share = (qd == 3 && pp1 > 0) ? 1 : 0;
-    // ---- gap 0: the polynomial of chunk 0, and the carried-in state of a later segment
-    wait(B_BURST, 0, 0x404u);
-    fence_after_sync();
-    if (has_init) {
-      // Preload state^T (fp32, TMEM) and its bf16 operand copy with the sum over the earlier segments.
-      const float* src = p.seg_state + ((size_t)bh * (p.nseg - 1) + (seg - 1)) * (size_t)((dv + 1) * DR) + (size_t)t * DR;
-      const bool row = t <= dv;
-#pragma unroll 1
-      for (int i = 0; i < 5; ++i) {
-        uint32_t r0[16], r1[16];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint4 x = row ? __ldg(reinterpret_cast<const uint4*>(src + 32 * i + 4 * e)) : make_uint4(0, 0, 0, 0);
-          const uint4 y2 = row ? __ldg(reinterpret_cast<const uint4*>(src + 32 * i + 16 + 4 * e)) : make_uint4(0, 0, 0, 0);
-          r0[4 * e] = x.x; r0[4 * e + 1] = x.y; r0[4 * e + 2] = x.z; r0[4 * e + 3] = x.w;
-          r1[4 * e] = y2.x; r1[4 * e + 1] = y2.y; r1[4 * e + 2] = y2.z; r1[4 * e + 3] = y2.w;
-        }
-        tmem_st16(tlane + TM_ST + 32 * i, r0);
-        tmem_st16(tlane + TM_ST + 32 * i + 16, r1);
-        store_stb(i, r0, r1);
-      }
-      tmem_st_wait();
-      fence_proxy_async();
-    }
-    if (pp1 > 0) poly_pieces(0, pp1, share);
-    gap_arrive();
-    for (int c = 0; c < nchunks; ++c) {
-      const bool last = c + 1 == nchunks;
-      wait(B_BURST, c + 1, 0x402u);                          // U(c) and S(c+1) complete
+    if (mode == MODE_SEG_STATE) {
+      wait(B_FIN, 0, 0x410u);
       fence_after_sync();
-      if (!last) {
-        // ---- state after chunk c: fp32 TMEM -> bf16 smem operand.  32 feature columns per round trip, the next
-        // round's loads in flight while this one is converted.
-        if (my_rows) {
-          uint32_t ra[16], rb[16], rc[16], rd[16];
-          tmem_ld16(tlane + TM_ST, ra);
-          tmem_ld16(tlane + TM_ST + 16, rb);
-          tmem_ld_wait();
+      stage_state();
+    } else {
+      const int share = (qd == 3 && pp1 > 0) ? 1 : 0;
+      if (pp1 > 0) make_p(0, 0, pp1, share);
+      if (has_init) {
+        // Preload state^T (fp32, TMEM) and its bf16 operand copy (buffer 1) with the sum over the earlier segments.
+        const float* src = p.seg_state + ((size_t)bh * (p.nseg - 1) + (seg - 1)) * (size_t)((dv + 1) * DR) + (size_t)t * DR;
+        const bool row = t <= dv;
+#pragma unroll 1
+        for (int i = 0; i < 5; ++i) {
+          uint32_t r0[16], r1[16];
 #pragma unroll
-          for (int i = 0; i < 5; ++i) {
-            if (i & 1) {
-              if (i < 4) { tmem_ld16(tlane + TM_ST + 32 * (i + 1), ra); tmem_ld16(tlane + TM_ST + 32 * (i + 1) + 16, rb); }
-              store_stb(i, rc, rd);
-            } else {
-              if (i < 4) { tmem_ld16(tlane + TM_ST + 32 * (i + 1), rc); tmem_ld16(tlane + TM_ST + 32 * (i + 1) + 16, rd); }
-              store_stb(i, ra, rb);
+          for (int e = 0; e < 4; ++e) {
+            const uint4 x = row ? __ldg(reinterpret_cast<const uint4*>(src + 32 * i + 4 * e)) : make_uint4(0, 0, 0, 0);
+            const uint4 y2 = row ? __ldg(reinterpret_cast<const uint4*>(src + 32 * i + 16 + 4 * e)) : make_uint4(0, 0, 0, 0);
+            r0[4 * e] = x.x; r0[4 * e + 1] = x.y; r0[4 * e + 2] = x.z; r0[4 * e + 3] = x.w;
+            r1[4 * e] = y2.x; r1[4 * e + 1] = y2.y; r1[4 * e + 2] = y2.z; r1[4 * e + 3] = y2.w;
+          }
+          tmem_st16(tlane + TM_ST + 32 * i, r0);
+          tmem_st16(tlane + TM_ST + 32 * i + 16, r1);
+          store_stb(1, i, r0, r1);
+        }
+        tmem_st_wait();
+        fence_proxy_async();
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_INIT));
+      }
+      for (int c = 0; c < nchunks; ++c) {
+        const bool last = c + 1 == nchunks;
+        // ---- state after chunk c: fp32 TMEM -> bf16 smem operand (buffer c & 1), or fp32 staging at the end ----
+        wait(B_ST_DONE, c, 0x402u);
+        fence_after_sync();
+        if (!last) {
+          if (my_rows) {
+            // 32 feature columns per round trip, the next round's loads in flight while this one is converted
+            uint32_t ra[16], rb[16], rc[16], rd[16];
+            tmem_ld16(tlane + TM_ST, ra);
+            tmem_ld16(tlane + TM_ST + 16, rb);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 5; ++i) {
+              if (i & 1) {
+                if (i < 4) { tmem_ld16(tlane + TM_ST + 32 * (i + 1), ra); tmem_ld16(tlane + TM_ST + 32 * (i + 1) + 16, rb); }
+                store_stb(c & 1, i, rc, rd);
+              } else {
+                if (i < 4) { tmem_ld16(tlane + TM_ST + 32 * (i + 1), rc); tmem_ld16(tlane + TM_ST + 32 * (i + 1) + 16, rd); }
+                store_stb(c & 1, i, ra, rb);
+              }
+              if (i < 4) tmem_ld_wait();
             }
-            if (i < 4) tmem_ld_wait();
           }
           fence_proxy_async();
+          fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_STB_READY));
+          if (pp1 > 0) make_p(c + 1, 0, pp1, share);
+        } else if (write_state) {
+          wait(B_FIN, 0, 0x404u);   // the last chunk's P V' and readout still read the stages and the operand buffers
+          fence_after_sync();
+          stage_state();
         }
-        if (pp1 > 0) poly_pieces(0, pp1, share);
-        gap_arrive();
-      } else if (write_state) {
-        // final fp32 state^T -> shared memory at offset 0 (every MMA and every other warp's use of the stages is
-        // over).  The TMEM loads are warp-collective, so every lane issues them; only rows < NV are kept.
-        float* stg = reinterpret_cast<float*>(smem) + t * STAGE_STRIDE_F;
-#pragma unroll 1
-        for (int i = 0; i < 10; ++i) {
-          uint32_t r[16];
-          tmem_ld16(tlane + TM_ST + 16 * i, r);
-          tmem_ld_wait();
-          if (t < NV) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              *reinterpret_cast<uint4*>(stg + 16 * i + 4 * e) = make_uint4(r[4 * e], r[4 * e + 1], r[4 * e + 2], r[4 * e + 3]);
-          }
-        }
-      }
-    }
-  }
-  if (mode == MODE_SEG_STATE && warp >= 4 && warp < 8) {
-    // state-only mode: the segment's fp32 state^T -> shared memory, rows 0..dv
-    wait(B_FIN, 0, 0x410u);
-    fence_after_sync();
-    float* stg = reinterpret_cast<float*>(smem) + t * STAGE_STRIDE_F;
-#pragma unroll 1
-    for (int i = 0; i < 10; ++i) {
-      uint32_t r[16];
-      tmem_ld16(tlane + TM_ST + 16 * i, r);
-      tmem_ld_wait();
-      if (t < NV) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          *reinterpret_cast<uint4*>(stg + 16 * i + 4 * e) = make_uint4(r[4 * e], r[4 * e + 1], r[4 * e + 2], r[4 * e + 3]);
       }
     }
   }
@@ -737,18 +778,6 @@ static int grouped_map(CUtensorMap* out, const void* base, int groups, int L, in
   return 0;
 }
 
-// Tensor map of v [B][H][L][dv]: boxes of 64 columns x 128 tokens with 128-byte swizzle; cached.
-static int swizzled_map(CUtensorMap* out, const void* base, int dv, int L, int H, int B, Strides3 s) {
-  static tma::MapCache cache;
-  const int64_t sh = H == 1 ? 8 : s.h, sbb = B == 1 ? 8 : s.b, sl = L == 1 ? 128 : s.l;
-  if (sh <= 0 || sbb <= 0 || sl <= 0) return BASED_ERR_IMPL;
-  const tma::MapKey key = tma::make_key(base, (uint64_t)dv, (uint64_t)L, (uint64_t)H, (uint64_t)B, 0, sl, sh, sbb, 0, 64, C, 0, 4);
-  if (cache.find(key, out)) return 0;
-  if (tma::encode_bf16_4d_sw128(out, base, dv, L, H, B, sl, sh, sbb, 64, C)) return BASED_ERR_IMPL;
-  cache.put(key, *out);
-  return 0;
-}
-
 int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void* y, void* kv_state, void* k_state,
                               int B, int H, int L, int dv, Strides3 sq, Strides3 sk, Strides3 sv, Strides3 sy,
                               int state_dtype, float eps, int nseg, void* scratch, size_t scratch_bytes,
@@ -762,7 +791,7 @@ int launch_linattn_prefill_tc(const void* q, const void* k, const void* v, void*
   Params p;
   int rc = grouped_map(&p.mq, q, 2, L, H, B, sq);
   if (rc == 0) rc = grouped_map(&p.mk, k, 2, L, H, B, sk);
-  if (rc == 0) rc = swizzled_map(&p.mv, v, dv, L, H, B, sv);
+  if (rc == 0) rc = grouped_map(&p.mv, v, dv / 8, L, H, B, sv);
   if (rc != 0) return rc;
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k = static_cast<const __nv_bfloat16*>(k);

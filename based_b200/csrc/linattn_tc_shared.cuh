@@ -120,7 +120,7 @@ __device__ __forceinline__ int packed_index(int f, bool& offdiag) {
 }
 
 struct Params {
-  CUtensorMap mq, mk, mv;   // q, k: [B][H][2 k-halves][L][8]; v: [B][H][L][dv], 64-column boxes, 128-byte swizzle; 128 tokens per box
+  CUtensorMap mq, mk, mv;   // q, k: [B][H][2 k-halves][L][8]; v: [B][H][dv/8 groups][L][8]; box = 128 tokens
   const __nv_bfloat16 *q, *k, *v;
   __nv_bfloat16* y;
   void *kv_state, *k_state;
