@@ -35,17 +35,8 @@ __device__ unsigned int g_tc_status = 0;  // ORed with a code when a bounded wai
 static __device__ __align__(256) unsigned char g_static_scratch[BASED_STATIC_SCRATCH_BYTES];
 
 
-#ifndef K1_MMA_UNROLL
-#define K1_MMA_UNROLL 1
-#endif
-#ifndef K1_OUT_FAST
-#define K1_OUT_FAST 1
-#endif
-#ifndef K1_QFIRST
-#define K1_QFIRST 0
-#endif
-#ifndef K1_OUT_DIRECT
-#define K1_OUT_DIRECT 0
+#ifndef K1_EARLY_TMA
+#define K1_EARLY_TMA 1
 #endif
 namespace {
 
@@ -82,16 +73,18 @@ constexpr uint32_t TM_PQ = 416;   // phi'(Q) bf16, 80 columns
 constexpr uint32_t TM_COLS = 512;
 
 // mbarrier slots (8 bytes each) from Smem::bar
-//   B_FULL / B_EMPTY   per stage: tile landed (TMA transaction bytes) / the MMAs that read it have completed
+//   B_FULL             per stage: tile landed (TMA transaction bytes)
+//   B_EMPTY            per stage, state-only mode: the update that read the tile has completed      (commit)
 //   B_S_DONE           S(c) = Q K^T complete                                   (tcgen05.commit)
 //   B_A_READY          P(c) written AND O free (O(c-1) read out) AND tile c+1 landed   (poly warps + output warps)
 //   B_X_READY          phase 0: phi'(K_0) written; phase c+1: phi'(Q_c) and phi'(K_{c+1}) written   (expansion warps)
 //   B_O_DONE           readout of chunk c complete: O(c) final, phi'(Q_c) consumed   (commit)
-//   B_ST_DONE          state update of chunk c complete                              (commit)
 //   B_STB_READY        bf16 copy of the state after chunk c written (drain warps)
-//   B_PK_FREE[2]       the update that read this phi'(K) buffer has completed        (commit)
+//   B_PK_FREE[2]       state update of chunk c complete (buffer c % NPK, phase c / NPK): its phi'(K) buffer is
+//                      free again, and the state may be drained                     (commit)
+// The MMA thread pays for every commit and every wait with idle tensor cycles, so the main loop has three of each.
 //   B_INIT             carried-in state preloaded (sequence split)      B_FIN   last update complete (state-only mode)
-enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_A_READY, B_X_READY, B_O_DONE, B_ST_DONE, B_STB_READY, B_PK_FREE,
+enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_A_READY, B_X_READY, B_O_DONE, B_STB_READY, B_PK_FREE,
            B_PK_FREE1, B_INIT, B_FIN, B_COUNT };
 
 // P(c) = causal(1 + s/4 + s^2/32), evaluated in bf16x2 (two FMAs per pair), in place over S, for the 32-column
@@ -181,7 +174,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
     for (int i = 0; i < 3; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
     mbar_init(bar(B_S_DONE), 1);
     mbar_init(bar(B_O_DONE), 1);
-    mbar_init(bar(B_ST_DONE), 1);
     // polynomial warps: 4 (one per quadrant), 5 when quadrant 3 is shared by two warps; + 4 output warps
     mbar_init(bar(B_A_READY), 4 + (q3_has_state ? 4 : 5));
     mbar_init(bar(B_X_READY), 4);
@@ -215,7 +207,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   const bool need_q = mode != MODE_SEG_STATE;
   auto issue_tile = [&](int j) {
     const int st = j % NS;
-    if (j >= NS) wait1(B_EMPTY + st, j / NS - 1, 0x100u);
     const uint32_t base = sb + st * lay.stage_bytes;
     const int tok = tok_base + j * C;
     tma::mbar_expect_tx(bar(B_FULL + st), (need_q ? 8192u : 4096u) + (uint32_t)dv * 256u);
@@ -229,13 +220,25 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   // need not test that barrier itself; with two stages the tile is requested only after this arrival, and the MMA
   // thread waits for it where it needs it
   const bool full_via_a = NS >= 3;
-  auto make_p = [&](int c, int p0, int p1, int share) {
+  auto make_p = [&](int c, int p0, int p1, int share, bool producer) {
     wait(B_S_DONE, c, 0x400u);
     fence_after_sync();
+#if K1_EARLY_TMA
+    // S(c) is complete, hence so is P(c-1) V'(c-1), issued before it: the MMAs are done with the stage of chunk
+    // c - 1, and so are the expansion warps (see their loop).  Its refill starts here, ahead of the polynomial.
+    if (producer && lane == 0 && c >= 1 && c + NS - 1 < nchunks) issue_tile(c + NS - 1);
+    __syncwarp();
+#endif
     poly_pieces(tlane, qd, lane, p0, p1, share);
     tmem_st_wait();
     fence_before_sync();
     if (full_via_a && c + 1 < nchunks) wait(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x403u);
+#if !K1_EARLY_TMA
+    // The producer's warp refills the stage of chunk c - 1 after this arrival; the readout of chunk c - 1 was that
+    // stage's last reader.  Waiting for it BEFORE arriving keeps the wait at most one phase behind: the readout
+    // of chunk c cannot complete without this arrival.
+    if (producer && c >= 1) wait(B_O_DONE, c - 1, 0x100u);
+#endif
     __syncwarp();
     if (lane == 0) mbar_arrive(bar(B_A_READY));
   };
@@ -245,7 +248,10 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
     // lane 0 is also the TMA producer
     if (mode == MODE_SEG_STATE) {
       if (warp == W_LOAD && lane == 0)
-        for (int j = 0; j < nchunks; ++j) issue_tile(j);
+        for (int j = 0; j < nchunks; ++j) {
+          if (j >= NS) wait1(B_EMPTY + j % NS, j / NS - 1, 0x100u);   // the update that read tile j - NS is complete
+          issue_tile(j);
+        }
     } else {
       if (warp == W_LOAD && lane == 0)
         for (int j = 0; j < min(NS, nchunks); ++j) issue_tile(j);
@@ -254,10 +260,12 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       const bool shared_q3 = qd == 3 && !q3_has_state;
       const int p0 = shared_q3 ? 2 : 0;
       for (int c = 0; c < nchunks; ++c) {
-        make_p(c, p0, 4, shared_q3 ? 2 : 0);
+        make_p(c, p0, 4, shared_q3 ? 2 : 0, warp == W_LOAD);
         // tile c + NS - 1 replaces tile c - 1, whose last reader was the readout of chunk c - 1
+#if !K1_EARLY_TMA
         if (warp == W_LOAD && lane == 0 && c >= 1 && c + NS - 1 < nchunks) issue_tile(c + NS - 1);
         __syncwarp();
+#endif
       }
     }
   } else if (warp == W_MMA) {
@@ -278,11 +286,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       // U(c): St^T (+)= V'(c)^T phi'(K_c)
       auto issue_update = [&](int c, bool acc0) {
         const uint64_t dv_c = d_v + (c % NS) * stage_units, d_pk_c = d_pk + (c % NPK) * (40960 >> 4);
-#if K1_MMA_UNROLL
 #pragma unroll
-#else
-#pragma unroll 1
-#endif
         for (int j = 0; j < C / 16; ++j)
           mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (acc0 || j > 0) ? 1u : 0u);
       };
@@ -306,7 +310,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
         if (has_init) wait1(B_INIT, 0, 0x207u);            // state^T and its bf16 copy were preloaded
         fence_after_sync();
         issue_update(0, has_init);
-        mma_commit(bar(B_ST_DONE));
         mma_commit(bar(B_PK_FREE + 0));
         for (int c = 0; c < nchunks; ++c) {
           const int st = c % NS;
@@ -315,11 +318,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
           fence_after_sync();
           {
             const uint64_t dv_c = d_v + st * stage_units;
-#if K1_MMA_UNROLL
 #pragma unroll
-#else
-#pragma unroll 1
-#endif
             for (int j = 0; j < C / 16; ++j)
               mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
           }
@@ -339,22 +338,16 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
           fence_after_sync();
           if (c > 0 || has_init) {
             const uint64_t d_stb_c = d_stb + ((c + 1) & 1) * stb_units;
-#if K1_MMA_UNROLL
 #pragma unroll
-#else
-#pragma unroll 1
-#endif
             for (int j = 0; j < DR / 16; ++j)
               mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb_c + stb_step * j, idesc_o_st, 1);
           }
           mma_commit(bar(B_O_DONE));
-          mma_commit(bar(B_EMPTY + st));
           // U(c+1): must not start before the drain of State(c) has read the accumulator
           if (c + 1 < nchunks) {
             wait1(B_STB_READY, c, 0x205u);
             fence_after_sync();
             issue_update(c + 1, true);
-            mma_commit(bar(B_ST_DONE));
             mma_commit(bar(B_PK_FREE + (c + 1) % NPK));
           }
         }
@@ -389,10 +382,8 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       });
       fence_proxy_async();
     };
-    auto expand_q = [&](int c) {
-      wait(B_FULL + c % NS, c / NS, 0x303u);
-      uint32_t X[8];
-      load_x(c, 0, X);
+    // phi'(Q_c) from the raw q held in X (taken from the stage one step earlier, see below)
+    auto expand_q = [&](int c, const uint32_t (&X)[8]) {
       if (c > 0) wait(B_O_DONE, c - 1, 0x301u);  // the previous phi'(Q) has been consumed
       fence_after_sync();
       uint32_t hold[4];
@@ -415,19 +406,21 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
         if (lane == 0) mbar_arrive(bar(B_X_READY));
       }
     } else {
+      // phi'(Q_c) goes first in a step: it only waits for the readout of chunk c - 1, while phi'(K_{c+1}) also needs
+      // tile c + 1, the youngest load in flight.  The raw q of chunk c + 1 is taken into registers BEFORE the arrival
+      // of step c, so that once the MMA thread has seen that arrival nothing on the CUDA cores reads tile c + 1's
+      // q or k any more - the producer relies on it when it refills a stage.
+      uint32_t XQ[8];
       expand_k(0);
+      load_x(0, 0, XQ);
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_X_READY));        // phase 0
       for (int c = 0; c < nchunks; ++c) {
-#if K1_QFIRST
-        // phi'(Q_c) first: it only waits for the readout of chunk c - 1, while phi'(K_{c+1}) also needs tile c + 1,
-        // the youngest load in flight
-        expand_q(c);
-        if (c + 1 < nchunks) expand_k(c + 1);
-#else
-        if (c + 1 < nchunks) expand_k(c + 1);            // does not depend on the readout: runs ahead
-        expand_q(c);
-#endif
+        expand_q(c, XQ);
+        if (c + 1 < nchunks) {
+          expand_k(c + 1);                               // waits for tile c + 1
+          load_x(c + 1, 0, XQ);
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_X_READY));      // phase c + 1
       }
@@ -484,7 +477,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
           }
           __syncwarp();  // the tile is rewritten in the next round
         };
-#if K1_OUT_FAST
         if (n16 == 4) {
           // dv = 64: all of O(c) into registers first, so that the accumulator is free again as early as possible
           uint32_t r0[16], r1[16], r2[16], r3[16];
@@ -495,22 +487,10 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
           tmem_ld_wait();
           free_o();
           inv = 1.0f / (__uint_as_float(dreg) + p.eps);
-#if K1_OUT_DIRECT
-          if (tok_w + lane < L) {
-            uint4* yrow_g = reinterpret_cast<uint4*>(ytok + (int64_t)lane * p.sy.l);
-            uint32_t pk[8];
-            pack16(r0, inv, pk); yrow_g[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]); yrow_g[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-            pack16(r1, inv, pk); yrow_g[2] = make_uint4(pk[0], pk[1], pk[2], pk[3]); yrow_g[3] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-            pack16(r2, inv, pk); yrow_g[4] = make_uint4(pk[0], pk[1], pk[2], pk[3]); yrow_g[5] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-            pack16(r3, inv, pk); yrow_g[6] = make_uint4(pk[0], pk[1], pk[2], pk[3]); yrow_g[7] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-          }
-#else
           round_out(0, true, r0, r1);
           round_out(1, true, r2, r3);
-#endif
           continue;
         }
-#endif
         // y = O[:, :dv] / (O[:, dv] + eps), 32 columns per round.  The loop is kept rolled: this kernel's hot
         // code has to stay inside the SM's instruction cache.
 #pragma unroll 1
@@ -579,7 +559,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       stage_state();
     } else {
       const int share = (qd == 3 && pp1 > 0) ? 1 : 0;
-      if (pp1 > 0) make_p(0, 0, pp1, share);
+      if (pp1 > 0) make_p(0, 0, pp1, share, false);
       if (has_init) {
         // Preload state^T (fp32, TMEM) and its bf16 operand copy (buffer 1) with the sum over the earlier segments.
         const float* src = p.seg_state + ((size_t)bh * (p.nseg - 1) + (seg - 1)) * (size_t)((dv + 1) * DR) + (size_t)t * DR;
@@ -607,7 +587,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       for (int c = 0; c < nchunks; ++c) {
         const bool last = c + 1 == nchunks;
         // ---- state after chunk c: fp32 TMEM -> bf16 smem operand (buffer c & 1), or fp32 staging at the end ----
-        wait(B_ST_DONE, c, 0x402u);
+        wait(B_PK_FREE + c % NPK, c / NPK, 0x402u);   // the state update of chunk c is complete
         fence_after_sync();
         if (!last) {
           if (my_rows) {
@@ -632,7 +612,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
           fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(B_STB_READY));
-          if (pp1 > 0) make_p(c + 1, 0, pp1, share);
+          if (pp1 > 0) make_p(c + 1, 0, pp1, share, false);
         } else if (write_state) {
           wait(B_FIN, 0, 0x404u);   // the last chunk's P V' and readout still read the stages and the operand buffers
           fence_after_sync();
