@@ -77,14 +77,17 @@ constexpr uint32_t TM_COLS = 512;
 //   B_EMPTY            per stage, state-only mode: the update that read the tile has completed      (commit)
 //   B_S_DONE           S(c) = Q K^T complete                                   (tcgen05.commit)
 //   B_A_READY          P(c) written AND O free (O(c-1) read out) AND tile c+1 landed   (poly warps + output warps)
-//   B_X_READY          phase 0: phi'(K_0) written; phase c+1: phi'(Q_c) and phi'(K_{c+1}) written   (expansion warps)
+//   B_XQ_READY         phi'(Q_c) written (phase c)                                   (expansion warps)
+//   B_XK_READY[2]      phi'(K_c) written, and the raw q of chunk c taken into registers (buffer c % NPK, phase
+//                      c / NPK: one barrier per phi'(K) buffer, because the expansion warps may run a whole
+//                      buffer ahead of the MMA thread and a waiter must never fall two phases behind)
 //   B_O_DONE           readout of chunk c complete: O(c) final, phi'(Q_c) consumed   (commit)
 //   B_STB_READY        bf16 copy of the state after chunk c written (drain warps)
 //   B_PK_FREE[2]       state update of chunk c complete (buffer c % NPK, phase c / NPK): its phi'(K) buffer is
 //                      free again, and the state may be drained                     (commit)
 // The MMA thread pays for every commit and every wait with idle tensor cycles, so the main loop has three of each.
 //   B_INIT             carried-in state preloaded (sequence split)      B_FIN   last update complete (state-only mode)
-enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_A_READY, B_X_READY, B_O_DONE, B_STB_READY, B_PK_FREE,
+enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_A_READY, B_XQ_READY, B_XK_READY, B_XK_READY1, B_O_DONE, B_STB_READY, B_PK_FREE,
            B_PK_FREE1, B_INIT, B_FIN, B_COUNT };
 
 // P(c) = causal(1 + s/4 + s^2/32), evaluated in bf16x2 (two FMAs per pair), in place over S, for the 32-column
@@ -176,7 +179,9 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
     mbar_init(bar(B_O_DONE), 1);
     // polynomial warps: 4 (one per quadrant), 5 when quadrant 3 is shared by two warps; + 4 output warps
     mbar_init(bar(B_A_READY), 4 + (q3_has_state ? 4 : 5));
-    mbar_init(bar(B_X_READY), 4);
+    mbar_init(bar(B_XQ_READY), 4);
+    mbar_init(bar(B_XK_READY), 4);
+    mbar_init(bar(B_XK_READY1), 4);
     mbar_init(bar(B_STB_READY), 4);
     mbar_init(bar(B_PK_FREE), 1);
     mbar_init(bar(B_PK_FREE + 1), 1);
@@ -294,7 +299,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
         // state only: St += V'(c)^T phi'(K_c) for every chunk of the segment
         for (int c = 0; c < nchunks; ++c) {
           wait1(B_FULL + c % NS, c / NS, 0x210u);
-          wait1(B_X_READY, c, 0x211u);
+          wait1(B_XK_READY + c % NPK, c / NPK, 0x211u);
           fence_after_sync();
           issue_update(c, c > 0);
           mma_commit(bar(B_EMPTY + c % NS));
@@ -306,7 +311,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
         fence_after_sync();
         mma_ss(tmem + TM_S, d_q, d_k, idesc_s, 0);
         mma_commit(bar(B_S_DONE));
-        wait1(B_X_READY, 0, 0x208u);                       // phi'(K_0)
+        wait1(B_XK_READY, 0, 0x208u);                      // phi'(K_0)
         if (has_init) wait1(B_INIT, 0, 0x207u);            // state^T and its bf16 copy were preloaded
         fence_after_sync();
         issue_update(0, has_init);
@@ -334,7 +339,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
           }
           // R(c): O(c) += phi'(Q_c) State(c-1).  The bf16 state of chunk c-1 sits in buffer (c-1) & 1 and was
           // awaited before U(c) was issued (see below); a carried-in state was preloaded into buffer 1.
-          wait1(B_X_READY, c + 1, 0x204u);                 // phi'(Q_c) and phi'(K_{c+1})
+          wait1(B_XQ_READY, c, 0x204u);                    // phi'(Q_c)
           fence_after_sync();
           if (c > 0 || has_init) {
             const uint64_t d_stb_c = d_stb + ((c + 1) & 1) * stb_units;
@@ -346,6 +351,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
           // U(c+1): must not start before the drain of State(c) has read the accumulator
           if (c + 1 < nchunks) {
             wait1(B_STB_READY, c, 0x205u);
+            wait1(B_XK_READY + (c + 1) % NPK, (c + 1) / NPK, 0x206u);   // phi'(K_{c+1})
             fence_after_sync();
             issue_update(c + 1, true);
             mma_commit(bar(B_PK_FREE + (c + 1) % NPK));
@@ -403,26 +409,30 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       for (int c = 0; c < nchunks; ++c) {
         expand_k(c);
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_X_READY));
+        if (lane == 0) mbar_arrive(bar(B_XK_READY + c % NPK));
       }
     } else {
-      // phi'(Q_c) goes first in a step: it only waits for the readout of chunk c - 1, while phi'(K_{c+1}) also needs
-      // tile c + 1, the youngest load in flight.  The raw q of chunk c + 1 is taken into registers BEFORE the arrival
-      // of step c, so that once the MMA thread has seen that arrival nothing on the CUDA cores reads tile c + 1's
-      // q or k any more - the producer relies on it when it refills a stage.
+      // phi'(Q_c) goes first in a step and is announced on its own: it only waits for the readout of chunk c - 1, and
+      // the readout of chunk c needs nothing else from these warps, while phi'(K_{c+1}) also needs tile c + 1, the
+      // youngest load in flight, and is only needed by the state update at the end of the MMA thread's step.  The
+      // raw q of chunk c + 1 is taken into registers BEFORE the arrival for phi'(K_{c+1}), so that once the MMA
+      // thread has seen that arrival nothing on the CUDA cores reads tile c + 1's q or k any more - the producer
+      // relies on it when it refills a stage.
       uint32_t XQ[8];
       expand_k(0);
       load_x(0, 0, XQ);
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_X_READY));        // phase 0
+      if (lane == 0) mbar_arrive(bar(B_XK_READY));
       for (int c = 0; c < nchunks; ++c) {
         expand_q(c, XQ);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_XQ_READY));
         if (c + 1 < nchunks) {
           expand_k(c + 1);                               // waits for tile c + 1
           load_x(c + 1, 0, XQ);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_XK_READY + (c + 1) % NPK));
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_X_READY));      // phase c + 1
       }
     }
   } else if (warp >= W_OUT && warp < W_MMA) {
