@@ -34,10 +34,6 @@ __device__ unsigned int g_tc_status = 0;  // ORed with a code when a bounded wai
 // written earlier in the same call, so nothing here has to start at zero.
 static __device__ __align__(256) unsigned char g_static_scratch[BASED_STATIC_SCRATCH_BYTES];
 
-
-#ifndef K1_EARLY_TMA
-#define K1_EARLY_TMA 1
-#endif
 namespace {
 
 using namespace tc;
@@ -45,16 +41,18 @@ using namespace tcp;
 
 
 // Shared memory map (bytes).  One stage = Q [2 k-halves][128 tok][16 B] K-major (4096) + K (4096) +
-// V' MN-major [NV/8 groups of 8 columns][128 tok][16 B].  The state-update MMA reads V'^T as an
-// M = 128 operand, i.e. 16 column groups from the stage's V' base; the groups past NV/8 are
-// whatever follows in shared memory and only feed accumulator lanes >= NV, which nobody reads.
+// V' MN-major [dv/8 + 1 groups of 8 columns][128 tok][16 B]: the columns of V, then the group that starts with
+// the ones column.  The MMAs address NV/8 = dv/8 + 2 groups (N must be a multiple of 16) and the state-update
+// MMA reads V'^T as an M = 128 operand, i.e. 16 groups from the stage's V' base: the groups past dv/8 + 1 are
+// whatever follows in shared memory.  They only feed accumulator columns / lanes > dv + 8 of O and of the
+// state, which nobody reads (a column of an MMA result depends on that column of its B operand alone).
 struct Smem {
   int nstage, npk, stage_bytes, phik, stb, stb_bytes, ystage, yrow_bytes, bar, total;
   __host__ __device__ explicit Smem(int dv) {
     const int nv = dv + 16;
     nstage = dv <= 64 ? 3 : 2;     // what fits in 227 KB
     npk = dv <= 64 ? 2 : 1;        // phi'(K) buffers
-    stage_bytes = 8192 + (nv >> 3) * 2048;
+    stage_bytes = 8192 + ((dv >> 3) + 1) * 2048;
     phik = nstage * stage_bytes;   // npk x 40960  MN-major [20 groups of 8 feats][128 tok][16 B]
     stb = phik + npk * 40960;      // 2 x stb_bytes: bf16 state, K-major [20 k-units][NV rows][16 B], double-buffered
     stb_bytes = nv * 320;
@@ -67,9 +65,13 @@ struct Smem {
 
 // TMEM columns (32-bit each), 512 allocated
 constexpr uint32_t TM_ST = 0;     // state^T accumulator: lanes = V' column, 160 feature columns, fp32
-constexpr uint32_t TM_S = 160;    // S fp32 (128 cols), overwritten in place by P bf16 (64 cols)
+constexpr uint32_t TM_S = 160;    // S fp32 (128 cols); with NV > 80 overwritten in place by P bf16 (64 cols)
 constexpr uint32_t TM_O = 288;    // O accumulator, NV <= 128 columns
-constexpr uint32_t TM_PQ = 416;   // phi'(Q) bf16, 80 columns
+constexpr uint32_t TM_PQ = 416;   // phi'(Q) bf16, 80 columns (NV > 80)
+// With NV <= 80 (dv <= 64) the O accumulator leaves room for P in columns of its own, 368-431, and phi'(Q) moves
+// to 432-511: the pieces of P right of the diagonal, which are zeros, are then written once instead of once per
+// chunk (S(c+1) no longer overwrites them), and P's stores cannot land on S columns another warp has yet to read.
+constexpr uint32_t TM_P_SEP = 368, TM_PQ_SEP = 432;
 constexpr uint32_t TM_COLS = 512;
 
 // mbarrier slots (8 bytes each) from Smem::bar
@@ -99,7 +101,8 @@ enum Bar { B_FULL = 0, B_EMPTY = 3, B_S_DONE = 6, B_A_READY, B_XQ_READY, B_XK_RE
 // second waits there before its first store (share == 2).
 // A function of its own, not inlined: two roles call it, and the kernel's hot code has to stay inside the SM's
 // instruction cache.
-__device__ __noinline__ void poly_pieces(uint32_t tlane, int qd, int lane, int p0, int p1, int share) {
+__device__ __noinline__ void poly_pieces(uint32_t tlane, uint32_t tm_p, bool zeros, int qd, int lane, int p0, int p1,
+                                         int share) {
   constexpr uint32_t k1 = 0x3F803F80u, kq = 0x3E803E80u, k32 = 0x3D003D00u;  // (1,1) (1/4,1/4) (1/32,1/32)
 #pragma unroll 1
   for (int piece = p0; piece < p1; ++piece) {
@@ -124,12 +127,12 @@ __device__ __noinline__ void poly_pieces(uint32_t tlane, int qd, int lane, int p
         }
       }
       if (share == 2 && piece == p0) asm volatile("bar.sync 1, 64;\n" ::: "memory");
-      tmem_st16(tlane + TM_S + piece * 16, pk);
-    } else {
+      tmem_st16(tlane + tm_p + piece * 16, pk);
+    } else if (zeros) {
       uint32_t z[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) z[i] = 0;
-      tmem_st16(tlane + TM_S + piece * 16, z);
+      tmem_st16(tlane + tm_p + piece * 16, z);
     }
   }
 }
@@ -139,9 +142,18 @@ __device__ __noinline__ void poly_pieces(uint32_t tlane, int qd, int lane, int p
 //   S(c+1)                                     1 MMA   M128 N128  K16
 //   R(c):   O += phi'(Q_c) State(c-1)          10 MMAs M128 N=NV  K16   A = phi'(Q) in TMEM, B = bf16 state (smem)
 //   U(c+1): St^T += V'(c+1)^T phi'(K_{c+1})    8 MMAs  M128 N160  K16   (the state update runs ONE CHUNK AHEAD)
-// so that the output warps read O(c) while U(c+1) keeps the tensor pipe busy, the polynomial of chunk c+1 and
-// the expansions run under PV / R, and the only chain carried from chunk to chunk is
+// so that the output warps read O(c) while U(c+1) keeps the tensor pipe busy, the polynomial of chunk c+1 runs
+// under R(c) and U(c+1), the expansions run a step ahead, and the only chain carried from chunk to chunk is
 // U(c) -> drain (fp32 state -> bf16 operand) -> U(c+1): the drain reads the accumulator that U(c+1) writes.
+//
+// Two properties of the SM shaped the code as much as the schedule did:
+//  * The 16 warps run five different programs, and what they execute per chunk has to stay inside the SM's
+//    instruction cache: misses go to a cache shared by all SMs of a GPC, and with every SM running this kernel
+//    that cache saturates - the same CTA ran 1.6x slower with 128 CTAs on the chip than with 16.  Hence the rolled
+//    output rounds, the polynomial as one function shared by its two callers, and no variant code in the loops.
+//  * The MMA thread's own instructions between two MMAs are idle tensor time (an issue blocks until the pipe
+//    accepts it, so the thread cannot run ahead): its MMA loops are unrolled and it has three waits and three
+//    commits per chunk.
 __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_constant__ Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = smem_u32(smem);
@@ -192,11 +204,11 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TM_COLS);
-  // V' column groups dv/8 (ones column) and dv/8 + 1 (zeros) are constant for the whole kernel.
-  for (int i = tid; i < NS * 2 * C; i += NT) {
-    const int st = i / (2 * C), r = i - st * 2 * C, g = r / C, tk = r - g * C;
-    const uint4 val = g == 0 ? make_uint4(0x00003F80u, 0, 0, 0) : make_uint4(0, 0, 0, 0);  // bf16 1.0 in element 0
-    *reinterpret_cast<uint4*>(smem + st * lay.stage_bytes + 8192 + ((dv >> 3) + g) * 2048 + tk * 16) = val;
+  // V' column group dv/8 (the ones column, then zeros) is constant for the whole kernel.
+  for (int i = tid; i < NS * C; i += NT) {
+    const int st = i / C, tk = i - st * C;
+    *reinterpret_cast<uint4*>(smem + st * lay.stage_bytes + 8192 + (dv >> 3) * 2048 + tk * 16) =
+        make_uint4(0x00003F80u, 0, 0, 0);  // bf16 1.0 in element 0
   }
   fence_proxy_async();
   fence_before_sync();
@@ -225,25 +237,19 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   // need not test that barrier itself; with two stages the tile is requested only after this arrival, and the MMA
   // thread waits for it where it needs it
   const bool full_via_a = NS >= 3;
+  const bool p_separate = NV <= 80;
+  const uint32_t tm_p = p_separate ? TM_P_SEP : TM_S, tm_pq = p_separate ? TM_PQ_SEP : TM_PQ;
   auto make_p = [&](int c, int p0, int p1, int share, bool producer) {
     wait(B_S_DONE, c, 0x400u);
     fence_after_sync();
-#if K1_EARLY_TMA
     // S(c) is complete, hence so is P(c-1) V'(c-1), issued before it: the MMAs are done with the stage of chunk
     // c - 1, and so are the expansion warps (see their loop).  Its refill starts here, ahead of the polynomial.
     if (producer && lane == 0 && c >= 1 && c + NS - 1 < nchunks) issue_tile(c + NS - 1);
     __syncwarp();
-#endif
-    poly_pieces(tlane, qd, lane, p0, p1, share);
+    poly_pieces(tlane, tm_p, !p_separate || c == 0, qd, lane, p0, p1, share);
     tmem_st_wait();
     fence_before_sync();
     if (full_via_a && c + 1 < nchunks) wait(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x403u);
-#if !K1_EARLY_TMA
-    // The producer's warp refills the stage of chunk c - 1 after this arrival; the readout of chunk c - 1 was that
-    // stage's last reader.  Waiting for it BEFORE arriving keeps the wait at most one phase behind: the readout
-    // of chunk c cannot complete without this arrival.
-    if (producer && c >= 1) wait(B_O_DONE, c - 1, 0x100u);
-#endif
     __syncwarp();
     if (lane == 0) mbar_arrive(bar(B_A_READY));
   };
@@ -266,11 +272,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       const int p0 = shared_q3 ? 2 : 0;
       for (int c = 0; c < nchunks; ++c) {
         make_p(c, p0, 4, shared_q3 ? 2 : 0, warp == W_LOAD);
-        // tile c + NS - 1 replaces tile c - 1, whose last reader was the readout of chunk c - 1
-#if !K1_EARLY_TMA
-        if (warp == W_LOAD && lane == 0 && c >= 1 && c + NS - 1 < nchunks) issue_tile(c + NS - 1);
-        __syncwarp();
-#endif
       }
     }
   } else if (warp == W_MMA) {
@@ -325,7 +326,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
             const uint64_t dv_c = d_v + st * stage_units;
 #pragma unroll
             for (int j = 0; j < C / 16; ++j)
-              mma_ts(tmem + TM_O, tmem + TM_S + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
+              mma_ts(tmem + TM_O, tmem + tm_p + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
           }
           // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
           if (c + 1 < nchunks) {
@@ -345,7 +346,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
             const uint64_t d_stb_c = d_stb + ((c + 1) & 1) * stb_units;
 #pragma unroll
             for (int j = 0; j < DR / 16; ++j)
-              mma_ts(tmem + TM_O, tmem + TM_PQ + 8 * j, d_stb_c + stb_step * j, idesc_o_st, 1);
+              mma_ts(tmem + TM_O, tmem + tm_pq + 8 * j, d_stb_c + stb_step * j, idesc_o_st, 1);
           }
           mma_commit(bar(B_O_DONE));
           // U(c+1): must not start before the drain of State(c) has read the accumulator
@@ -399,7 +400,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
           hold[0] = w0; hold[1] = w1; hold[2] = w2; hold[3] = w3;
         } else {
           const uint32_t r[8] = {hold[0], hold[1], hold[2], hold[3], w0, w1, w2, w3};
-          tmem_st8(tlane + TM_PQ + 4 * (g - 1), r);
+          tmem_st8(tlane + tm_pq + 4 * (g - 1), r);
         }
       });
       tmem_st_wait();
