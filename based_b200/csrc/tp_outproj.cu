@@ -29,7 +29,7 @@ __device__ unsigned int g_tp_status = 0;  // ORed with a code when a bounded wai
 
 namespace {
 
-constexpr int WARPS = 4;
+constexpr int WARPS = 8;     // the K slice of a rank is split over the warps: one round of loads in flight per warp
 constexpr int kMaxWorld = 8;
 constexpr int kCtrlBytes = 256;
 
@@ -58,6 +58,11 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ unsigned int ld_relaxed_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 // data written by a peer: read past L1 (a line of the previous use of this buffer may still sit there)
 __device__ __forceinline__ float2 ld_peer_written(const float* p) {
   float2 v;
@@ -84,8 +89,13 @@ __global__ void __launch_bounds__(WARPS * 32) tp_outproj_allreduce_kernel(const 
   const int mtiles = (p.M + 15) >> 4;
   unsigned char* my_ws = p.ws[rank];
   unsigned int* ctrl = reinterpret_cast<unsigned int*>(my_ws);
-  // the epoch of this call: written by the last block of the previous launch (1 after the workspace was prepared)
-  const unsigned int epoch = ld_acquire_sys(ctrl);
+  // The epoch of this call: written by the last block of the previous launch on this GPU (1 after the workspace was
+  // prepared), so the kernel boundary already orders it.  ONE thread reads it: an acquire at system scope by every
+  // thread of every block costs each warp a system-wide fence, and those queue up per SM.
+  __shared__ unsigned int s_epoch;
+  if (threadIdx.x == 0) s_epoch = ld_relaxed_sys(ctrl);
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
   const int parity = epoch & 1u;
 
   // ---- partial products of this rank: all rows, columns n0..n0+7, over the rank's K slice (split over the warps)
@@ -128,90 +138,100 @@ __global__ void __launch_bounds__(WARPS * 32) tp_outproj_allreduce_kernel(const 
     }
   }
   __shared__ float red[WARPS][kMaxRowTiles][4][32];
+  __shared__ int s_ok;
 #pragma unroll
   for (int m = 0; m < kMaxRowTiles; ++m)
 #pragma unroll
     for (int e = 0; e < 4; ++e) red[warp][m][e][lane] = acc[m][e];
+  if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
-  if (warp == 0) {
+  // From here warp m owns row tile m (rows 16m .. 16m+15) of the block's 8 columns: the four warps push, wait and
+  // add side by side, so the chain of NVLink round trips a block goes through is as short as one tile's.
+  static_assert(kMaxRowTiles <= WARPS, "one warp per row tile");
+  const int m = warp < kMaxRowTiles ? warp : 0;
+  const bool have = warp < kMaxRowTiles && warp < mtiles;
+  float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int m = 0; m < kMaxRowTiles; ++m)
+  for (int e = 0; e < 4; ++e) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) s += red[w][m][e][lane];
-        acc[m][e] = s;
-      }
-    // this lane holds, per row tile m, rows 16m + g (acc 0, 1) and 16m + g + 8 (acc 2, 3), columns c0 and c0 + 1
-    const int c0 = n0 + 2 * t;
-    const size_t doff = data_offset(p.world, tiles);
-    const size_t slab = (size_t)p.Mmax * p.N;                               // floats per (parity, src rank)
-    const size_t my_slab = ((size_t)parity * p.world + rank) * slab;
-    // ---- push the tile column into every rank's receive buffer (own included), then publish its flag there
-    for (int d = 0; d < p.world; ++d) {
-      const int dst = (rank + d) % p.world;                                  // spread the first stores over the peers
-      float* data = reinterpret_cast<float*>(p.ws[dst] + doff) + my_slab;
-#pragma unroll
-      for (int m = 0; m < kMaxRowTiles; ++m) {
-        const int r0 = 16 * m + g, r1 = r0 + 8;
-        if (r0 < p.M) *reinterpret_cast<float2*>(data + (size_t)r0 * p.N + c0) = make_float2(acc[m][0], acc[m][1]);
-        if (r1 < p.M) *reinterpret_cast<float2*>(data + (size_t)r1 * p.N + c0) = make_float2(acc[m][2], acc[m][3]);
-      }
-    }
-    __threadfence_system();
-    __syncwarp();
-    if (lane < p.world) {
-      const int dst = (rank + lane) % p.world;
-      unsigned int* flags = reinterpret_cast<unsigned int*>(p.ws[dst] + flags_offset());
-      st_release_sys(flags + ((size_t)parity * p.world + rank) * tiles + tile, epoch);
-    }
-    // ---- wait for this tile column from every rank (lane s watches source rank s), bounded
-    bool ok = true;
-    if (lane < p.world) {
-      const unsigned int* flag =
-          reinterpret_cast<const unsigned int*>(my_ws + flags_offset()) + ((size_t)parity * p.world + lane) * tiles + tile;
-      if (ld_acquire_sys(flag) != epoch) {
-        const long long t0 = clock64();
-        while (ld_acquire_sys(flag) != epoch) {
-          if (clock64() - t0 > p.max_wait_cycles) {
-            ok = false;
-            if (p.status) atomicOr(p.status, 0x1000u | (unsigned)lane);
-            break;
-          }
-          __nanosleep(64);
+    for (int w = 0; w < WARPS; ++w) part[e] += red[w][m][e][lane];
+  }
+  // this lane holds rows 16m + g (part 0, 1) and 16m + g + 8 (part 2, 3), columns c0 and c0 + 1
+  const int c0 = n0 + 2 * t;
+  const int r0 = 16 * m + g, r1 = r0 + 8;
+  const bool v0 = have && r0 < p.M, v1 = have && r1 < p.M;
+  const size_t doff = data_offset(p.world, tiles);
+  const size_t slab = (size_t)p.Mmax * p.N;                               // floats per (parity, src rank)
+  const size_t my_slab = ((size_t)parity * p.world + rank) * slab;
+  // ---- push the tile column into every rank's receive buffer (own included), then publish its flag there
+  for (int d = 0; d < p.world; ++d) {
+    const int dst = (rank + d) % p.world;                                  // spread the first stores over the peers
+    float* data = reinterpret_cast<float*>(p.ws[dst] + doff) + my_slab;
+    if (v0) *reinterpret_cast<float2*>(data + (size_t)r0 * p.N + c0) = make_float2(part[0], part[1]);
+    if (v1) *reinterpret_cast<float2*>(data + (size_t)r1 * p.N + c0) = make_float2(part[2], part[3]);
+  }
+  // The block's stores are ordered before the flags by the barrier (all threads) followed by ONE release at system
+  // scope per flag (release is cumulative over what the barrier ordered before it): a system-wide fence by every
+  // thread instead cost 6 us per call.
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    const int lane_rank = threadIdx.x;
+    const int dst = (rank + lane_rank) % p.world;
+    unsigned int* flags = reinterpret_cast<unsigned int*>(p.ws[dst] + flags_offset());
+    st_release_sys(flags + ((size_t)parity * p.world + rank) * tiles + tile, epoch);
+    // ---- wait for this tile column from every rank (thread s watches source rank s), bounded:
+    // relaxed polls (a load each), then ONE acquire that orders the reads of the partials behind the flag
+    const unsigned int* flag =
+        reinterpret_cast<const unsigned int*>(my_ws + flags_offset()) + ((size_t)parity * p.world + lane_rank) * tiles + tile;
+    if (ld_relaxed_sys(flag) != epoch) {
+      const long long t0 = clock64();
+      while (ld_relaxed_sys(flag) != epoch) {
+        if (clock64() - t0 > p.max_wait_cycles) {
+          s_ok = 0;
+          if (p.status) atomicOr(p.status, 0x1000u | (unsigned)lane_rank);
+          break;
         }
+        __nanosleep(32);
       }
     }
-    ok = __all_sync(0xffffffffu, ok);
-    // ---- sum the partials in rank order, add the bias, round once
-    const float* mine = reinterpret_cast<const float*>(my_ws + doff) + (size_t)parity * p.world * slab;
-    float b0 = 0.f, b1 = 0.f;
-    if (p.bias) { b0 = __bfloat162float(p.bias[c0]); b1 = __bfloat162float(p.bias[c0 + 1]); }
-    __nv_bfloat16* out = p.out[slot];
+    (void)ld_acquire_sys(flag);
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+  // ---- sum the partials in rank order (all loads first, then the adds), add the bias, round once
+  const float* mine = reinterpret_cast<const float*>(my_ws + doff) + (size_t)parity * p.world * slab;
+  float2 in0[kMaxWorld], in1[kMaxWorld];
 #pragma unroll
-    for (int m = 0; m < kMaxRowTiles; ++m) {
-      const int r0 = 16 * m + g, r1 = r0 + 8;
-      float s[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int src = 0; src < p.world; ++src) {
-        const float* data = mine + (size_t)src * slab;
-        if (r0 < p.M) { const float2 a = ld_peer_written(data + (size_t)r0 * p.N + c0); s[0] += a.x; s[1] += a.y; }
-        if (r1 < p.M) { const float2 a = ld_peer_written(data + (size_t)r1 * p.N + c0); s[2] += a.x; s[3] += a.y; }
-      }
-      s[0] += b0; s[1] += b1; s[2] += b0; s[3] += b1;
-      if (!ok) { s[0] = s[1] = s[2] = s[3] = __int_as_float(0x7fc00000); }   // a partial never came: NaN, not a silent sum
-      if (r0 < p.M) *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)r0 * p.so + c0) = __floats2bfloat162_rn(s[0], s[1]);
-      if (r1 < p.M) *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)r1 * p.so + c0) = __floats2bfloat162_rn(s[2], s[3]);
+  for (int src = 0; src < kMaxWorld; ++src) {
+    in0[src] = make_float2(0.f, 0.f);
+    in1[src] = make_float2(0.f, 0.f);
+    if (src < p.world) {
+      const float* data = mine + (size_t)src * slab;
+      if (v0) in0[src] = ld_peer_written(data + (size_t)r0 * p.N + c0);
+      if (v1) in1[src] = ld_peer_written(data + (size_t)r1 * p.N + c0);
     }
-    // ---- the last block of this rank's launch advances the epoch for the next call
-    if (lane == 0) {
-      __threadfence();
-      const unsigned int done = atomicAdd(ctrl + 1, 1u);
-      if (done == (unsigned)tiles - 1) {
-        ctrl[1] = 0;
-        __threadfence();
-        st_release_sys(ctrl, epoch + 1u);
-      }
+  }
+  float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int src = 0; src < kMaxWorld; ++src) {
+    if (src < p.world) { sum[0] += in0[src].x; sum[1] += in0[src].y; sum[2] += in1[src].x; sum[3] += in1[src].y; }
+  }
+  if (p.bias) {
+    const float b0 = __bfloat162float(p.bias[c0]), b1 = __bfloat162float(p.bias[c0 + 1]);
+    sum[0] += b0; sum[1] += b1; sum[2] += b0; sum[3] += b1;
+  }
+  if (!ok) { sum[0] = sum[1] = sum[2] = sum[3] = __int_as_float(0x7fc00000); }   // a partial never came: NaN, not a silent sum
+  __nv_bfloat16* out = p.out[slot];
+  if (v0) *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)r0 * p.so + c0) = __floats2bfloat162_rn(sum[0], sum[1]);
+  if (v1) *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)r1 * p.so + c0) = __floats2bfloat162_rn(sum[2], sum[3]);
+  // ---- the last block of this rank's launch advances the epoch for the next call
+  __syncthreads();
+  // (nothing of this block has to be ordered before the count: the next launch starts after this one has ended)
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(ctrl + 1, 1u);
+    if (done == (unsigned)tiles - 1) {
+      ctrl[1] = 0;
+      st_release_sys(ctrl, epoch + 1u);
     }
   }
 }
