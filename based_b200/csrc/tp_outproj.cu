@@ -23,6 +23,8 @@
 // call e (it needs their tiles of call e + 1, pushed by kernels that run after their call e).
 #include "common.cuh"
 
+#include <mutex>
+
 namespace based {
 
 __device__ unsigned int g_tp_status = 0;  // ORed with a code when a bounded wait expires
@@ -282,15 +284,33 @@ int launch_tp_outproj_allreduce(const void* const* x, const void* const* w, cons
   p.M = M; p.N = N; p.K = K; p.Mmax = Mmax; p.world = world; p.rank = rank; p.emulate = emulate ? 1 : 0;
   p.sx = sx; p.so = so;
   p.max_wait_cycles = 2000000000LL;
-  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_tp_status);
+  // Once per device: the status word's address, the SM count and how many blocks of this kernel an SM holds.
+  constexpr int kMaxDevices = 64;
+  struct DeviceInfo { bool done = false; unsigned int* status = nullptr; int sms = 0, per_sm = 0; };
+  static std::mutex mu;
+  static DeviceInfo info[kMaxDevices];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return BASED_ERR_TOO_LARGE;
+  int sms = 0, per_sm = 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    DeviceInfo& di = info[dev];
+    if (!di.done) {
+      if ((e = cudaGetSymbolAddress(reinterpret_cast<void**>(&di.status), g_tp_status)) != cudaSuccess) return (int)e;
+      if ((e = cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+      if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&di.per_sm, tp_outproj_allreduce_kernel, WARPS * 32, 0)) !=
+          cudaSuccess)
+        return (int)e;
+      di.done = true;
+    }
+    p.status = di.status;
+    sms = di.sms;
+    per_sm = di.per_sm;
+  }
   const dim3 grid(N / 8, 1, sets);
   // Blocks wait for blocks of other ranks that handle the same tile: every block of the launch must be resident.
-  int dev = 0, sms = 0, per_sm = 0;
-  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
-  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
-  if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tp_outproj_allreduce_kernel, WARPS * 32, 0)) != cudaSuccess)
-    return (int)e;
   if ((long long)grid.x * grid.y * grid.z > (long long)per_sm * sms) return BASED_ERR_TOO_LARGE;
   if (emulate) {
     // several ranks inside one launch wait on one another: co-residency must be guaranteed, not just likely

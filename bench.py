@@ -612,7 +612,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
     K, W, pool = args.steps, args.warmup, 16
-    PREROLL = 200   # untimed steps before the warm-up: brings clocks and caches to their loaded state
+    PREROLL = 2000  # untimed steps before the warm-up (0.2 s): brings clocks and caches to their loaded state
 
     def barrier():
         if world > 1:
@@ -631,12 +631,15 @@ def main():
             for i in range(n):
                 ops.linattn_decode(q[i % pool], k[i % pool], v[i % pool], kv, ks, out=y)
 
-        steps(PREROLL)
-        steps(W)
+        # The clock sampler (a child process) is started BEFORE the untimed steps, so that nothing but the barrier
+        # and the synchronize stands between the warm-up and the timed region: a GPU left idle while a process is
+        # spawned starts the region from its idle state, which a 2 ms region feels.
         sampler = ClockSampler(local_rank) if rank == 0 else None
-        barrier()
         if sampler:
             sampler.start()
+        steps(PREROLL)
+        steps(W)
+        barrier()
         times = []
         for r in range(regions):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -739,7 +742,8 @@ def main():
             "repeats": {"regions": len(times), "steps_per_region": K, "what": "the same K-step region run again; "
                         "ms per step, slowest rank's median, and every rank's (median, min, max)",
                         "ms_per_step_median": med, "frac_at_median": DEC_BYTES_PER_UNIT * Bd * H / (med * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                        "per_rank_ms_per_step": allr},
+                        "per_rank_ms_per_step": allr,
+                        "first_regions_ms_per_step": [t / K for t in times[:6]]},
             "e2e": {"value": world * Bd * Ke / (ms_e2e * 1e-3), "unit": "tok/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ke},
             "gpu_launches": K,
