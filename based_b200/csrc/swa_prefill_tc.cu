@@ -134,8 +134,10 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
     if (lo > hi) return 0u;
     return (0xFFFFFFFFu << lo) & (0xFFFFFFFFu >> (31 - hi));
   };
-  // one probability pair -> bf16x2, and what the MMA will see of it added to the normaliser
-  float sum = 0.f;
+  // one probability pair -> bf16x2, and what the MMA will see of it added to the normaliser.  The row is one
+  // thread's work, and a tile's life is mostly this thread's dependent chain: the running maximum and the running
+  // sum are kept in four independent lanes each, so that neither is a chain of 96 dependent operations.
+  float sum4[4] = {0.f, 0.f, 0.f, 0.f};
   auto exp_piece = [&](const uint32_t (&r)[32], uint32_t mask, float msc, int pc) {
     uint32_t pk[16];
 #pragma unroll
@@ -150,14 +152,15 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
       }
       pk[i] = pack_bf16(e[0], e[1]);
       // the normaliser sums what the MMA will see: the bf16-rounded probabilities
-      sum += __uint_as_float(pk[i] << 16) + __uint_as_float(pk[i] & 0xffff0000u);
+      sum4[i & 3] += __uint_as_float(pk[i] << 16) + __uint_as_float(pk[i] & 0xffff0000u);
     }
     tmem_st16(tlane + TM_S + ((c_lo + 32 * pc) >> 1), pk);
   };
   auto max_piece = [&](const uint32_t (&r)[32], uint32_t mask, float m) {
+    float m4[4] = {m, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int i = 0; i < 32; ++i) m = fmaxf(m, (mask & (1u << i)) ? __uint_as_float(r[i]) : -INFINITY);
-    return m;
+    for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], (mask & (1u << i)) ? __uint_as_float(r[i]) : -INFINITY);
+    return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
   };
   if (npieces <= 3) {
     // window <= 64: the row's 96 scores stay in registers between the max and the exponentials, so S is read from
@@ -224,12 +227,10 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
     // Each thread writes its normalised row into the output tile (Q's space, free since S was
     // computed) in the 128-byte-swizzled layout; one thread then hands the tile to the TMA unit,
     // which clips rows past the end of the sequence.
-    const float inv = 1.0f / sum;
+    const float inv = 1.0f / ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
     const int t = tid;
-    for (int i = 0; i < (hd >> 4); ++i) {
-      uint32_t r[16];
-      tmem_ld16(tlane + TM_O + 16 * i, r);
-      tmem_ld_wait();
+    // four 16-column pieces per round: their TMEM loads are in flight together
+    auto put = [&](int i, const uint32_t (&r)[16]) {
       uint4 lo, hi;
       lo.x = pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
       lo.y = pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
@@ -242,6 +243,19 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
       uint8_t* atom = smem + SM_Q + (i >> 2) * q_atom;  // 16 columns = 2 chunks; 4 such pieces per 64-column atom
       *reinterpret_cast<uint4*>(atom + tma::sw128_offset(t, 2 * (i & 3))) = lo;
       *reinterpret_cast<uint4*>(atom + tma::sw128_offset(t, 2 * (i & 3) + 1)) = hi;
+    };
+    const int np = hd >> 4;
+    for (int i0 = 0; i0 < np; i0 += 4) {
+      uint32_t ra[16], rb[16], rc[16], rd[16];
+      tmem_ld16(tlane + TM_O + 16 * i0, ra);
+      if (i0 + 1 < np) tmem_ld16(tlane + TM_O + 16 * (i0 + 1), rb);
+      if (i0 + 2 < np) tmem_ld16(tlane + TM_O + 16 * (i0 + 2), rc);
+      if (i0 + 3 < np) tmem_ld16(tlane + TM_O + 16 * (i0 + 3), rd);
+      tmem_ld_wait();
+      put(i0, ra);
+      if (i0 + 1 < np) put(i0 + 1, rb);
+      if (i0 + 2 < np) put(i0 + 2, rc);
+      if (i0 + 3 < np) put(i0 + 3, rd);
     }
     fence_proxy_async();  // generic-proxy writes -> visible to the TMA unit
     __syncthreads();
