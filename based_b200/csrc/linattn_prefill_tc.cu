@@ -406,34 +406,27 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       tmem_st_wait();
       fence_before_sync();
     };
-    if (mode == MODE_SEG_STATE) {
-      for (int c = 0; c < nchunks; ++c) {
-        expand_k(c);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_XK_READY + c % NPK));
-      }
-    } else {
-      // phi'(Q_c) goes first in a step and is announced on its own: it only waits for the readout of chunk c - 1, and
-      // the readout of chunk c needs nothing else from these warps, while phi'(K_{c+1}) also needs tile c + 1, the
-      // youngest load in flight, and is only needed by the state update at the end of the MMA thread's step.  The
-      // raw q of chunk c + 1 is taken into registers BEFORE the arrival for phi'(K_{c+1}), so that once the MMA
-      // thread has seen that arrival nothing on the CUDA cores reads tile c + 1's q or k any more - the producer
-      // relies on it when it refills a stage.
-      uint32_t XQ[8];
-      expand_k(0);
-      load_x(0, 0, XQ);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_XK_READY));
-      for (int c = 0; c < nchunks; ++c) {
+    // phi'(Q_c) goes first in a step and is announced on its own: it only waits for the readout of chunk c - 1, and
+    // the readout of chunk c needs nothing else from these warps, while phi'(K_{c+1}) also needs tile c + 1, the
+    // youngest load in flight, and is only needed by the state update at the end of the MMA thread's step.  The
+    // raw q of chunk c + 1 is taken into registers BEFORE the arrival for phi'(K_{c+1}), so that once the MMA
+    // thread has seen that arrival nothing on the CUDA cores reads tile c + 1's q or k any more - the producer
+    // relies on it when it refills a stage.  Step -1 only expands phi'(K_0); the state-only mode has no phi'(Q).
+    // (One loop for both modes, so that each expansion exists once in the kernel's code: the less code lies between
+    // the hot loops, the fewer instruction-cache misses reach the GPC's shared cache.)
+    const bool with_q = mode != MODE_SEG_STATE;
+    uint32_t XQ[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    for (int c = -1; c < nchunks; ++c) {
+      if (with_q && c >= 0) {
         expand_q(c, XQ);
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_XQ_READY));
-        if (c + 1 < nchunks) {
-          expand_k(c + 1);                               // waits for tile c + 1
-          load_x(c + 1, 0, XQ);
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(B_XK_READY + (c + 1) % NPK));
-        }
+      }
+      if (c + 1 < nchunks) {
+        expand_k(c + 1);                                 // waits for tile c + 1
+        if (with_q) load_x(c + 1, 0, XQ);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_XK_READY + (c + 1) % NPK));
       }
     }
   } else if (warp >= W_OUT && warp < W_MMA) {
