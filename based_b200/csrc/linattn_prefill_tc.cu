@@ -215,6 +215,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_v = tmem;
   const uint32_t tlane = tmem + ((uint32_t)(qd * 32) << 16);  // this warp's lane window, column 0
 
   // One thread feeds the stages: Q and K land as [k-half][token][16 B], V' as [8-column group][token][16 B] - the
@@ -275,8 +276,14 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       }
     }
   } else if (warp == W_MMA) {
-    // ================================================================ MMA issue: one thread runs the whole loop
-    if (lane == 0) {
+    // ================================================================ MMA issue.  The WHOLE warp runs the loop and the waits,
+    // converged, and one elected lane issues the MMAs and the commits: every operand of an MMA is then a value the
+    // compiler can see to be the same in all lanes (the TMEM base is broadcast by a shuffle for that reason), so
+    // the descriptors are built and kept in uniform registers instead of being moved there, several moves per MMA,
+    // by a single diverged lane - whose own instructions between two MMAs are idle tensor time.
+    {
+      const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_v, 0);
+      const bool leader = elect_one_sync();
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_o_pv = make_idesc_bf16(128, NV, 0, 1);   // A = P (TMEM), B = V' MN-major
       const uint32_t idesc_o_st = make_idesc_bf16(128, NV, 0, 0);   // A = phi'(Q) (TMEM), B = state K-major
@@ -292,73 +299,85 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
       // U(c): St^T (+)= V'(c)^T phi'(K_c)
       auto issue_update = [&](int c, bool acc0) {
         const uint64_t dv_c = d_v + (c % NS) * stage_units, d_pk_c = d_pk + (c % NPK) * (40960 >> 4);
+        if (leader) {
 #pragma unroll
-        for (int j = 0; j < C / 16; ++j)
-          mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (acc0 || j > 0) ? 1u : 0u);
+          for (int j = 0; j < C / 16; ++j)
+            mma_ss(tmem + TM_ST, dv_c + 16 * j, d_pk_c + 16 * j, idesc_st, (acc0 || j > 0) ? 1u : 0u);
+        }
       };
       if (mode == MODE_SEG_STATE) {
         // state only: St += V'(c)^T phi'(K_c) for every chunk of the segment
         for (int c = 0; c < nchunks; ++c) {
-          wait1(B_FULL + c % NS, c / NS, 0x210u);
-          wait1(B_XK_READY + c % NPK, c / NPK, 0x211u);
+          wait(B_FULL + c % NS, c / NS, 0x210u);
+          wait(B_XK_READY + c % NPK, c / NPK, 0x211u);
           fence_after_sync();
           issue_update(c, c > 0);
-          mma_commit(bar(B_EMPTY + c % NS));
-          mma_commit(bar(B_PK_FREE + c % NPK));
+          if (leader) {
+            mma_commit(bar(B_EMPTY + c % NS));
+            mma_commit(bar(B_PK_FREE + c % NPK));
+          }
         }
-        mma_commit(bar(B_FIN));
+        if (leader) mma_commit(bar(B_FIN));
       } else {
-        wait1(B_FULL + 0, 0, 0x200u);
+        wait(B_FULL + 0, 0, 0x200u);
         fence_after_sync();
-        mma_ss(tmem + TM_S, d_q, d_k, idesc_s, 0);
-        mma_commit(bar(B_S_DONE));
-        wait1(B_XK_READY, 0, 0x208u);                      // phi'(K_0)
-        if (has_init) wait1(B_INIT, 0, 0x207u);            // state^T and its bf16 copy were preloaded
+        if (leader) {
+          mma_ss(tmem + TM_S, d_q, d_k, idesc_s, 0);
+          mma_commit(bar(B_S_DONE));
+        }
+        wait(B_XK_READY, 0, 0x208u);                      // phi'(K_0)
+        if (has_init) wait(B_INIT, 0, 0x207u);            // state^T and its bf16 copy were preloaded
         fence_after_sync();
         issue_update(0, has_init);
-        mma_commit(bar(B_PK_FREE + 0));
+        if (leader) mma_commit(bar(B_PK_FREE + 0));
         for (int c = 0; c < nchunks; ++c) {
           const int st = c % NS;
           // PV(c): needs P(c) and a free O; the same barrier covers tile c + 1
-          wait1(B_A_READY, c, 0x201u);
+          wait(B_A_READY, c, 0x201u);
           fence_after_sync();
           {
             const uint64_t dv_c = d_v + st * stage_units;
+            if (leader) {
 #pragma unroll
-            for (int j = 0; j < C / 16; ++j)
-              mma_ts(tmem + TM_O, tmem + tm_p + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
+              for (int j = 0; j < C / 16; ++j)
+                mma_ts(tmem + TM_O, tmem + tm_p + 8 * j, dv_c + 16 * j, idesc_o_pv, j > 0);
+            }
           }
           // S(c+1): issued behind the P(c) reads above; the tensor core executes MMAs in issue order
           if (c + 1 < nchunks) {
             if (!full_via_a) {
-              wait1(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x203u);
+              wait(B_FULL + (c + 1) % NS, (c + 1) / NS, 0x203u);
               fence_after_sync();
             }
             const uint32_t so = ((c + 1) % NS) * stage_units;
-            mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
-            mma_commit(bar(B_S_DONE));
+            if (leader) {
+              mma_ss(tmem + TM_S, d_q + so, d_k + so, idesc_s, 0);
+              mma_commit(bar(B_S_DONE));
+            }
           }
           // R(c): O(c) += phi'(Q_c) State(c-1).  The bf16 state of chunk c-1 sits in buffer (c-1) & 1 and was
           // awaited before U(c) was issued (see below); a carried-in state was preloaded into buffer 1.
-          wait1(B_XQ_READY, c, 0x204u);                    // phi'(Q_c)
+          wait(B_XQ_READY, c, 0x204u);                    // phi'(Q_c)
           fence_after_sync();
           if (c > 0 || has_init) {
             const uint64_t d_stb_c = d_stb + ((c + 1) & 1) * stb_units;
+            if (leader) {
 #pragma unroll
-            for (int j = 0; j < DR / 16; ++j)
-              mma_ts(tmem + TM_O, tmem + tm_pq + 8 * j, d_stb_c + stb_step * j, idesc_o_st, 1);
+              for (int j = 0; j < DR / 16; ++j)
+                mma_ts(tmem + TM_O, tmem + tm_pq + 8 * j, d_stb_c + stb_step * j, idesc_o_st, 1);
+            }
           }
-          mma_commit(bar(B_O_DONE));
+          if (leader) mma_commit(bar(B_O_DONE));
           // U(c+1): must not start before the drain of State(c) has read the accumulator
           if (c + 1 < nchunks) {
-            wait1(B_STB_READY, c, 0x205u);
-            wait1(B_XK_READY + (c + 1) % NPK, (c + 1) / NPK, 0x206u);   // phi'(K_{c+1})
+            wait(B_STB_READY, c, 0x205u);
+            wait(B_XK_READY + (c + 1) % NPK, (c + 1) / NPK, 0x206u);   // phi'(K_{c+1})
             fence_after_sync();
             issue_update(c + 1, true);
-            mma_commit(bar(B_PK_FREE + (c + 1) % NPK));
+            if (leader) mma_commit(bar(B_PK_FREE + (c + 1) % NPK));
           }
         }
-        mma_commit(bar(B_FIN));   // every MMA is complete: the stages may be reused for the final state
+        if (leader) mma_commit(bar(B_FIN));   // every MMA is complete: the stages may be reused for the final state
       }
     }
   } else if (warp < 4) {
