@@ -97,8 +97,12 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
   const uint32_t TM_S = 0, TM_O = (uint32_t)NK;
 
   // ---- S = Q K^T as soon as Q and K have landed (V may still be in flight) ----
-  if (tid == 0) {
-    mbar_wait_bounded<false>(bar_qk, 0, abort_flag, p.status, 64u);
+  // Warp 0 runs the issue loops converged and one elected lane issues: the descriptors are then values the compiler
+  // can keep in uniform registers, instead of being moved there, several moves per MMA, by a single diverged lane.
+  const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+  const bool leader = warp == 0 && elect_one_sync();
+  if (warp == 0) {
+    mbar_wait_bounded(bar_qk, 0, abort_flag, p.status, 64u);
     fence_after_sync();
     const uint32_t idesc = make_idesc_bf16(128, NK, 0, 0);
     int first = 1;
@@ -107,11 +111,11 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
       for (int ks = 0; ks < ksteps; ++ks) {  // a K-step of 16 elements = 32 bytes inside the swizzled row
         const uint64_t da = make_smem_desc_sw128(sb + SM_Q + a * q_atom + ks * 32, 16, 1024);
         const uint64_t db = make_smem_desc_sw128(sb + SM_K + a * kv_atom + ks * 32, 16, 1024);
-        mma_ss(tmem + TM_S, da, db, idesc, first ? 0u : 1u);
+        if (leader) mma_ss(tmem_u + TM_S, da, db, idesc, first ? 0u : 1u);
         first = 0;
       }
     }
-    mma_commit(bar_s);
+    if (leader) mma_commit(bar_s);
   }
   __syncwarp();
 
@@ -208,15 +212,16 @@ __global__ void __launch_bounds__(NT) swa_prefill_tc_kernel(const __grid_constan
   __syncthreads();
 
   // ---- O = P V ----
-  if (tid == 0) {
-    mbar_wait_bounded<false>(bar_v, 0, abort_flag, p.status, 128u);
+  if (warp == 0) {
+    mbar_wait_bounded(bar_v, 0, abort_flag, p.status, 128u);
     fence_after_sync();
     // V tiles are MN-major: 64-column atoms kv_atom apart (LBO), groups of 8 keys 1024 B apart (SBO)
     const uint32_t idesc = make_idesc_bf16(128, hd, 0, 1);
-    for (int ks = 0; ks < (NK >> 4); ++ks)
-      mma_ts(tmem + TM_O, tmem + TM_S + 8 * ks, make_smem_desc_sw128(sb + SM_V + ks * 2048, kv_atom, 1024), idesc,
-             ks > 0);
-    mma_commit(bar_o);
+    for (int ks = 0; ks < (NK >> 4); ++ks) {
+      const uint64_t dvd = make_smem_desc_sw128(sb + SM_V + ks * 2048, kv_atom, 1024);
+      if (leader) mma_ts(tmem_u + TM_O, tmem_u + TM_S + 8 * ks, dvd, idesc, ks > 0);
+    }
+    if (leader) mma_commit(bar_o);
   }
   __syncwarp();
 
