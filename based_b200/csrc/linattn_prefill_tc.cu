@@ -184,8 +184,24 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
     mbar_wait_bounded<false>(bar(i), parity & 1u, abort_flag, p.status, code);
   };
 
-  // ------------------------------------------------------------------ set-up
-  if (tid == 0) {
+  // One thread feeds the stages: Q and K land as [k-half][token][16 B], V' as [8-column group][token][16 B] - the
+  // no-swizzle UMMA layouts - by one cp.async.bulk.tensor each (the tensor maps cut a row into 16-byte groups and
+  // put the group index outside the token index).  Tokens past the end of the sequence are zero-filled by the
+  // copy unit.  Chunk j goes to stage j % NS once the MMAs that read chunk j - NS have completed.
+  const bool need_q = mode != MODE_SEG_STATE;
+  auto issue_tile = [&](int j) {
+    const int st = j % NS;
+    const uint32_t base = sb + st * lay.stage_bytes;
+    const int tok = tok_base + j * C;
+    tma::mbar_expect_tx(bar(B_FULL + st), (need_q ? 8192u : 4096u) + (uint32_t)dv * 256u);
+    if (need_q) tma::load_5d(base, &p.mq, bar(B_FULL + st), 0, tok, 0, h, b);
+    tma::load_5d(base + 4096, &p.mk, bar(B_FULL + st), 0, tok, 0, h, b);
+    tma::load_5d(base + 8192, &p.mv, bar(B_FULL + st), 0, tok, 0, h, b);
+  };
+
+  // ------------------------------------------------------------------ set-up (by the producer thread, which then
+  // requests the first tiles at once: they travel while TMEM is allocated and the constants are written)
+  if (tid == W_LOAD * 32) {
     for (int i = 0; i < 3; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
     mbar_init(bar(B_S_DONE), 1);
     mbar_init(bar(B_O_DONE), 1);
@@ -201,6 +217,7 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
     mbar_init(bar(B_FIN), 1);
     *abort_flag = 0;
     fence_mbar_init();
+    for (int j = 0; j < min(NS, nchunks); ++j) issue_tile(j);
   }
   __syncwarp();
   if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TM_COLS);
@@ -217,21 +234,6 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_v = tmem;
   const uint32_t tlane = tmem + ((uint32_t)(qd * 32) << 16);  // this warp's lane window, column 0
-
-  // One thread feeds the stages: Q and K land as [k-half][token][16 B], V' as [8-column group][token][16 B] - the
-  // no-swizzle UMMA layouts - by one cp.async.bulk.tensor each (the tensor maps cut a row into 16-byte groups and
-  // put the group index outside the token index).  Tokens past the end of the sequence are zero-filled by the
-  // copy unit.  Chunk j goes to stage j % NS once the MMAs that read chunk j - NS have completed.
-  const bool need_q = mode != MODE_SEG_STATE;
-  auto issue_tile = [&](int j) {
-    const int st = j % NS;
-    const uint32_t base = sb + st * lay.stage_bytes;
-    const int tok = tok_base + j * C;
-    tma::mbar_expect_tx(bar(B_FULL + st), (need_q ? 8192u : 4096u) + (uint32_t)dv * 256u);
-    if (need_q) tma::load_5d(base, &p.mq, bar(B_FULL + st), 0, tok, 0, h, b);
-    tma::load_5d(base + 4096, &p.mk, bar(B_FULL + st), 0, tok, 0, h, b);
-    tma::load_5d(base + 8192, &p.mv, bar(B_FULL + st), 0, tok, 0, h, b);
-  };
 
   // the polynomial of chunk c by this warp (pieces [p0, p1)), then one arrival on B_A_READY - which, with three
   // stages, also vouches for tile c + 1 having landed (it was requested two chunks earlier), so that the MMA thread
@@ -260,14 +262,11 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
     // lane 0 is also the TMA producer
     if (mode == MODE_SEG_STATE) {
       if (warp == W_LOAD && lane == 0)
-        for (int j = 0; j < nchunks; ++j) {
+        for (int j = min(NS, nchunks); j < nchunks; ++j) {
           if (j >= NS) wait1(B_EMPTY + j % NS, j / NS - 1, 0x100u);   // the update that read tile j - NS is complete
           issue_tile(j);
         }
     } else {
-      if (warp == W_LOAD && lane == 0)
-        for (int j = 0; j < min(NS, nchunks); ++j) issue_tile(j);
-      __syncwarp();
       // quadrant 3 is shared with warp 7 when that warp has no state rows to drain
       const bool shared_q3 = qd == 3 && !q3_has_state;
       const int p0 = shared_q3 ? 2 : 0;
@@ -658,22 +657,24 @@ __global__ void __launch_bounds__(NT, 1) linattn_prefill_tc_kernel(const __grid_
     }
   } else if (write_state) {
     const float* stg = reinterpret_cast<const float*>(smem);
-    const int total = (dv + 1) * kExpandedDim;
-    for (int e = tid; e < total; e += NT) {
-      const int n = e / kExpandedDim, f = e - n * kExpandedDim;
+    // thread f walks the dv + 1 rows of feature f: its place in the packed vector is worked out once, and a warp's
+    // stores of one row are contiguous
+    for (int f = tid; f < kExpandedDim; f += NT) {
       bool offdiag;
       const int idx = packed_index(f, offdiag);
-      float val = stg[n * STAGE_STRIDE_F + idx];
-      if (offdiag) val *= 0.70710678118654752f;
-      if (n < dv) {
-        const size_t o = (size_t)bh * dv * kExpandedDim + e;
+      const float scale = offdiag ? 0.70710678118654752f : 1.0f;
+      const size_t kv0 = (size_t)bh * dv * kExpandedDim + f;
+#pragma unroll 4
+      for (int n = 0; n < dv; ++n) {
+        const float val = stg[n * STAGE_STRIDE_F + idx] * scale;
+        const size_t o = kv0 + (size_t)n * kExpandedDim;
         if (p.state_bf16) static_cast<__nv_bfloat16*>(p.kv_state)[o] = __float2bfloat16_rn(val);
         else static_cast<float*>(p.kv_state)[o] = val;
-      } else {
-        const size_t o = (size_t)bh * kExpandedDim + f;
-        if (p.state_bf16) static_cast<__nv_bfloat16*>(p.k_state)[o] = __float2bfloat16_rn(val);
-        else static_cast<float*>(p.k_state)[o] = val;
       }
+      const float val = stg[dv * STAGE_STRIDE_F + idx] * scale;
+      const size_t o = (size_t)bh * kExpandedDim + f;
+      if (p.state_bf16) static_cast<__nv_bfloat16*>(p.k_state)[o] = __float2bfloat16_rn(val);
+      else static_cast<float*>(p.k_state)[o] = val;
     }
   }
   __syncthreads();
