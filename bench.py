@@ -637,6 +637,10 @@ def main():
         sampler = ClockSampler(local_rank) if rank == 0 else None
         if sampler:
             sampler.start()
+        # With several ranks, a barrier BEFORE the untimed steps lines the ranks up (their start-up times differ by
+        # seconds), so that the barrier in front of the timed region is a short wait and not a long idle period on
+        # the ranks that came first.
+        barrier()
         steps(PREROLL)
         steps(W)
         barrier()
