@@ -641,7 +641,11 @@ def main():
         # seconds), so that the barrier in front of the timed region is a short wait and not a long idle period on
         # the ranks that came first.
         barrier()
-        steps(PREROLL)
+        # The untimed steps are drained in slices: with a thousand launches queued ahead of the GPU, the first
+        # region after them measured 3-8 % slower than the following ones (and than after a drained pre-roll).
+        for _ in range(PREROLL // 200):
+            steps(200)
+            torch.cuda.synchronize()
         steps(W)
         barrier()
         times = []
